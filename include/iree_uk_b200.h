@@ -1,0 +1,370 @@
+/*
+ * iree_uk_b200.h — C ABI of the B200 (sm_100a) data-tiled contraction library.
+ *
+ * The library is a drop-in for the three IREE microkernels
+ *   iree_uk_mmt4d   (runtime/src/iree/builtins/ukernel/mmt4d.h:14-22)
+ *   iree_uk_pack    (runtime/src/iree/builtins/ukernel/pack.h:26-34)
+ *   iree_uk_unpack  (runtime/src/iree/builtins/ukernel/unpack.h:17-25)
+ * with the same parameter structs, the same flag values and the same 4-D tiled
+ * layouts, except that every buffer is a CUDA device pointer and every call takes the
+ * CUDA stream the work is enqueued on (for IREE that is the dispatch stream owned by
+ * the CUDA HAL device, runtime/src/iree/hal/drivers/cuda/cuda_device.c:542-547).
+ *
+ * Contract shared by all entry points
+ *   - asynchronous: kernels are enqueued on `cu_stream` in call order; the stream is
+ *     never synchronised and no other stream is touched;
+ *   - no implicit device allocation: scratch memory, when a fast path wants it, is
+ *     passed in by the caller (see iree_uk_b200_mmt4d_ws);
+ *   - arguments are validated on the host with the reference's rules
+ *     (mmt4d.c:12-48, pack.c:51-104, unpack.c:31-82) and a violation returns
+ *     IREE_UK_B200_INVALID_ARGUMENT instead of asserting; nothing is launched then;
+ *   - bytes of the output allocation that the reference does not write are never
+ *     written (pinned by the whole-buffer memcmp of tools/mmt4d_test.c:430-440);
+ *   - offsets and strides are in elements, exactly as in the reference; for the u4
+ *     right-hand side they must be even (whole bytes, mmt4d.c:39-46);
+ *   - `cpu_data` is ignored and may be NULL;
+ *   - thread-safe; one CUDA device per call (the one `cu_stream` belongs to must be
+ *     current on the calling thread).
+ *
+ * This header is plain C99 and also valid C++.
+ */
+#ifndef IREE_UK_B200_H_
+#define IREE_UK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define IREE_UK_B200_EXPORT __declspec(dllexport)
+#else
+#define IREE_UK_B200_EXPORT __attribute__((visibility("default")))
+#endif
+
+/* iree_uk_index_t is int64 on 64-bit hosts (ukernel/common.h:269-275). */
+typedef int64_t iree_uk_index_t;
+
+/*===----------------------------------------------------------------------===*/
+/* Flags — values frozen by ukernel/exported_bits.h:29-83                      */
+/*===----------------------------------------------------------------------===*/
+
+#define IREE_UK_FLAG_MMT4D_TYPE_MASK 0xFF
+#define IREE_UK_FLAG_MMT4D_TYPE_NONE 0x00
+#define IREE_UK_FLAG_MMT4D_TYPE_F32F32F32 0x01
+#define IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 0x02
+#define IREE_UK_FLAG_MMT4D_TYPE_F16F16F32 0x03
+#define IREE_UK_FLAG_MMT4D_TYPE_F16F16F16 0x04
+#define IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32 0x05
+#define IREE_UK_FLAG_MMT4D_TYPE_BF16BF16BF16 0x06
+#define IREE_UK_FLAG_MMT4D_TYPE_S16S16S32 0x07
+#define IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 0x08
+#define IREE_UK_FLAG_MMT4D_TYPE_S16S8S32 0x09
+#define IREE_UK_FLAG_MMT4D_TYPE_S8S4S32 0x0A
+#define IREE_UK_FLAG_MMT4D_TYPE_END 0x0B
+#define IREE_UK_FLAG_MMT4D_ACCUMULATE 0x100
+#define IREE_UK_FLAG_MMT4D_ALLOW_GENERIC_FALLBACK_TILE_FUNCTION 0x200
+#define IREE_UK_FLAG_MMT4D_SKIP_INTERMEDIATE_ROUNDINGS 0x400
+#define IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION 0x1
+
+#define IREE_UK_FLAG_PACK_TYPE_MASK 0xFF
+#define IREE_UK_FLAG_PACK_TYPE_NONE 0x00
+#define IREE_UK_FLAG_PACK_TYPE_F32F32 0x01
+#define IREE_UK_FLAG_PACK_TYPE_I8I8 0x02
+#define IREE_UK_FLAG_PACK_TYPE_I32I32 0x03
+#define IREE_UK_FLAG_PACK_TYPE_F16F16 0x04
+#define IREE_UK_FLAG_PACK_TYPE_BF16BF16 0x05
+#define IREE_UK_FLAG_PACK_TRANSPOSE_INNER 0x100
+#define IREE_UK_FLAG_PACK_TRANSPOSE_OUTER 0x200
+
+#define IREE_UK_FLAG_UNPACK_TYPE_MASK 0xFF
+#define IREE_UK_FLAG_UNPACK_TYPE_NONE 0x00
+#define IREE_UK_FLAG_UNPACK_TYPE_F32F32 0x01
+#define IREE_UK_FLAG_UNPACK_TYPE_I32I32 0x03
+#define IREE_UK_FLAG_UNPACK_TYPE_F16F16 0x04
+#define IREE_UK_FLAG_UNPACK_TYPE_BF16BF16 0x05
+#define IREE_UK_FLAG_UNPACK_TRANSPOSE_INNER 0x100
+#define IREE_UK_FLAG_UNPACK_TRANSPOSE_OUTER 0x200
+
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_MASK 0xFF
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_LHS 0x01
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_RHS 0x02
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_RESULT 0x03
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MASK 0xFF00
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F32F32F32 0x0100
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_I8I8I32 0x0200
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F16F16F32 0x0300
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F16F16F16 0x0400
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16F32 0x0500
+#define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16BF16 0x0600
+
+/*===----------------------------------------------------------------------===*/
+/* Parameter structs — field-for-field the reference's                         */
+/*===----------------------------------------------------------------------===*/
+
+/* ukernel/mmt4d_internal.h:14-32. 120 bytes on LP64.
+ * out[i][j][i0][j0] (+)= sum_{k,k0} lhs[i][k][i0][k0] * rhs[j][k][j0][k0]
+ * lhs element index: lhs_offset + i*lhs_stride0 + k*M0*K0 + i0*K0 + k0
+ * rhs element index: rhs_offset + j*rhs_stride0 + k*N0*K0 + j0*K0 + k0
+ * out element index: out_offset + i*out_stride0 + j*M0*N0 + i0*N0 + j0 */
+typedef struct iree_uk_mmt4d_params_t {
+  const void* lhs_buffer; /* device pointer */
+  iree_uk_index_t lhs_offset;
+  iree_uk_index_t lhs_stride0;
+  const void* rhs_buffer; /* device pointer */
+  iree_uk_index_t rhs_offset;
+  iree_uk_index_t rhs_stride0;
+  void* out_buffer; /* device pointer */
+  iree_uk_index_t out_offset;
+  iree_uk_index_t out_stride0;
+  iree_uk_index_t M; /* number of LHS tile rows   (M1) */
+  iree_uk_index_t N; /* number of RHS tile rows   (N1) */
+  iree_uk_index_t K; /* number of tiles along K   (K1) */
+  int32_t M0;
+  int32_t N0;
+  int32_t K0;
+  uint32_t flags;
+  const uint64_t* cpu_data; /* ignored */
+} iree_uk_mmt4d_params_t;
+
+/* ukernel/pack_internal.h:12-30. 136 bytes on LP64. */
+typedef struct iree_uk_pack_params_t {
+  const void* in_buffer; /* device pointer */
+  iree_uk_index_t in_offset;
+  iree_uk_index_t in_stride0;
+  iree_uk_index_t in_stride1;
+  void* out_buffer; /* device pointer */
+  iree_uk_index_t out_offset;
+  iree_uk_index_t out_stride0;
+  iree_uk_index_t out_stride1; /* must equal out_size2*out_size3 (pack.c:72) */
+  iree_uk_index_t in_size0;
+  iree_uk_index_t in_size1;
+  iree_uk_index_t out_size0;
+  iree_uk_index_t out_size1;
+  iree_uk_index_t out_size2;
+  iree_uk_index_t out_size3;
+  uint64_t padding_value; /* low elem-size bytes are the fill pattern (pack.h:16-25) */
+  uint32_t flags;
+  const uint64_t* cpu_data; /* ignored */
+} iree_uk_pack_params_t;
+
+/* ukernel/unpack_internal.h:12-29. 128 bytes on LP64. */
+typedef struct iree_uk_unpack_params_t {
+  const void* in_buffer; /* device pointer */
+  iree_uk_index_t in_offset;
+  iree_uk_index_t in_stride0;
+  iree_uk_index_t in_stride1; /* must equal in_size2*in_size3 (unpack.c:49) */
+  void* out_buffer;           /* device pointer */
+  iree_uk_index_t out_offset;
+  iree_uk_index_t out_stride0;
+  iree_uk_index_t out_stride1;
+  iree_uk_index_t in_size0;
+  iree_uk_index_t in_size1;
+  iree_uk_index_t in_size2;
+  iree_uk_index_t in_size3;
+  iree_uk_index_t out_size0;
+  iree_uk_index_t out_size1;
+  uint32_t flags;
+  const uint64_t* cpu_data; /* ignored */
+} iree_uk_unpack_params_t;
+
+/* ukernel/query_tile_sizes.h:17-24. */
+typedef struct iree_uk_query_tile_sizes_2d_params_t {
+  uint32_t flags;
+  iree_uk_index_t size0;
+  iree_uk_index_t size1;
+  const uint64_t* cpu_data; /* ignored */
+} iree_uk_query_tile_sizes_2d_params_t;
+
+/* ukernel/query_tile_sizes.h:26-29. */
+typedef struct iree_uk_query_tile_sizes_2d_out_params_t {
+  iree_uk_index_t tile_size0;
+  iree_uk_index_t tile_size1;
+} iree_uk_query_tile_sizes_2d_out_params_t;
+
+/*===----------------------------------------------------------------------===*/
+/* Status codes (the reference returns void and asserts; this ABI reports)     */
+/*===----------------------------------------------------------------------===*/
+
+typedef enum iree_uk_b200_status_t {
+  IREE_UK_B200_OK = 0,
+  IREE_UK_B200_INVALID_ARGUMENT = 1, /* a reference *_validate rule is violated   */
+  IREE_UK_B200_UNSUPPORTED = 2,      /* valid for the reference, not served here  */
+  IREE_UK_B200_CUDA_ERROR = 3,       /* a CUDA runtime/driver call failed         */
+  IREE_UK_B200_WORKSPACE_TOO_SMALL = 4,
+  IREE_UK_B200_DEVICE_TIMEOUT = 5 /* a bounded device-side wait gave up          */
+} iree_uk_b200_status_t;
+
+IREE_UK_B200_EXPORT const char* iree_uk_b200_status_string(int status);
+
+/*===----------------------------------------------------------------------===*/
+/* Which kernel serves a call (reported, never a CPU path)                     */
+/*===----------------------------------------------------------------------===*/
+
+typedef enum iree_uk_b200_path_t {
+  IREE_UK_B200_PATH_NONE = 0,         /* early-out: nothing is launched            */
+  IREE_UK_B200_PATH_GENERIC = 1,      /* CUDA-core kernel, any tile shape / stride */
+  IREE_UK_B200_PATH_TCGEN05 = 2,      /* TMA + tcgen05 + TMEM, operands read as is */
+  IREE_UK_B200_PATH_TCGEN05_RETILE = 3, /* re-tile pre-pass into workspace, then 2 */
+  IREE_UK_B200_PATH_GEMV = 4,         /* s16u4s32 M0=1 weight-streaming kernel     */
+  IREE_UK_B200_PATH_FAST_COPY = 5,    /* pack/unpack 16-byte vectorised relayout   */
+  IREE_UK_B200_PATH_ZERO_FILL = 6     /* K==0 without ACCUMULATE: zero the tiles   */
+} iree_uk_b200_path_t;
+
+/*===----------------------------------------------------------------------===*/
+/* mmt4d                                                                       */
+/*===----------------------------------------------------------------------===*/
+
+/* Replaces iree_uk_mmt4d_p (ukernel/mmt4d.c:115-141). Uses no scratch memory: shapes
+ * whose tensor-core path wants a re-tiled operand run the generic kernel here; call
+ * iree_uk_b200_mmt4d_ws to let them use the tensor-core path. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d(const iree_uk_mmt4d_params_t* params,
+                                           void* cu_stream);
+
+/* Bytes of scratch iree_uk_b200_mmt4d_ws can use for `params` (0 when the call is served
+ * without scratch). The size depends on M,N,K,M0,N0,K0 and the type only. */
+IREE_UK_B200_EXPORT size_t
+iree_uk_b200_mmt4d_workspace_size(const iree_uk_mmt4d_params_t* params);
+
+/* Same operation as iree_uk_b200_mmt4d with caller-owned scratch (256-byte aligned
+ * device memory, at least iree_uk_b200_mmt4d_workspace_size bytes, free to reuse once
+ * the enqueued work has completed). Replaces iree_uk_mmt4d_p (ukernel/mmt4d.c:115-141). */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* params,
+                                              void* workspace, size_t workspace_bytes,
+                                              void* cu_stream);
+
+/* Flat-argument twin of iree_uk_mmt4d (ukernel/mmt4d.h:14-22, mmt4d.c:151-177) with the
+ * workspace and the stream appended; `cpu_data` is kept in the list so a call site can be
+ * substituted one for one. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_flat(
+    const void* lhs_buffer, iree_uk_index_t lhs_offset, iree_uk_index_t lhs_stride0,
+    const void* rhs_buffer, iree_uk_index_t rhs_offset, iree_uk_index_t rhs_stride0,
+    void* out_buffer, iree_uk_index_t out_offset, iree_uk_index_t out_stride0,
+    iree_uk_index_t M, iree_uk_index_t N, iree_uk_index_t K, int32_t M0, int32_t N0,
+    int32_t K0, uint32_t flags, const uint64_t* cpu_data, void* workspace,
+    size_t workspace_bytes, void* cu_stream);
+
+/* Replaces iree_uk_mmt4d_info (ukernel/mmt4d.h:25-27, mmt4d.c:143-149): bit 0 is set when
+ * a tensor-core (tcgen05) kernel exists for this (types, M0, N0, K0). */
+IREE_UK_B200_EXPORT uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0,
+                                                     uint32_t flags);
+
+/* Which kernel iree_uk_b200_mmt4d_ws (with_workspace != 0) or iree_uk_b200_mmt4d
+ * (with_workspace == 0) would launch for `params`; an iree_uk_b200_path_t, or a negative
+ * status when the parameters are rejected. Mirrors the tile-function selection of
+ * ukernel/mmt4d.c:124-138. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_path(const iree_uk_mmt4d_params_t* params,
+                                                int with_workspace);
+
+/* Parameters of GPU `rank` of `world` when the N dimension (RHS tile rows = weight tiles)
+ * is split contiguously across GPUs: rank r owns tile rows [r*N/world, (r+1)*N/world)
+ * (remainder spread over the first ranks). `rhs_is_local` != 0 means the caller's
+ * rhs_buffer already holds only this rank's rows (rhs_offset is kept); otherwise the
+ * offset is advanced inside a full RHS. `out_is_local` != 0 means out_buffer is a slab
+ * [M][N_local][M0][N0] (out_stride0 is set to N_local*M0*N0); otherwise the slab is
+ * addressed inside a full [M][N][M0][N0] output through out_offset. The j loop of
+ * ukernel/mmt4d.c:84-98 only advances rhs_panel and out_tile, which is why this needs no
+ * reduction. Returns the first owned tile row in *n_begin (may be NULL). */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_shard_params(
+    const iree_uk_mmt4d_params_t* full, int rank, int world, int rhs_is_local,
+    int out_is_local, iree_uk_mmt4d_params_t* shard, iree_uk_index_t* n_begin);
+
+/* Interleaves `world` gathered output slabs [r][M][N_r][M0*N0] (the layout an all-gather of
+ * equal slabs produces) into one [M][N][M0*N0] buffer; elem_size in bytes. N must be
+ * divisible by world. No counterpart in the reference (its callers never shard). */
+IREE_UK_B200_EXPORT int iree_uk_b200_interleave_slabs(const void* gathered, void* out,
+                                                      iree_uk_index_t M, iree_uk_index_t N,
+                                                      iree_uk_index_t tile_elems,
+                                                      int elem_size, int world,
+                                                      void* cu_stream);
+
+/*===----------------------------------------------------------------------===*/
+/* pack / unpack                                                               */
+/*===----------------------------------------------------------------------===*/
+
+/* Replaces iree_uk_pack_p (ukernel/pack.c:315-322). */
+IREE_UK_B200_EXPORT int iree_uk_b200_pack(const iree_uk_pack_params_t* params,
+                                          void* cu_stream);
+
+/* Flat-argument twin of iree_uk_pack (ukernel/pack.h:26-34, pack.c:325-352). */
+IREE_UK_B200_EXPORT int iree_uk_b200_pack_flat(
+    const void* in_buffer, iree_uk_index_t in_offset, iree_uk_index_t in_stride0,
+    iree_uk_index_t in_stride1, void* out_buffer, iree_uk_index_t out_offset,
+    iree_uk_index_t out_stride0, iree_uk_index_t out_stride1, iree_uk_index_t in_size0,
+    iree_uk_index_t in_size1, iree_uk_index_t out_size0, iree_uk_index_t out_size1,
+    iree_uk_index_t out_size2, iree_uk_index_t out_size3, uint64_t padding_value,
+    uint32_t flags, const uint64_t* cpu_data, void* cu_stream);
+
+/* Which kernel serves the pack call (iree_uk_b200_path_t) or a negative status. Mirrors
+ * iree_uk_pack_select_tile_func (ukernel/pack_tile.c:57-71). */
+IREE_UK_B200_EXPORT int iree_uk_b200_pack_path(const iree_uk_pack_params_t* params);
+
+/* Replaces iree_uk_unpack_p (ukernel/unpack.c:249-257). */
+IREE_UK_B200_EXPORT int iree_uk_b200_unpack(const iree_uk_unpack_params_t* params,
+                                            void* cu_stream);
+
+/* Flat-argument twin of iree_uk_unpack (ukernel/unpack.h:17-25, unpack.c:259-285). */
+IREE_UK_B200_EXPORT int iree_uk_b200_unpack_flat(
+    const void* in_buffer, iree_uk_index_t in_offset, iree_uk_index_t in_stride0,
+    iree_uk_index_t in_stride1, void* out_buffer, iree_uk_index_t out_offset,
+    iree_uk_index_t out_stride0, iree_uk_index_t out_stride1, iree_uk_index_t in_size0,
+    iree_uk_index_t in_size1, iree_uk_index_t in_size2, iree_uk_index_t in_size3,
+    iree_uk_index_t out_size0, iree_uk_index_t out_size1, uint32_t flags,
+    const uint64_t* cpu_data, void* cu_stream);
+
+/* Which kernel serves the unpack call, as for pack. Mirrors
+ * iree_uk_unpack_select_tile_func (ukernel/unpack_tile.c:57-71). */
+IREE_UK_B200_EXPORT int iree_uk_b200_unpack_path(const iree_uk_unpack_params_t* params);
+
+/*===----------------------------------------------------------------------===*/
+/* query_tile_sizes                                                            */
+/*===----------------------------------------------------------------------===*/
+
+/* Replaces iree_uk_query_tile_sizes_2d (ukernel/query_tile_sizes.c:65-76): the (M0,K0),
+ * (N0,K0) or (M0,N0) tile a caller should pack with so that mmt4d lands on the tensor-core
+ * path: M0xN0xK0 = 16x16x1 for f16, 16x16x2 for bf16 and i8 — the shapes the reference's
+ * x86-64 encoder picks (compiler/src/iree/compiler/Codegen/ExternalInterfaces/
+ * CPUEncodingExternalModels.cpp:479-585) — and, for f32 (no tensor-core kernel here), the
+ * 16x16x1 the reference answers on AVX-512 (ukernel/arch/x86_64/
+ * query_tile_sizes_x86_64_entry_point.c:10-25). */
+IREE_UK_B200_EXPORT int iree_uk_b200_query_tile_sizes_2d(
+    const iree_uk_query_tile_sizes_2d_params_t* params,
+    iree_uk_query_tile_sizes_2d_out_params_t* out_params);
+
+/*===----------------------------------------------------------------------===*/
+/* Device-side status                                                          */
+/*===----------------------------------------------------------------------===*/
+
+/* Every device-side wait in this library (mbarrier phases of the TMA/MMA pipeline) is
+ * bounded; a wait that runs out records a code in a per-device status word and the kernel
+ * returns. This call synchronises `cu_stream`, reads and clears that word and returns
+ * IREE_UK_B200_OK or IREE_UK_B200_DEVICE_TIMEOUT; *detail (may be NULL) receives the raw
+ * word. It is the only entry point that synchronises. No counterpart in the reference. */
+IREE_UK_B200_EXPORT int iree_uk_b200_device_status(void* cu_stream, uint32_t* detail);
+
+/* Library build identification: "iree_uk_b200 <version> sm_100a". */
+IREE_UK_B200_EXPORT const char* iree_uk_b200_version(void);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#if defined(__cplusplus)
+static_assert(sizeof(iree_uk_mmt4d_params_t) == 120, "mmt4d params layout");
+static_assert(sizeof(iree_uk_pack_params_t) == 136, "pack params layout");
+static_assert(sizeof(iree_uk_unpack_params_t) == 128, "unpack params layout");
+static_assert(offsetof(iree_uk_mmt4d_params_t, M0) == 96, "mmt4d params layout");
+static_assert(offsetof(iree_uk_mmt4d_params_t, flags) == 108, "mmt4d params layout");
+static_assert(offsetof(iree_uk_mmt4d_params_t, cpu_data) == 112, "mmt4d params layout");
+static_assert(offsetof(iree_uk_pack_params_t, padding_value) == 112, "pack params layout");
+static_assert(offsetof(iree_uk_pack_params_t, flags) == 120, "pack params layout");
+static_assert(offsetof(iree_uk_unpack_params_t, flags) == 112, "unpack params layout");
+#else
+_Static_assert(sizeof(iree_uk_mmt4d_params_t) == 120, "mmt4d params layout");
+_Static_assert(sizeof(iree_uk_pack_params_t) == 136, "pack params layout");
+_Static_assert(sizeof(iree_uk_unpack_params_t) == 128, "unpack params layout");
+#endif
+
+#endif /* IREE_UK_B200_H_ */
