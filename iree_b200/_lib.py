@@ -1,0 +1,55 @@
+"""Loads ``libiree_uk_b200.so`` and declares the C ABI of ``include/iree_uk_b200.h``.
+
+There is no fallback: if the shared library is missing or lacks a symbol, importing this
+module raises. Build it with ``python -m iree_b200.build``.
+"""
+import ctypes as C
+import os
+
+from . import abi
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libiree_uk_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "%s not found: the CUDA library is not built (python -m iree_b200.build). "
+        "There is no CPU or PyTorch fallback for this path." % LIB_PATH)
+
+lib = C.CDLL(LIB_PATH)
+
+_P, _I, _i32, _u32, _u64, _sz = C.c_void_p, abi.index_t, C.c_int32, C.c_uint32, C.c_uint64, C.c_size_t
+
+#: every symbol the public header declares: name -> (restype, argtypes)
+SIGNATURES = {
+    "iree_uk_b200_status_string": (C.c_char_p, [C.c_int]),
+    "iree_uk_b200_version": (C.c_char_p, []),
+    "iree_uk_b200_mmt4d": (C.c_int, [_P, _P]),
+    "iree_uk_b200_mmt4d_workspace_size": (_sz, [_P]),
+    "iree_uk_b200_mmt4d_ws": (C.c_int, [_P, _P, _sz, _P]),
+    "iree_uk_b200_mmt4d_flat": (C.c_int, [_P, _I, _I, _P, _I, _I, _P, _I, _I, _I, _I, _I, _i32,
+                                          _i32, _i32, _u32, _P, _P, _sz, _P]),
+    "iree_uk_b200_mmt4d_info": (_u32, [_i32, _i32, _i32, _u32]),
+    "iree_uk_b200_mmt4d_path": (C.c_int, [_P, C.c_int]),
+    "iree_uk_b200_mmt4d_shard_params": (C.c_int, [_P, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "iree_uk_b200_interleave_slabs": (C.c_int, [_P, _P, _I, _I, _I, C.c_int, C.c_int, _P]),
+    "iree_uk_b200_pack": (C.c_int, [_P, _P]),
+    "iree_uk_b200_pack_flat": (C.c_int, [_P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                                         _u64, _u32, _P, _P]),
+    "iree_uk_b200_pack_path": (C.c_int, [_P]),
+    "iree_uk_b200_unpack": (C.c_int, [_P, _P]),
+    "iree_uk_b200_unpack_flat": (C.c_int, [_P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I,
+                                           _u32, _P, _P]),
+    "iree_uk_b200_unpack_path": (C.c_int, [_P]),
+    "iree_uk_b200_query_tile_sizes_2d": (C.c_int, [_P, _P]),
+    "iree_uk_b200_device_status": (C.c_int, [_P, _P]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)  # AttributeError if the library lacks a declared symbol
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+# internal entry point (not in the public header): explicit operand-staging variant
+lib.iree_uk_b200_debug_mmt4d_variant.restype = C.c_int
+lib.iree_uk_b200_debug_mmt4d_variant.argtypes = [_P, _P, _sz, C.c_int, _P]

@@ -1,0 +1,346 @@
+// extern "C" entry points of libiree_uk_b200.so: validation, kernel selection, launch.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "uk_common.h"
+
+namespace uk {
+
+// Written by kernels whose bounded waits ran out; lives in each device's static memory, so
+// nothing is allocated for it.
+__device__ uint32_t g_status_word;
+
+uint32_t* device_status_word() {
+  constexpr int kMaxDevices = 64;
+  static uint32_t* addr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+    addr[dev] = static_cast<uint32_t*>(p);
+  }
+  return addr[dev];
+}
+
+namespace {
+
+enum class Mmt4dPath { None, Generic, Tc, TcRetile, Gemv, ZeroFill };
+
+// Kernel selection, the analogue of ukernel/mmt4d.c:105-138 (early-out, then an
+// architecture-specific tile function, else the generic one).
+int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path) {
+  const int rc = validate_mmt4d(p);
+  if (rc) return rc;
+  const bool acc = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) != 0;
+  if (p->M == 0 || p->N == 0 || (p->K == 0 && acc)) { *path = Mmt4dPath::None; return 0; }
+  Mmt4dTypes t;
+  mmt4d_types(p->flags, &t);
+  if (elem_bits(t.out) != 32) return IREE_UK_B200_UNSUPPORTED;  // f16/bf16 outputs: not served yet
+  // A zero-sized inner tile addresses no output element.
+  if (p->M0 == 0 || p->N0 == 0) { *path = Mmt4dPath::None; return 0; }
+  if (p->K == 0 || p->K0 == 0) { *path = Mmt4dPath::ZeroFill; return 0; }
+  const bool force_generic = env_flag("IREE_UK_B200_FORCE_GENERIC");
+  if (!force_generic) {
+    if (mmt4d_gemv_s16u4_eligible(p)) { *path = Mmt4dPath::Gemv; return 0; }
+    if (have_ws && mmt4d_tc_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
+  }
+  *path = Mmt4dPath::Generic;
+  return 0;
+}
+
+int path_code(Mmt4dPath p) {
+  switch (p) {
+    case Mmt4dPath::None: return IREE_UK_B200_PATH_NONE;
+    case Mmt4dPath::Generic: return IREE_UK_B200_PATH_GENERIC;
+    case Mmt4dPath::Tc: return IREE_UK_B200_PATH_TCGEN05;
+    case Mmt4dPath::TcRetile: return IREE_UK_B200_PATH_TCGEN05_RETILE;
+    case Mmt4dPath::Gemv: return IREE_UK_B200_PATH_GEMV;
+    default: return IREE_UK_B200_PATH_ZERO_FILL;
+  }
+}
+
+int run_mmt4d(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, bool have_ws,
+              void* cu_stream) {
+  Mmt4dPath path;
+  const int rc = select_mmt4d(p, have_ws, &path);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  switch (path) {
+    case Mmt4dPath::None: return IREE_UK_B200_OK;
+    case Mmt4dPath::ZeroFill: return launch_mmt4d_zero_fill(p, stream);
+    case Mmt4dPath::Gemv: return launch_mmt4d_gemv_s16u4(p, stream);
+    case Mmt4dPath::TcRetile: return launch_mmt4d_tc(p, ws, ws_bytes, kTcVariantDefault, stream);
+    default: return launch_mmt4d_generic(p, stream);
+  }
+}
+
+}  // namespace
+}  // namespace uk
+
+using namespace uk;
+
+extern "C" {
+
+const char* iree_uk_b200_status_string(int status) {
+  switch (status) {
+    case IREE_UK_B200_OK: return "OK";
+    case IREE_UK_B200_INVALID_ARGUMENT: return "INVALID_ARGUMENT";
+    case IREE_UK_B200_UNSUPPORTED: return "UNSUPPORTED";
+    case IREE_UK_B200_CUDA_ERROR: return "CUDA_ERROR";
+    case IREE_UK_B200_WORKSPACE_TOO_SMALL: return "WORKSPACE_TOO_SMALL";
+    case IREE_UK_B200_DEVICE_TIMEOUT: return "DEVICE_TIMEOUT";
+    default: return "UNKNOWN";
+  }
+}
+
+const char* iree_uk_b200_version(void) { return "iree_uk_b200 0.1 sm_100a"; }
+
+int iree_uk_b200_mmt4d(const iree_uk_mmt4d_params_t* params, void* cu_stream) {
+  return run_mmt4d(params, nullptr, 0, false, cu_stream);
+}
+
+size_t iree_uk_b200_mmt4d_workspace_size(const iree_uk_mmt4d_params_t* params) {
+  Mmt4dPath path;
+  if (select_mmt4d(params, true, &path) || path != Mmt4dPath::TcRetile) {
+    // Alignment of the buffers may differ between this query and the call; size by shape.
+    if (!params || validate_mmt4d(params)) return 0;
+  }
+  return mmt4d_tc_workspace_size(params);
+}
+
+int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* params, void* workspace,
+                          size_t workspace_bytes, void* cu_stream) {
+  const bool have_ws = workspace != nullptr && workspace_bytes > 0 &&
+                       workspace_bytes >= mmt4d_tc_workspace_size(params);
+  return run_mmt4d(params, workspace, workspace_bytes, have_ws, cu_stream);
+}
+
+int iree_uk_b200_mmt4d_flat(const void* lhs_buffer, iree_uk_index_t lhs_offset,
+                            iree_uk_index_t lhs_stride0, const void* rhs_buffer,
+                            iree_uk_index_t rhs_offset, iree_uk_index_t rhs_stride0,
+                            void* out_buffer, iree_uk_index_t out_offset,
+                            iree_uk_index_t out_stride0, iree_uk_index_t M, iree_uk_index_t N,
+                            iree_uk_index_t K, int32_t M0, int32_t N0, int32_t K0, uint32_t flags,
+                            const uint64_t* cpu_data, void* workspace, size_t workspace_bytes,
+                            void* cu_stream) {
+  iree_uk_mmt4d_params_t p;
+  p.lhs_buffer = lhs_buffer; p.lhs_offset = lhs_offset; p.lhs_stride0 = lhs_stride0;
+  p.rhs_buffer = rhs_buffer; p.rhs_offset = rhs_offset; p.rhs_stride0 = rhs_stride0;
+  p.out_buffer = out_buffer; p.out_offset = out_offset; p.out_stride0 = out_stride0;
+  p.M = M; p.N = N; p.K = K; p.M0 = M0; p.N0 = N0; p.K0 = K0;
+  p.flags = flags; p.cpu_data = cpu_data;
+  return iree_uk_b200_mmt4d_ws(&p, workspace, workspace_bytes, cu_stream);
+}
+
+uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t flags) {
+  const uint32_t type = flags & IREE_UK_FLAG_MMT4D_TYPE_MASK;
+  const bool tc_type = type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 ||
+                       type == IREE_UK_FLAG_MMT4D_TYPE_F16F16F32 ||
+                       type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32;
+  const int es = type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 ? 1 : 2;
+  const int g = K0 * es;
+  if (tc_type && M0 == 16 && N0 == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16))
+    return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
+  return 0;
+}
+
+int iree_uk_b200_mmt4d_path(const iree_uk_mmt4d_params_t* params, int with_workspace) {
+  Mmt4dPath path;
+  const int rc = select_mmt4d(params, with_workspace != 0, &path);
+  if (rc) return -rc;
+  return path_code(path);
+}
+
+int iree_uk_b200_mmt4d_shard_params(const iree_uk_mmt4d_params_t* full, int rank, int world,
+                                    int rhs_is_local, int out_is_local,
+                                    iree_uk_mmt4d_params_t* shard, iree_uk_index_t* n_begin) {
+  if (!full || !shard || world < 1 || rank < 0 || rank >= world) return IREE_UK_B200_INVALID_ARGUMENT;
+  const int rc = validate_mmt4d(full);
+  if (rc) return rc;
+  const int64_t base = full->N / world, rem = full->N % world;
+  const int64_t begin = rank * base + (rank < rem ? rank : rem);
+  const int64_t count = base + (rank < rem ? 1 : 0);
+  *shard = *full;
+  shard->N = count;
+  if (!rhs_is_local) shard->rhs_offset = full->rhs_offset + begin * full->rhs_stride0;
+  if (out_is_local) {
+    shard->out_stride0 = count * int64_t(full->M0) * full->N0;
+  } else {
+    shard->out_offset = full->out_offset + begin * int64_t(full->M0) * full->N0;
+  }
+  if (n_begin) *n_begin = begin;
+  return IREE_UK_B200_OK;
+}
+
+int iree_uk_b200_interleave_slabs(const void* gathered, void* out, iree_uk_index_t M,
+                                  iree_uk_index_t N, iree_uk_index_t tile_elems, int elem_size,
+                                  int world, void* cu_stream) {
+  if (!gathered || !out || M < 0 || N < 0 || tile_elems <= 0 || elem_size <= 0)
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  return launch_interleave_slabs(gathered, out, M, N, tile_elems, elem_size, world,
+                                 static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---- pack ----
+
+static int select_pack(const iree_uk_pack_params_t* p, int* path) {
+  const int rc = validate_pack(p);
+  if (rc) return rc;
+  if (p->out_size0 == 0 || p->out_size1 == 0 || p->out_size2 == 0 || p->out_size3 == 0) {
+    *path = IREE_UK_B200_PATH_NONE;  // ukernel/pack.c:106-109
+    return 0;
+  }
+  *path = (!env_flag("IREE_UK_B200_FORCE_GENERIC") && pack_staged_eligible(p))
+              ? IREE_UK_B200_PATH_FAST_COPY
+              : IREE_UK_B200_PATH_GENERIC;
+  return 0;
+}
+
+int iree_uk_b200_pack(const iree_uk_pack_params_t* params, void* cu_stream) {
+  int path;
+  const int rc = select_pack(params, &path);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  if (path == IREE_UK_B200_PATH_NONE) return IREE_UK_B200_OK;
+  if (path == IREE_UK_B200_PATH_FAST_COPY) return launch_pack_staged(params, stream);
+  return launch_pack_generic(params, stream);
+}
+
+int iree_uk_b200_pack_path(const iree_uk_pack_params_t* params) {
+  int path;
+  const int rc = select_pack(params, &path);
+  return rc ? -rc : path;
+}
+
+int iree_uk_b200_pack_flat(const void* in_buffer, iree_uk_index_t in_offset,
+                           iree_uk_index_t in_stride0, iree_uk_index_t in_stride1,
+                           void* out_buffer, iree_uk_index_t out_offset,
+                           iree_uk_index_t out_stride0, iree_uk_index_t out_stride1,
+                           iree_uk_index_t in_size0, iree_uk_index_t in_size1,
+                           iree_uk_index_t out_size0, iree_uk_index_t out_size1,
+                           iree_uk_index_t out_size2, iree_uk_index_t out_size3,
+                           uint64_t padding_value, uint32_t flags, const uint64_t* cpu_data,
+                           void* cu_stream) {
+  iree_uk_pack_params_t p;
+  p.in_buffer = in_buffer; p.in_offset = in_offset; p.in_stride0 = in_stride0;
+  p.in_stride1 = in_stride1; p.out_buffer = out_buffer; p.out_offset = out_offset;
+  p.out_stride0 = out_stride0; p.out_stride1 = out_stride1; p.in_size0 = in_size0;
+  p.in_size1 = in_size1; p.out_size0 = out_size0; p.out_size1 = out_size1;
+  p.out_size2 = out_size2; p.out_size3 = out_size3; p.padding_value = padding_value;
+  p.flags = flags; p.cpu_data = cpu_data;
+  return iree_uk_b200_pack(&p, cu_stream);
+}
+
+// ---- unpack ----
+
+static int select_unpack(const iree_uk_unpack_params_t* p, int* path) {
+  const int rc = validate_unpack(p);
+  if (rc) return rc;
+  if (p->out_size0 == 0 || p->out_size1 == 0 || p->in_size0 == 0 || p->in_size1 == 0 ||
+      p->in_size2 == 0 || p->in_size3 == 0) {
+    *path = IREE_UK_B200_PATH_NONE;  // ukernel/unpack.c:84-86
+    return 0;
+  }
+  *path = (!env_flag("IREE_UK_B200_FORCE_GENERIC") && unpack_staged_eligible(p))
+              ? IREE_UK_B200_PATH_FAST_COPY
+              : IREE_UK_B200_PATH_GENERIC;
+  return 0;
+}
+
+int iree_uk_b200_unpack(const iree_uk_unpack_params_t* params, void* cu_stream) {
+  int path;
+  const int rc = select_unpack(params, &path);
+  if (rc) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  if (path == IREE_UK_B200_PATH_NONE) return IREE_UK_B200_OK;
+  if (path == IREE_UK_B200_PATH_FAST_COPY) return launch_unpack_staged(params, stream);
+  return launch_unpack_generic(params, stream);
+}
+
+int iree_uk_b200_unpack_path(const iree_uk_unpack_params_t* params) {
+  int path;
+  const int rc = select_unpack(params, &path);
+  return rc ? -rc : path;
+}
+
+int iree_uk_b200_unpack_flat(const void* in_buffer, iree_uk_index_t in_offset,
+                             iree_uk_index_t in_stride0, iree_uk_index_t in_stride1,
+                             void* out_buffer, iree_uk_index_t out_offset,
+                             iree_uk_index_t out_stride0, iree_uk_index_t out_stride1,
+                             iree_uk_index_t in_size0, iree_uk_index_t in_size1,
+                             iree_uk_index_t in_size2, iree_uk_index_t in_size3,
+                             iree_uk_index_t out_size0, iree_uk_index_t out_size1, uint32_t flags,
+                             const uint64_t* cpu_data, void* cu_stream) {
+  iree_uk_unpack_params_t p;
+  p.in_buffer = in_buffer; p.in_offset = in_offset; p.in_stride0 = in_stride0;
+  p.in_stride1 = in_stride1; p.out_buffer = out_buffer; p.out_offset = out_offset;
+  p.out_stride0 = out_stride0; p.out_stride1 = out_stride1; p.in_size0 = in_size0;
+  p.in_size1 = in_size1; p.in_size2 = in_size2; p.in_size3 = in_size3;
+  p.out_size0 = out_size0; p.out_size1 = out_size1; p.flags = flags; p.cpu_data = cpu_data;
+  return iree_uk_b200_unpack(&p, cu_stream);
+}
+
+// ---- query_tile_sizes ----
+
+int iree_uk_b200_query_tile_sizes_2d(const iree_uk_query_tile_sizes_2d_params_t* params,
+                                     iree_uk_query_tile_sizes_2d_out_params_t* out_params) {
+  if (!params || !out_params) return IREE_UK_B200_INVALID_ARGUMENT;
+  int64_t m = 16, n = 16, k = 1;
+  switch (params->flags & IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MASK) {
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F32F32F32: k = 1; break;
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_I8I8I32: k = 2; break;
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F16F16F32: k = 1; break;
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F16F16F16: k = 1; break;
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16F32: k = 2; break;
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16BF16: k = 2; break;
+    default: return IREE_UK_B200_INVALID_ARGUMENT;  // query_tile_sizes.c:20-21
+  }
+  switch (params->flags & IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_MASK) {
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_LHS:
+      out_params->tile_size0 = m; out_params->tile_size1 = k; break;
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_RHS:
+      out_params->tile_size0 = n; out_params->tile_size1 = k; break;
+    case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_RESULT:
+      out_params->tile_size0 = m; out_params->tile_size1 = n; break;
+    default: return IREE_UK_B200_INVALID_ARGUMENT;  // query_tile_sizes.c:22-25
+  }
+  return IREE_UK_B200_OK;
+}
+
+// ---- device status ----
+
+int iree_uk_b200_device_status(void* cu_stream, uint32_t* detail) {
+  uint32_t* word = device_status_word();
+  if (!word) return IREE_UK_B200_CUDA_ERROR;
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  uint32_t host = 0;
+  if (cudaMemcpyAsync(&host, word, sizeof host, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return IREE_UK_B200_CUDA_ERROR;
+  if (detail) *detail = host;
+  if (host) {
+    if (cudaMemsetAsync(word, 0, sizeof host, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess)
+      return IREE_UK_B200_CUDA_ERROR;
+    return IREE_UK_B200_DEVICE_TIMEOUT;
+  }
+  return IREE_UK_B200_OK;
+}
+
+// Internal, not declared in the public header: runs the tensor-core kernel with an explicit
+// operand-staging variant. Used to validate experimental staging layouts on hardware.
+IREE_UK_B200_EXPORT int iree_uk_b200_debug_mmt4d_variant(const iree_uk_mmt4d_params_t* params,
+                                                         void* workspace, size_t workspace_bytes,
+                                                         int variant, void* cu_stream) {
+  const int rc = validate_mmt4d(params);
+  if (rc) return rc;
+  if (!mmt4d_tc_eligible(params)) return IREE_UK_B200_UNSUPPORTED;
+  return launch_mmt4d_tc(params, workspace, workspace_bytes, variant,
+                         static_cast<cudaStream_t>(cu_stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,82 @@
+// Internal declarations shared by the translation units of libiree_uk_b200.so.
+#ifndef IREE_UK_B200_CSRC_UK_COMMON_H_
+#define IREE_UK_B200_CSRC_UK_COMMON_H_
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "../../include/iree_uk_b200.h"
+
+namespace uk {
+
+// Element types of the path, by width and interpretation.
+enum class Elem : int { F32, S32, F16, BF16, S16, S8, U4, S4 };
+
+inline int elem_bits(Elem e) {
+  switch (e) {
+    case Elem::F32: case Elem::S32: return 32;
+    case Elem::F16: case Elem::BF16: case Elem::S16: return 16;
+    case Elem::S8: return 8;
+    default: return 4;
+  }
+}
+
+// (lhs, rhs, out) of a mmt4d type id; false when the id is not a mmt4d type.
+// Mirrors iree_uk_mmt4d_type (ukernel/mmt4d_internal.h:63-97).
+struct Mmt4dTypes {
+  Elem lhs, rhs, out;
+};
+bool mmt4d_types(uint32_t flags, Mmt4dTypes* t);
+
+// Bytes per element of a pack / unpack type id, 0 when invalid
+// (ukernel/pack_internal.h:43-59, unpack_internal.h:39-53).
+int pack_elem_size(uint32_t flags);
+int unpack_elem_size(uint32_t flags);
+
+// Host-side restatements of the reference's *_validate functions. Return IREE_UK_B200_OK
+// or IREE_UK_B200_INVALID_ARGUMENT.
+int validate_mmt4d(const iree_uk_mmt4d_params_t* p);    // ukernel/mmt4d.c:12-48
+int validate_pack(const iree_uk_pack_params_t* p);      // ukernel/pack.c:51-104
+int validate_unpack(const iree_uk_unpack_params_t* p);  // ukernel/unpack.c:31-82
+
+// ---- launchers (each enqueues on `stream`, returns a status) -------------------------
+
+int launch_mmt4d_generic(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
+int launch_mmt4d_zero_fill(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
+int launch_mmt4d_gemv_s16u4(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
+bool mmt4d_gemv_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
+
+// Tensor-core path. `variant` selects the operand staging layout (see uk_mmt4d_tc.cu).
+bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p);
+size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
+int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
+                    cudaStream_t stream);
+constexpr int kTcVariantDefault = 0;
+
+int launch_pack_generic(const iree_uk_pack_params_t* p, cudaStream_t stream);
+int launch_unpack_generic(const iree_uk_unpack_params_t* p, cudaStream_t stream);
+// Shared-memory staged relayouts; return IREE_UK_B200_UNSUPPORTED when the shape does not
+// fit their staging buffer (the caller then uses the generic kernel).
+int launch_pack_staged(const iree_uk_pack_params_t* p, cudaStream_t stream);
+int launch_unpack_staged(const iree_uk_unpack_params_t* p, cudaStream_t stream);
+bool pack_staged_eligible(const iree_uk_pack_params_t* p);
+bool unpack_staged_eligible(const iree_uk_unpack_params_t* p);
+
+int launch_interleave_slabs(const void* gathered, void* out, int64_t M, int64_t N,
+                            int64_t tile_elems, int elem_size, int world, cudaStream_t stream);
+
+// Per-device status word written by kernels whose bounded waits ran out.
+// Returns a device pointer valid on the current device, or nullptr on CUDA failure.
+uint32_t* device_status_word();
+
+inline int cuda_status(cudaError_t e) {
+  return e == cudaSuccess ? IREE_UK_B200_OK : IREE_UK_B200_CUDA_ERROR;
+}
+
+// True when the environment variable is set to a non-empty value other than "0".
+bool env_flag(const char* name);
+
+}  // namespace uk
+
+#endif  // IREE_UK_B200_CSRC_UK_COMMON_H_

@@ -1,0 +1,256 @@
+// mmt4d on CUDA cores: the kernel that serves every tile shape, stride and offset the
+// reference accepts (ukernel/mmt4d.c:26-46), plus the K==0 zero fill and the s16u4s32
+// weight-streaming GEMV. The tensor-core kernels of uk_mmt4d_tc.cu take over for the tile
+// shapes they specialise; this file is what the rest falls to — never a CPU path.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "uk_common.h"
+
+namespace uk {
+namespace {
+
+struct GenericArgs {
+  const char* lhs;  // first addressed byte (offset applied)
+  const char* rhs;
+  char* out;
+  int64_t lhs_stride_b, rhs_stride_b;  // bytes between tile rows
+  int64_t out_stride0;                 // elements
+  int64_t M, N, K;
+  int32_t M0, N0, K0;
+  int32_t accumulate;
+};
+
+template <uint32_t TYPE> struct Traits;
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_F32F32F32> {
+  using Acc = float; static constexpr int LB = 32, RB = 32;
+  static __device__ float lhs(const char* p, int64_t e) { return reinterpret_cast<const float*>(p)[e]; }
+  static __device__ float rhs(const char* p, int64_t e) { return reinterpret_cast<const float*>(p)[e]; }
+};
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_F16F16F32> {
+  using Acc = float; static constexpr int LB = 16, RB = 16;
+  static __device__ float lhs(const char* p, int64_t e) { return __half2float(reinterpret_cast<const __half*>(p)[e]); }
+  static __device__ float rhs(const char* p, int64_t e) { return __half2float(reinterpret_cast<const __half*>(p)[e]); }
+};
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32> {
+  using Acc = float; static constexpr int LB = 16, RB = 16;
+  static __device__ float lhs(const char* p, int64_t e) { return __uint_as_float(uint32_t(reinterpret_cast<const uint16_t*>(p)[e]) << 16); }
+  static __device__ float rhs(const char* p, int64_t e) { return lhs(p, e); }
+};
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S8S8S32> {
+  using Acc = uint32_t; static constexpr int LB = 8, RB = 8;
+  static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
+  static __device__ int32_t rhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
+};
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S16S16S32> {
+  using Acc = uint32_t; static constexpr int LB = 16, RB = 16;
+  static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
+  static __device__ int32_t rhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
+};
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S16S8S32> {
+  using Acc = uint32_t; static constexpr int LB = 16, RB = 8;
+  static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
+  static __device__ int32_t rhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
+};
+// 4-bit right-hand sides: element e is in byte e/2, low nibble when e is even
+// (ukernel/mmt4d_tile_generic.c:35-44 signed, :130-136 unsigned).
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S16U4S32> {
+  using Acc = uint32_t; static constexpr int LB = 16, RB = 4;
+  static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
+  static __device__ int32_t rhs(const char* p, int64_t e) {
+    const uint32_t b = reinterpret_cast<const uint8_t*>(p)[e >> 1];
+    return int32_t((e & 1) ? (b >> 4) : (b & 0xF));
+  }
+};
+template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S8S4S32> {
+  using Acc = uint32_t; static constexpr int LB = 8, RB = 4;
+  static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
+  static __device__ int32_t rhs(const char* p, int64_t e) {
+    const uint32_t b = reinterpret_cast<const uint8_t*>(p)[e >> 1];
+    int32_t v = int32_t((e & 1) ? (b >> 4) : (b & 0xF));
+    return (v & 8) ? v - 16 : v;
+  }
+};
+
+__device__ __forceinline__ float mac(float acc, float a, float b) { return fmaf(a, b, acc); }
+__device__ __forceinline__ uint32_t mac(uint32_t acc, int32_t a, int32_t b) {
+  return acc + uint32_t(a * b);  // wraps modulo 2^32 like the reference's int32 sums
+}
+
+// One thread per output element; the K loop is the reference's: k-major, then k0
+// (ukernel/mmt4d_tile_generic.c:65-75).
+template <uint32_t TYPE>
+__global__ void __launch_bounds__(256) mmt4d_generic_kernel(GenericArgs a) {
+  using T = Traits<TYPE>;
+  using Acc = typename T::Acc;
+  const int64_t tile_elems = int64_t(a.M0) * a.N0;
+  const int64_t total = a.M * a.N * tile_elems;
+  const int64_t lhs_k_step = int64_t(a.M0) * a.K0, rhs_k_step = int64_t(a.N0) * a.K0;
+  for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total;
+       idx += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t tile = idx / tile_elems;
+    const int32_t e = int32_t(idx - tile * tile_elems);
+    const int64_t i = tile / a.N, j = tile - i * a.N;
+    const int32_t i0 = e / a.N0, j0 = e - i0 * a.N0;
+    const char* lp = a.lhs + i * a.lhs_stride_b;
+    const char* rp = a.rhs + j * a.rhs_stride_b;
+    Acc* op = reinterpret_cast<Acc*>(a.out) + i * a.out_stride0 + j * tile_elems + e;
+    Acc acc = a.accumulate ? *op : Acc(0);
+    int64_t le = int64_t(i0) * a.K0, re = int64_t(j0) * a.K0;
+    for (int64_t k = 0; k < a.K; ++k) {
+      for (int32_t k0 = 0; k0 < a.K0; ++k0) acc = mac(acc, T::lhs(lp, le + k0), T::rhs(rp, re + k0));
+      le += lhs_k_step;
+      re += rhs_k_step;
+    }
+    *op = acc;
+  }
+}
+
+__global__ void __launch_bounds__(256) mmt4d_zero_fill_kernel(char* out, int64_t out_stride0,
+                                                              int64_t M, int64_t row_elems) {
+  // K == 0 without ACCUMULATE: every addressed out tile becomes zero, stride gaps are left
+  // alone (ukernel/mmt4d.c:105-113 falls through to a tile function with an empty K loop).
+  const int64_t total = M * row_elems;
+  for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total;
+       idx += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t i = idx / row_elems, c = idx - i * row_elems;
+    reinterpret_cast<uint32_t*>(out)[i * out_stride0 + c] = 0u;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// s16u4s32, M0 = 1, N0 = 32, K0 = 8: weight-streaming GEMV.
+// RHS tile (n1, k1) is 128 contiguous bytes [n0 = 32][4 bytes = 8 nibbles, low nibble =
+// even k0]; the whole RHS row n1 is K*128 contiguous bytes. One block per (m, n1) pair
+// keeps 32 int32 sums; each lane streams 16 bytes (4 n0 rows of one k1) per step, four k1
+// per warp step, and the eight warps interleave along K. HBM-bound by construction: every
+// weight byte is read once with 16-byte loads.
+// ---------------------------------------------------------------------------------------
+constexpr int kGemvWarps = 8;
+
+__global__ void __launch_bounds__(kGemvWarps * 32) mmt4d_gemv_s16u4_kernel(GenericArgs a) {
+  __shared__ int32_t partial[kGemvWarps][32];
+  const int64_t m = blockIdx.x / a.N, n1 = blockIdx.x - m * a.N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kq = lane >> 3;      // which of the 4 k1 of this warp step
+  const int ng = lane & 7;       // which group of 4 n0 rows
+  const uint4* rhs = reinterpret_cast<const uint4*>(a.rhs + n1 * a.rhs_stride_b);
+  const uint4* lhs = reinterpret_cast<const uint4*>(a.lhs + m * a.lhs_stride_b);
+  int32_t acc[4] = {0, 0, 0, 0};
+  for (int64_t k = int64_t(warp) * 4 + kq; k < a.K; k += kGemvWarps * 4) {
+    const uint4 w = __ldg(rhs + k * 8 + ng);  // 4 n0 rows x 8 nibbles
+    const uint4 x = __ldg(lhs + k);           // 8 s16 of this k1
+    const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      int32_t s = 0;
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {  // byte h holds k0 = 2h (low nibble) and 2h+1 (high)
+        const uint32_t byte = (ws[r] >> (8 * h)) & 0xFFu;
+        const int32_t x0 = int16_t(xs[h] & 0xFFFFu), x1 = int16_t(xs[h] >> 16);
+        s += x0 * int32_t(byte & 0xFu) + x1 * int32_t(byte >> 4);
+      }
+      acc[r] += s;
+    }
+  }
+  // lanes with the same ng hold partial sums of the same 4 outputs
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 8);
+    acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 16);
+  }
+  if (lane < 8) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) partial[warp][ng * 4 + r] = acc[r];
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    int32_t s = 0;
+#pragma unroll
+    for (int w = 0; w < kGemvWarps; ++w) s += partial[w][threadIdx.x];
+    int32_t* op = reinterpret_cast<int32_t*>(a.out) + m * a.out_stride0 + n1 * 32 + threadIdx.x;
+    *op = a.accumulate ? int32_t(uint32_t(*op) + uint32_t(s)) : s;
+  }
+}
+
+bool fill_args(const iree_uk_mmt4d_params_t* p, GenericArgs* a) {
+  Mmt4dTypes t;
+  if (!mmt4d_types(p->flags, &t)) return false;
+  const int lb = elem_bits(t.lhs), rb = elem_bits(t.rhs), ob = elem_bits(t.out);
+  a->lhs = static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * lb / 8;
+  a->rhs = static_cast<const char*>(p->rhs_buffer) + p->rhs_offset * rb / 8;
+  a->out = static_cast<char*>(p->out_buffer) + p->out_offset * (ob / 8);
+  a->lhs_stride_b = p->lhs_stride0 * lb / 8;
+  a->rhs_stride_b = p->rhs_stride0 * rb / 8;
+  a->out_stride0 = p->out_stride0;
+  a->M = p->M; a->N = p->N; a->K = p->K;
+  a->M0 = p->M0; a->N0 = p->N0; a->K0 = p->K0;
+  a->accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
+  return true;
+}
+
+template <uint32_t TYPE>
+int launch_generic_typed(const GenericArgs& a, cudaStream_t stream) {
+  const int64_t total = a.M * a.N * a.M0 * a.N0;
+  if (total <= 0) return IREE_UK_B200_OK;
+  const int64_t blocks = std::min<int64_t>((total + 255) / 256, 148 * 64);
+  mmt4d_generic_kernel<TYPE><<<int(blocks), 256, 0, stream>>>(a);
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace
+
+int launch_mmt4d_generic(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
+  GenericArgs a;
+  if (!fill_args(p, &a)) return IREE_UK_B200_INVALID_ARGUMENT;
+  switch (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) {
+    case IREE_UK_FLAG_MMT4D_TYPE_F32F32F32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_F32F32F32>(a, stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S8S8S32>(a, stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_F16F16F32>(a, stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32>(a, stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_S16S16S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S16S16S32>(a, stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_S16U4S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S16U4S32>(a, stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_S16S8S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S16S8S32>(a, stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_S8S4S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S8S4S32>(a, stream);
+    default: return IREE_UK_B200_UNSUPPORTED;  // 16-bit-output triples: not served yet
+  }
+}
+
+int launch_mmt4d_zero_fill(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
+  GenericArgs a;
+  if (!fill_args(p, &a)) return IREE_UK_B200_INVALID_ARGUMENT;
+  Mmt4dTypes t;
+  mmt4d_types(p->flags, &t);
+  if (elem_bits(t.out) != 32) return IREE_UK_B200_UNSUPPORTED;
+  const int64_t row_elems = a.N * a.M0 * a.N0;
+  const int64_t total = a.M * row_elems;
+  if (total <= 0) return IREE_UK_B200_OK;
+  const int64_t blocks = std::min<int64_t>((total + 255) / 256, 148 * 16);
+  mmt4d_zero_fill_kernel<<<int(blocks), 256, 0, stream>>>(a.out, a.out_stride0, a.M, row_elems);
+  return cuda_status(cudaGetLastError());
+}
+
+bool mmt4d_gemv_s16u4_eligible(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) != IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) return false;
+  if (p->M0 != 1 || p->N0 != 32 || p->K0 != 8 || p->K < 1) return false;
+  if (p->M * p->N > 0x7FFFFFFF) return false;
+  // 16-byte loads: LHS tile rows are K*16 bytes, RHS tile rows K*128 bytes.
+  const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * 2);
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset / 2);
+  return (lhs % 16 == 0) && (rhs % 16 == 0) && ((p->lhs_stride0 * 2) % 16 == 0) &&
+         ((p->rhs_stride0 / 2) % 16 == 0);
+}
+
+int launch_mmt4d_gemv_s16u4(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
+  GenericArgs a;
+  if (!fill_args(p, &a)) return IREE_UK_B200_INVALID_ARGUMENT;
+  const int64_t blocks = a.M * a.N;
+  if (blocks <= 0) return IREE_UK_B200_OK;
+  mmt4d_gemv_s16u4_kernel<<<int(blocks), kGemvWarps * 32, 0, stream>>>(a);
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace uk

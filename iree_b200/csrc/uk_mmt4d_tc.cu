@@ -1,0 +1,728 @@
+// mmt4d on the 5th-generation tensor cores (sm_100a): TMA -> shared memory -> tcgen05.mma
+// -> TMEM -> tcgen05.ld -> [M1][N1][16][16] output tiles.
+//
+// One persistent, warp-specialised kernel serves s8s8s32 (kind::i8), f16f16f32 and
+// bf16bf16f32 (kind::f16) with M0 = N0 = 16:
+//
+//   warp 0      TMA producer: one elected lane issues cp.async.bulk.tensor loads (never
+//               with cluster multicast) into a ring of shared-memory stages
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M = 128, N = BN <= 256)
+//               into one of two TMEM accumulator buffers; also owns TMEM alloc / dealloc
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 16 columns -> one 64-byte row of one
+//               16x16 output tile per thread (+ the old tile when ACCUMULATE) -> st.global
+//
+// The CTA tile is 128 rows (8 LHS tile rows) x BN columns (BN/16 RHS tile rows). Tiles are
+// walked in a grouped order so that the CTAs of one wave share LHS / RHS panels in L2.
+//
+// How the operands reach shared memory is described by runtime parameters (tensor maps,
+// box coordinates, shared-memory descriptor fields), not by the kernel body. "Variants":
+//   0  K-major, SWIZZLE_128B: both operands are first re-tiled by retile_kernel from the
+//      mmt4d panel layout [tile][K1][16][K0] into row-major [row][K] scratch; this is the
+//      canonical tcgen05 layout and works for every K0
+//   1..4  MN-major, read directly from a K0 = 1, 16-bit mmt4d operand ([tile][K1][16] is
+//      already "16 contiguous M/N elements per k"); 1/2 use 128-byte swizzle with four
+//      tile rows side by side, 3/4 use 32-byte swizzle; even numbers swap the roles of the
+//      descriptor's two byte offsets. Experimental until validated on hardware.
+//
+// Every wait on an mbarrier is bounded (clock64 deadline). A wait that runs out records a
+// code in the per-device status word, raises a CTA-wide abort flag, and all roles leave
+// their loops; the producer then waits (bounded) for its own copies in flight, TMEM is
+// freed and the kernel returns.
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+
+#include "uk_common.h"
+
+namespace uk {
+namespace {
+
+constexpr int kMaxStages = 8;
+constexpr int kThreads = 192;
+constexpr long long kWaitCycles = 1ll << 31;  // ~1.1 s at 1.9 GHz
+constexpr int BM = 128;
+
+struct OperandStage {
+  int32_t nbox;       // TMA boxes per stage
+  int32_t box_bytes;  // shared-memory bytes per box
+  int32_t kstep[3];   // coordinate = kb*kstep + tile*tstep + box*bstep
+  int32_t tstep[3];
+  int32_t bstep[3];
+};
+
+struct TcParams {
+  CUtensorMap map_a;
+  CUtensorMap map_b;
+  OperandStage sa, sb;
+  uint32_t desc_hi_a, desc_hi_b;    // bits 32..63 of the shared-memory descriptors
+  uint32_t desc_lbo_a, desc_lbo_b;  // leading byte offset >> 4
+  uint32_t kadv_a, kadv_b;          // start-address advance per MMA along K, in 16-byte units
+  uint32_t idesc;
+  int32_t mma_per_stage;
+  int32_t stage_bytes_a, stage_bytes_b;
+  int32_t num_stages;
+  int32_t num_kb;
+  int32_t m_tiles, n_tiles, group_m;
+  int32_t bn;  // accumulator columns per CTA tile
+  char* out;
+  int64_t out_stride0;  // elements
+  int64_t M1, N1;
+  int32_t accumulate;
+  int32_t out_is_int;
+  uint32_t* status;
+};
+
+// ---------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. False when the deadline passed or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long deadline = clock64() + kWaitCycles;
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag || clock64() > deadline) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+template <bool IS_INT>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  if (IS_INT) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// mbarrier arrives once all tcgen05.mma issued so far by this thread have completed.
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr_units, uint32_t lbo, uint32_t hi) {
+  return (uint64_t(hi) << 32) | uint64_t((addr_units & 0x3FFFu) | (lbo << 16));
+}
+
+__device__ __forceinline__ void tile_coords(const TcParams& P, int tile, int* mt, int* nt) {
+  const int per_group = P.group_m * P.n_tiles;
+  const int g = tile / per_group, r = tile - g * per_group;
+  const int gm = min(P.group_m, P.m_tiles - g * P.group_m);
+  *nt = r / gm;
+  *mt = g * P.group_m + (r - *nt * gm);
+}
+
+enum : uint32_t {
+  kStatusProducerTimeout = 1u << 0,
+  kStatusMmaTimeout = 1u << 1,
+  kStatusEpilogueTimeout = 1u << 2,
+  kStatusDrainTimeout = 1u << 3,
+};
+
+// ---------------------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------------------
+template <bool IS_INT>
+__global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_constant__ TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t stage_base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzle atoms: 1 KB
+  const uint32_t stage_bytes = uint32_t(P.stage_bytes_a + P.stage_bytes_b);
+  const int S = P.num_stages;
+  const int num_tiles = P.m_tiles * P.n_tiles;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 4);  // one arrive per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mt, nt;
+        tile_coords(P, tile, &mt, &nt);
+        for (int kb = 0; kb < P.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
+            atomicOr(P.status, kStatusProducerTimeout);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&full_bar[stage]);
+          mbar_expect_tx(bar, stage_bytes);
+          const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
+          const uint32_t sb = sa + uint32_t(P.stage_bytes_a);
+          for (int b = 0; b < P.sa.nbox; ++b)
+            tma_load_3d(sa + uint32_t(b * P.sa.box_bytes), &P.map_a, bar,
+                        kb * P.sa.kstep[0] + mt * P.sa.tstep[0] + b * P.sa.bstep[0],
+                        kb * P.sa.kstep[1] + mt * P.sa.tstep[1] + b * P.sa.bstep[1],
+                        kb * P.sa.kstep[2] + mt * P.sa.tstep[2] + b * P.sa.bstep[2]);
+          for (int b = 0; b < P.sb.nbox; ++b)
+            tma_load_3d(sb + uint32_t(b * P.sb.box_bytes), &P.map_b, bar,
+                        kb * P.sb.kstep[0] + nt * P.sb.tstep[0] + b * P.sb.bstep[0],
+                        kb * P.sb.kstep[1] + nt * P.sb.tstep[1] + b * P.sb.bstep[1],
+                        kb * P.sb.kstep[2] + nt * P.sb.tstep[2] + b * P.sb.bstep[2]);
+          ++issued;
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok || *abortp) {
+        // Aborting: let this CTA's own copies land before its shared memory is released.
+        const long long n = issued < S ? issued : S;
+        for (long long i = 0; i < n; ++i) {
+          const long long idx = issued - 1 - i;
+          const int s = int(idx % S);
+          const uint32_t par = uint32_t((idx / S) & 1);
+          const long long deadline = clock64() + kWaitCycles;
+          while (!mbar_try_wait(smem_u32(&full_bar[s]), par)) {
+            if (clock64() > deadline) { atomicOr(P.status, kStatusDrainTimeout); break; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
+          atomicOr(P.status, kStatusMmaTimeout);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn);
+        for (int kb = 0; kb < P.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abortp)) {
+            atomicOr(P.status, kStatusMmaTimeout);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
+          const uint32_t sb = sa + uint32_t(P.stage_bytes_a);
+          const uint32_t a_units = sa >> 4, b_units = sb >> 4;
+          for (int j = 0; j < P.mma_per_stage; ++j) {
+            const uint64_t da = make_desc(a_units + uint32_t(j) * P.kadv_a, P.desc_lbo_a, P.desc_hi_a);
+            const uint64_t db = make_desc(b_units + uint32_t(j) * P.kadv_b, P.desc_lbo_b, P.desc_hi_b);
+            tc_mma<IS_INT>(d_tmem, da, db, P.idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs finish
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&tmem_full_bar[buf]));  // accumulator complete
+        if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const int m_local = q * 32 + lane;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    const int chunks = P.bn >> 4;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int mt, nt;
+      tile_coords(P, tile, &mt, &nt);
+      // Warp-uniform outcome: tcgen05.ld below needs all 32 lanes.
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp))) {
+        if (lane == 0) atomicOr(P.status, kStatusEpilogueTimeout);
+        abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int64_t m1 = int64_t(mt) * (BM / 16) + (m_local >> 4);
+      const int m0 = m_local & 15;
+      const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
+      for (int c = 0; c < chunks; ++c) {
+        uint32_t r[16];
+        tmem_ld16(taddr0 + uint32_t(c * 16), r);
+        tmem_ld_wait();
+        const int64_t n1 = int64_t(nt) * chunks + c;
+        if (m1 < P.M1 && n1 < P.N1) {
+          uint4* dst = reinterpret_cast<uint4*>(
+              P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4);
+          if (P.accumulate) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const uint4 old = dst[v];
+              if (P.out_is_int) {
+                r[4 * v + 0] += old.x; r[4 * v + 1] += old.y;
+                r[4 * v + 2] += old.z; r[4 * v + 3] += old.w;
+              } else {
+                r[4 * v + 0] = __float_as_uint(__uint_as_float(r[4 * v + 0]) + __uint_as_float(old.x));
+                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + __uint_as_float(old.y));
+                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + __uint_as_float(old.z));
+                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + __uint_as_float(old.w));
+              }
+            }
+          }
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            dst[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+      if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// re-tile: mmt4d panels [tile][K1][16][K0] -> row-major [tile*16 + r][K1*K0] scratch
+// ---------------------------------------------------------------------------------------
+// G = K0 * element bytes is the granule that stays contiguous; per tile row the kernel
+// transposes a [K1][16] matrix of granules into [16][K1]. A block moves 256/G k1 steps of
+// one tile row (4 KB) through shared memory: contiguous 16-byte loads, 16-byte stores of
+// 256-byte row segments. The shared-memory pitch per k1 is 16*G + 4 bytes so that walking
+// k1 at a fixed row is bank-conflict free.
+template <int G>
+__global__ void __launch_bounds__(256) retile_kernel(const char* __restrict__ src,
+                                                     int64_t src_stride_b, char* __restrict__ dst,
+                                                     int64_t dst_pitch_b, int64_t K1, int kchunks) {
+  constexpr int KC = 256 / G;             // k1 steps per block
+  constexpr int PITCH = 16 * G + 4;       // bytes per k1 in shared memory
+  constexpr int GV = 16 / G;              // granules per 16-byte vector
+  __shared__ __align__(16) unsigned char sm[KC * PITCH];
+  const int64_t tile = blockIdx.x / kchunks;
+  const int chunk = int(blockIdx.x - tile * kchunks);
+  const int64_t k_base = int64_t(chunk) * KC;
+  const int kn = int(min(int64_t(KC), K1 - k_base));
+  const char* sp = src + tile * src_stride_b + k_base * (16 * G);
+  // load: kn * 16 granules contiguous = kn * G vectors of 16 bytes
+  const int nvec = kn * G;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 x = __ldg(reinterpret_cast<const uint4*>(sp) + v);
+    const int byte = v * 16;
+    const int k = byte / (16 * G), within = byte - k * (16 * G);
+    uint32_t* d = reinterpret_cast<uint32_t*>(sm + k * PITCH + within);
+    d[0] = x.x; d[1] = x.y; d[2] = x.z; d[3] = x.w;
+  }
+  __syncthreads();
+  // store: 16 rows x kn granules; a thread builds 16 bytes = GV consecutive k1 of one row
+  // Lane mapping: 4 consecutive vectors of a row (64 bytes), then the next row; keeps the
+  // shared-memory reads spread over banks and the global stores in 64-byte pieces.
+  const int vec_per_row = (kn + GV - 1) / GV;
+  const int vec_per_row4 = (vec_per_row + 3) & ~3;
+  for (int v = threadIdx.x; v < 16 * vec_per_row4; v += blockDim.x) {
+    const int r = (v >> 2) & 15, kv = ((v >> 6) << 2) | (v & 3);
+    if (kv >= vec_per_row) continue;
+    const int k0 = kv * GV;
+    char* dp = dst + (tile * 16 + r) * dst_pitch_b + (k_base + k0) * G;
+    if (k0 + GV <= kn) {
+      uint32_t w[4];
+      if (G == 16) {
+        const uint32_t* s = reinterpret_cast<const uint32_t*>(sm + k0 * PITCH + r * G);
+        w[0] = s[0]; w[1] = s[1]; w[2] = s[2]; w[3] = s[3];
+      } else if (G == 8) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint32_t* s = reinterpret_cast<const uint32_t*>(sm + (k0 + j) * PITCH + r * G);
+          w[2 * j] = s[0]; w[2 * j + 1] = s[1];
+        }
+      } else if (G == 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          w[j] = *reinterpret_cast<const uint32_t*>(sm + (k0 + j) * PITCH + r * G);
+      } else if (G == 2) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t lo = *reinterpret_cast<const uint16_t*>(sm + (k0 + 2 * j) * PITCH + r * G);
+          const uint32_t hi = *reinterpret_cast<const uint16_t*>(sm + (k0 + 2 * j + 1) * PITCH + r * G);
+          w[j] = lo | (hi << 16);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t x = 0;
+#pragma unroll
+          for (int b = 0; b < 4; ++b) x |= uint32_t(sm[(k0 + 4 * j + b) * PITCH + r * G]) << (8 * b);
+          w[j] = x;
+        }
+      }
+      *reinterpret_cast<uint4*>(dp) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int k = k0; k < kn; ++k)
+        for (int b = 0; b < G; ++b) dp[(k - k0) * G + b] = char(sm[k * PITCH + r * G + b]);
+    }
+  }
+}
+
+int launch_retile(const char* src, int64_t src_stride_b, char* dst, int64_t dst_pitch_b,
+                  int64_t tiles, int64_t K1, int G, cudaStream_t stream) {
+  if (tiles <= 0 || K1 <= 0) return IREE_UK_B200_OK;
+  const int KC = 256 / G;
+  const int64_t kchunks = (K1 + KC - 1) / KC;
+  const int64_t blocks = tiles * kchunks;
+  if (blocks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
+  switch (G) {
+    case 1: retile_kernel<1><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
+    case 2: retile_kernel<2><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
+    case 4: retile_kernel<4><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
+    case 8: retile_kernel<8><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
+    case 16: retile_kernel<16><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
+    default: return IREE_UK_B200_UNSUPPORTED;
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------------
+// host side: tensor maps, descriptors, launch
+// ---------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+struct TypeInfo {
+  int es;         // operand element bytes
+  bool is_int;
+  uint32_t fmt;   // a/b format field of the instruction descriptor
+  uint32_t cfmt;  // accumulator format
+  CUtensorMapDataType tm_type;
+};
+
+bool tc_type_info(uint32_t flags, TypeInfo* ti) {
+  switch (flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) {
+    case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: *ti = {1, true, 1u, 2u, CU_TENSOR_MAP_DATA_TYPE_UINT8}; return true;
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32: *ti = {2, false, 0u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16}; return true;
+    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32: *ti = {2, false, 1u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16}; return true;
+    default: return false;
+  }
+}
+
+uint32_t make_idesc(const TypeInfo& ti, int n, bool mn_major) {
+  return (ti.cfmt << 4) | (ti.fmt << 7) | (ti.fmt << 10) | (uint32_t(mn_major) << 15) |
+         (uint32_t(mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+}
+
+// Upper word of a shared-memory matrix descriptor: stride byte offset, version 1
+// (Blackwell), swizzle mode (2 = 128 B, 4 = 64 B, 6 = 32 B, 0 = none).
+uint32_t desc_hi(uint32_t sbo_bytes, uint32_t layout) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (layout << 29);
+}
+
+int64_t round_up(int64_t v, int64_t q) { return (v + q - 1) / q * q; }
+
+int pick_bn(int64_t M1, int64_t N1) {
+  const int64_t m_tiles = (M1 + 7) / 8;
+  for (int bn : {256, 128, 64}) {
+    const int64_t n_tiles = (N1 * 16 + bn - 1) / bn;
+    if (m_tiles * n_tiles >= 148 || bn == 64) {
+      // never wider than the problem (rounded up to 16 columns)
+      const int64_t cap = round_up(N1 * 16, 16);
+      return int(std::min<int64_t>(bn, std::max<int64_t>(cap, 16)));
+    }
+  }
+  return 64;
+}
+
+bool encode_map(CUtensorMap* map, CUtensorMapDataType type, void* base, const uint64_t dims[3],
+                const uint64_t strides_b[2], const uint32_t box[3], CUtensorMapSwizzle swz) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t gd[3] = {dims[0], dims[1], dims[2]};
+  cuuint64_t gs[2] = {strides_b[0], strides_b[1]};
+  cuuint32_t bx[3] = {box[0], box[1], box[2]};
+  cuuint32_t es[3] = {1, 1, 1};
+  return fn(map, type, 3, base, gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
+  TypeInfo ti;
+  if (!tc_type_info(p->flags, &ti)) return false;
+  if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1 || p->N < 1) return false;
+  const int G = p->K0 * ti.es;
+  if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return false;
+  const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * ti.es);
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset * ti.es);
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * 4);
+  if ((lhs | rhs | out) & 15) return false;
+  if ((p->lhs_stride0 * ti.es) % 16 || (p->rhs_stride0 * ti.es) % 16 || (p->out_stride0 * 4) % 16)
+    return false;
+  if ((p->M + 7) / 8 * ((p->N + 3) / 4) > 0x3FFFFFFF) return false;
+  return true;
+}
+
+size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
+  TypeInfo ti;
+  if (!tc_type_info(p->flags, &ti)) return 0;
+  if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
+  const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
+  return size_t(round_up(p->M * 16 * pitch, 1024) + round_up(p->N * 16 * pitch, 1024));
+}
+
+int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
+                    cudaStream_t stream) {
+  TypeInfo ti;
+  if (!tc_type_info(p->flags, &ti) || !mmt4d_tc_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
+  uint32_t* status = device_status_word();
+  if (!status) return IREE_UK_B200_CUDA_ERROR;
+
+  TcParams P;
+  std::memset(&P, 0, sizeof P);
+  const int bn = pick_bn(p->M, p->N);
+  const int64_t kelems = p->K * p->K0;
+  char* lhs = const_cast<char*>(static_cast<const char*>(p->lhs_buffer)) + p->lhs_offset * ti.es;
+  char* rhs = const_cast<char*>(static_cast<const char*>(p->rhs_buffer)) + p->rhs_offset * ti.es;
+  const int kblk_elems = 128 / ti.es;  // one 128-byte swizzle row of K per stage
+  const int mma_k = 32 / ti.es;        // K per tcgen05.mma: 16 (16-bit) or 32 (8-bit)
+
+  if (variant == 0) {
+    const size_t need = mmt4d_tc_workspace_size(p);
+    if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+    if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+    const int64_t pitch = round_up(kelems * ti.es, 128);
+    char* ws_a = static_cast<char*>(ws);
+    char* ws_b = ws_a + round_up(p->M * 16 * pitch, 1024);
+    const int G = p->K0 * ti.es;
+    int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, pitch, p->M, p->K, G, stream);
+    if (rc) return rc;
+    rc = launch_retile(rhs, p->rhs_stride0 * ti.es, ws_b, pitch, p->N, p->K, G, stream);
+    if (rc) return rc;
+    const uint64_t da[3] = {uint64_t(kelems), uint64_t(p->M * 16), 1};
+    const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), 1};
+    const uint64_t sa[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->M * 16)};
+    const uint64_t sb[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->N * 16)};
+    const uint32_t ba[3] = {uint32_t(kblk_elems), BM, 1};
+    const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(bn), 1};
+    if (!encode_map(&P.map_a, ti.tm_type, ws_a, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_map(&P.map_b, ti.tm_type, ws_b, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+      return IREE_UK_B200_CUDA_ERROR;
+    P.sa = {1, BM * 128, {kblk_elems, 0, 0}, {0, BM, 0}, {0, 0, 0}};
+    P.sb = {1, bn * 128, {kblk_elems, 0, 0}, {0, bn, 0}, {0, 0, 0}};
+    P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
+    P.desc_lbo_a = P.desc_lbo_b = 1;
+    P.kadv_a = P.kadv_b = 2;  // 32 bytes of K per MMA inside the 128-byte swizzle row
+    P.idesc = make_idesc(ti, bn, false);
+    P.mma_per_stage = 4;
+    P.stage_bytes_a = BM * 128;
+    P.stage_bytes_b = bn * 128;
+    P.num_kb = int((kelems + kblk_elems - 1) / kblk_elems);
+  } else {
+    // MN-major, straight from a K0 = 1 16-bit operand (experimental variants 1..4).
+    if (ti.es != 2 || p->K0 != 1 || variant < 1 || variant > 4) return IREE_UK_B200_UNSUPPORTED;
+    const bool sw128 = variant <= 2, swapped = (variant % 2) == 0;
+    const int kblk = 64;
+    if (sw128) {
+      const uint64_t da[3] = {16, uint64_t(p->M), uint64_t(p->K)};
+      const uint64_t db[3] = {16, uint64_t(p->N), uint64_t(p->K)};
+      const uint64_t sa[2] = {uint64_t(p->lhs_stride0 * 2), 32};
+      const uint64_t sb[2] = {uint64_t(p->rhs_stride0 * 2), 32};
+      const uint32_t box[3] = {16, 4, uint32_t(kblk)};
+      if (!encode_map(&P.map_a, ti.tm_type, lhs, da, sa, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
+          !encode_map(&P.map_b, ti.tm_type, rhs, db, sb, box, CU_TENSOR_MAP_SWIZZLE_128B))
+        return IREE_UK_B200_CUDA_ERROR;
+      const int box_bytes = kblk * 128;
+      P.sa = {BM / 64, box_bytes, {0, 0, kblk}, {0, BM / 16, 0}, {0, 4, 0}};
+      P.sb = {bn / 64, box_bytes, {0, 0, kblk}, {0, bn / 16, 0}, {0, 4, 0}};
+      const uint32_t mn_off = uint32_t(box_bytes), k_off = 1024;
+      P.desc_hi_a = P.desc_hi_b = desc_hi(swapped ? mn_off : k_off, 2);
+      P.desc_lbo_a = P.desc_lbo_b = (swapped ? k_off : mn_off) >> 4;
+      P.kadv_a = P.kadv_b = (16 * 128) >> 4;
+      P.stage_bytes_a = BM * kblk * 2;
+      P.stage_bytes_b = bn * kblk * 2;
+      if (bn % 64) return IREE_UK_B200_UNSUPPORTED;
+    } else {
+      const uint64_t da[3] = {16, uint64_t(p->K), uint64_t(p->M)};
+      const uint64_t db[3] = {16, uint64_t(p->K), uint64_t(p->N)};
+      const uint64_t sa[2] = {32, uint64_t(p->lhs_stride0 * 2)};
+      const uint64_t sb[2] = {32, uint64_t(p->rhs_stride0 * 2)};
+      const uint32_t ba[3] = {16, uint32_t(kblk), BM / 16};
+      const uint32_t bb[3] = {16, uint32_t(kblk), uint32_t(bn / 16)};
+      if (!encode_map(&P.map_a, ti.tm_type, lhs, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_32B) ||
+          !encode_map(&P.map_b, ti.tm_type, rhs, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_32B))
+        return IREE_UK_B200_CUDA_ERROR;
+      P.sa = {1, BM * kblk * 2, {0, kblk, 0}, {0, 0, BM / 16}, {0, 0, 0}};
+      P.sb = {1, bn * kblk * 2, {0, kblk, 0}, {0, 0, bn / 16}, {0, 0, 0}};
+      const uint32_t mn_off = uint32_t(kblk * 32), k_off = 256;
+      P.desc_hi_a = P.desc_hi_b = desc_hi(swapped ? mn_off : k_off, 6);
+      P.desc_lbo_a = P.desc_lbo_b = (swapped ? k_off : mn_off) >> 4;
+      P.kadv_a = P.kadv_b = (16 * 32) >> 4;
+      P.stage_bytes_a = BM * kblk * 2;
+      P.stage_bytes_b = bn * kblk * 2;
+    }
+    P.idesc = make_idesc(ti, bn, true);
+    P.mma_per_stage = kblk / mma_k;
+    P.num_kb = int((p->K + kblk - 1) / kblk);
+  }
+
+  P.bn = bn;
+  P.m_tiles = int((p->M * 16 + BM - 1) / BM);
+  P.n_tiles = int((p->N * 16 + bn - 1) / bn);
+  P.group_m = std::min(P.m_tiles, 16);
+  P.out = static_cast<char*>(p->out_buffer) + p->out_offset * 4;
+  P.out_stride0 = p->out_stride0;
+  P.M1 = p->M;
+  P.N1 = p->N;
+  P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
+  P.out_is_int = ti.is_int ? 1 : 0;
+  P.status = status;
+
+  const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
+  const int smem_budget = 200 * 1024;
+  P.num_stages = std::max(2, std::min(kMaxStages, smem_budget / stage_bytes));
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
+
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = std::min(P.m_tiles * P.n_tiles, sms);
+  cudaError_t e;
+  if (ti.is_int) {
+    e = cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+    mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
+  } else {
+    e = cudaFuncSetAttribute(mmt4d_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+    mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace uk

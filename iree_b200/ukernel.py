@@ -1,0 +1,120 @@
+"""Host-side mirror of the reference's ukernel interface, over the C ABI.
+
+The three operations keep the reference's names and argument meaning
+(``iree_uk_mmt4d`` / ``iree_uk_pack`` / ``iree_uk_unpack``,
+runtime/src/iree/builtins/ukernel/mmt4d.h:14-22, pack.h:26-34, unpack.h:17-25); buffers are
+CUDA device pointers and each call is enqueued on a CUDA stream. A non-zero status from the
+library raises ``UkernelError`` (the reference asserts instead).
+
+torch is used only for device memory and streams.
+"""
+import ctypes as C
+
+from . import abi
+from ._lib import lib
+
+
+class UkernelError(RuntimeError):
+    def __init__(self, status, what):
+        self.status = status
+        super().__init__("%s: %s" % (what, lib.iree_uk_b200_status_string(status).decode()))
+
+
+def _stream_handle(stream):
+    if stream is None:
+        import torch
+        return torch.cuda.current_stream().cuda_stream
+    return getattr(stream, "cuda_stream", stream)
+
+
+def _check(status, what):
+    if status != abi.OK:
+        raise UkernelError(status, what)
+
+
+def mmt4d_workspace_size(params):
+    """Scratch bytes ``mmt4d(..., workspace=...)`` can use for ``params`` (0: none)."""
+    return int(lib.iree_uk_b200_mmt4d_workspace_size(C.addressof(params)))
+
+
+def mmt4d(params, stream=None, workspace=None):
+    """``iree_uk_mmt4d_p`` on device buffers. ``workspace``: a torch uint8 CUDA tensor of at
+    least ``mmt4d_workspace_size(params)`` bytes, or None (then no scratch is used)."""
+    s = _stream_handle(stream)
+    if workspace is None:
+        _check(lib.iree_uk_b200_mmt4d(C.addressof(params), s), "mmt4d")
+    else:
+        _check(lib.iree_uk_b200_mmt4d_ws(C.addressof(params), workspace.data_ptr(),
+                                         workspace.numel() * workspace.element_size(), s), "mmt4d")
+
+
+def mmt4d_path(params, with_workspace=True):
+    """Which kernel serves the call (``abi.PATH_*``); raises on rejected parameters."""
+    r = lib.iree_uk_b200_mmt4d_path(C.addressof(params), 1 if with_workspace else 0)
+    if r < 0:
+        raise UkernelError(-r, "mmt4d_path")
+    return r
+
+
+def mmt4d_info(M0, N0, K0, flags):
+    """``iree_uk_mmt4d_info``: bit 0 set when a tensor-core kernel exists for the tile."""
+    return int(lib.iree_uk_b200_mmt4d_info(M0, N0, K0, flags))
+
+
+def pack(params, stream=None):
+    """``iree_uk_pack_p`` on device buffers."""
+    _check(lib.iree_uk_b200_pack(C.addressof(params), _stream_handle(stream)), "pack")
+
+
+def pack_path(params):
+    r = lib.iree_uk_b200_pack_path(C.addressof(params))
+    if r < 0:
+        raise UkernelError(-r, "pack_path")
+    return r
+
+
+def unpack(params, stream=None):
+    """``iree_uk_unpack_p`` on device buffers."""
+    _check(lib.iree_uk_b200_unpack(C.addressof(params), _stream_handle(stream)), "unpack")
+
+
+def unpack_path(params):
+    r = lib.iree_uk_b200_unpack_path(C.addressof(params))
+    if r < 0:
+        raise UkernelError(-r, "unpack_path")
+    return r
+
+
+def query_tile_sizes_2d(flags, size0=0, size1=0):
+    """``iree_uk_query_tile_sizes_2d``: (tile_size0, tile_size1)."""
+    p = abi.QueryTileSizes2dParams(flags=flags, size0=size0, size1=size1, cpu_data=None)
+    o = abi.QueryTileSizes2dOut()
+    _check(lib.iree_uk_b200_query_tile_sizes_2d(C.addressof(p), C.addressof(o)),
+           "query_tile_sizes_2d")
+    return int(o.tile_size0), int(o.tile_size1)
+
+
+def device_status(stream=None):
+    """Synchronises the stream and returns (status, detail word) of the bounded device waits."""
+    detail = C.c_uint32(0)
+    st = lib.iree_uk_b200_device_status(_stream_handle(stream), C.addressof(detail))
+    return st, int(detail.value)
+
+
+def shard_params(full, rank, world, rhs_is_local=False, out_is_local=True):
+    """Parameters of ``rank`` when the RHS tile rows (N) are split across ``world`` GPUs.
+    Returns (params, first owned tile row)."""
+    shard = abi.Mmt4dParams()
+    begin = abi.index_t(0)
+    _check(lib.iree_uk_b200_mmt4d_shard_params(C.addressof(full), rank, world,
+                                               1 if rhs_is_local else 0,
+                                               1 if out_is_local else 0, C.addressof(shard),
+                                               C.addressof(begin)), "mmt4d_shard_params")
+    return shard, int(begin.value)
+
+
+def interleave_slabs(gathered, out, M, N, tile_elems, elem_size, world, stream=None):
+    """[world][M][N/world][tile] -> [M][N][tile] on device (after an all-gather of slabs)."""
+    _check(lib.iree_uk_b200_interleave_slabs(gathered.data_ptr(), out.data_ptr(), M, N,
+                                             tile_elems, elem_size, world,
+                                             _stream_handle(stream)), "interleave_slabs")

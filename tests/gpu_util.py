@@ -1,0 +1,67 @@
+"""Helpers for the GPU parity tests: run a case through the C ABI on device copies of its
+host buffers and hand back the whole output allocation as bytes."""
+import numpy as np
+import torch
+
+import oracle
+from iree_b200 import ukernel as uk
+
+
+def to_device(arr):
+    return torch.from_numpy(np.ascontiguousarray(arr)).cuda()
+
+
+def run_mmt4d_case(case, use_workspace=True):
+    """Returns (gpu_out_bytes, path)."""
+    lhs, rhs, out = to_device(case.lhs), to_device(case.rhs), to_device(case.out_init)
+    p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+    ws = None
+    if use_workspace:
+        n = uk.mmt4d_workspace_size(p)
+        if n:
+            ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+    path = uk.mmt4d_path(p, ws is not None)
+    uk.mmt4d(p, workspace=ws)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), path
+
+
+def oracle_mmt4d(case, impl="oracle"):
+    out = case.out_init.copy()
+    oracle.mmt4d(case.params(case.lhs, case.rhs, out), impl)
+    return out
+
+
+def run_pack_case(case):
+    inp, out = to_device(case.inp), to_device(case.out_init)
+    p = case.params(inp.data_ptr(), out.data_ptr())
+    path = uk.pack_path(p)
+    uk.pack(p)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), path
+
+
+def oracle_pack(case):
+    out = case.out_init.copy()
+    oracle.pack(case.params(case.inp, out))
+    return out
+
+
+def run_unpack_case(case):
+    inp, out = to_device(case.inp), to_device(case.out_init)
+    p = case.params(inp.data_ptr(), out.data_ptr())
+    path = uk.unpack_path(p)
+    uk.unpack(p)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), path
+
+
+def oracle_unpack(case):
+    out = case.out_init.copy()
+    oracle.unpack(case.params(case.inp, out))
+    return out
+
+
+def check_device_status():
+    st, detail = uk.device_status()
+    assert st == 0, "device-side bounded wait ran out: status %d detail 0x%x" % (st, detail)

@@ -1,0 +1,193 @@
+"""Host-side checks that need no GPU: the shared library loads, exports every symbol the
+public header declares, rejects what the reference's *_validate functions reject, and
+selects kernels as documented."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from iree_b200 import abi
+from iree_b200 import ukernel as uk
+from iree_b200._lib import SIGNATURES, lib
+from oracle import cases
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "iree_uk_b200.h")).read()
+    declared = set(re.findall(r"\b(iree_uk_b200_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(SIGNATURES), declared ^ set(SIGNATURES)
+    for name in declared:
+        assert getattr(lib, name) is not None
+    assert b"sm_100a" in lib.iree_uk_b200_version()
+
+
+def test_struct_layouts_match_reference():
+    assert C.sizeof(abi.Mmt4dParams) == 120
+    assert C.sizeof(abi.PackParams) == 136
+    assert C.sizeof(abi.UnpackParams) == 128
+    assert abi.Mmt4dParams.M0.offset == 96 and abi.Mmt4dParams.flags.offset == 108
+    assert abi.Mmt4dParams.cpu_data.offset == 112
+    assert abi.PackParams.padding_value.offset == 112 and abi.PackParams.flags.offset == 120
+    assert abi.UnpackParams.flags.offset == 112 and abi.UnpackParams.cpu_data.offset == 120
+
+
+def _mmt4d(flags=abi.MMT4D_S8S8S32, M=4, N=4, K=4, M0=16, N0=16, K0=2):
+    p = abi.Mmt4dParams()
+    p.lhs_buffer, p.rhs_buffer, p.out_buffer = 0x10000, 0x20000, 0x30000
+    p.M, p.N, p.K, p.M0, p.N0, p.K0, p.flags = M, N, K, M0, N0, K0, flags
+    p.lhs_stride0, p.rhs_stride0, p.out_stride0 = K * M0 * K0, K * N0 * K0, N * M0 * N0
+    return p
+
+
+def test_mmt4d_validation_mirrors_reference():
+    # ukernel/mmt4d.c:12-48
+    assert uk.mmt4d_path(_mmt4d()) == abi.PATH_TCGEN05_RETILE
+    for mutate in (lambda p: setattr(p, "flags", p.flags | 0x800),       # unknown flag bit
+                   lambda p: setattr(p, "flags", 0x0B),                  # type id out of range
+                   lambda p: setattr(p, "flags", 0x00),                  # no type
+                   lambda p: setattr(p, "M", -1),
+                   lambda p: setattr(p, "K", 1 << 31),
+                   lambda p: setattr(p, "M0", 1 << 15),
+                   lambda p: setattr(p, "N0", -1)):
+        p = _mmt4d()
+        mutate(p)
+        with pytest.raises(uk.UkernelError) as e:
+            uk.mmt4d_path(p)
+        assert e.value.status == abi.INVALID_ARGUMENT
+    # u4 right-hand side: K0, stride and offset must be whole bytes
+    p = _mmt4d(abi.MMT4D_S16U4S32, M0=1, N0=32, K0=8)
+    assert uk.mmt4d_path(p) == abi.PATH_GEMV
+    p.rhs_stride0 += 1
+    with pytest.raises(uk.UkernelError):
+        uk.mmt4d_path(p)
+    p = _mmt4d(abi.MMT4D_S16U4S32, M0=5, N0=3, K0=3)
+    with pytest.raises(uk.UkernelError):
+        uk.mmt4d_path(p)
+    # flags 0x200 / 0x400 are accepted and ignored
+    p = _mmt4d()
+    p.flags |= abi.MMT4D_ALLOW_GENERIC_FALLBACK | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS
+    assert uk.mmt4d_path(p) == abi.PATH_TCGEN05_RETILE
+
+
+def test_mmt4d_early_outs_and_paths():
+    # ukernel/mmt4d.c:105-113
+    assert uk.mmt4d_path(_mmt4d(M=0)) == abi.PATH_NONE
+    assert uk.mmt4d_path(_mmt4d(N=0)) == abi.PATH_NONE
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_S8S8S32 | abi.MMT4D_ACCUMULATE, K=0)) == abi.PATH_NONE
+    assert uk.mmt4d_path(_mmt4d(K=0)) == abi.PATH_ZERO_FILL
+    # without a workspace the tensor-core path is not taken
+    assert uk.mmt4d_path(_mmt4d(), with_workspace=False) == abi.PATH_GENERIC
+    # odd tile shapes and misaligned operands go to the generic kernel
+    assert uk.mmt4d_path(_mmt4d(M0=9, N0=6, K0=3)) == abi.PATH_GENERIC
+    p = _mmt4d()
+    p.lhs_offset = 1
+    assert uk.mmt4d_path(p) == abi.PATH_GENERIC
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F32F32F32, K0=1)) == abi.PATH_GENERIC
+    # 16-bit-output triples are valid for the reference but not served here
+    with pytest.raises(uk.UkernelError) as e:
+        uk.mmt4d_path(_mmt4d(abi.MMT4D_F16F16F16, K0=1))
+    assert e.value.status == abi.UNSUPPORTED
+
+
+def test_mmt4d_info_and_workspace_size():
+    assert uk.mmt4d_info(16, 16, 2, abi.MMT4D_S8S8S32) == 1
+    assert uk.mmt4d_info(16, 16, 1, abi.MMT4D_F16F16F32) == 1
+    assert uk.mmt4d_info(16, 16, 2, abi.MMT4D_BF16BF16F32) == 1
+    assert uk.mmt4d_info(9, 6, 3, abi.MMT4D_S8S8S32) == 0
+    assert uk.mmt4d_info(16, 16, 1, abi.MMT4D_F32F32F32) == 0
+    p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
+    # row-major copies of both operands, 128-byte row pitch
+    assert uk.mmt4d_workspace_size(p) == (512 + 1792) * 16 * 4096 * 2 * 2
+    assert uk.mmt4d_workspace_size(_mmt4d(M0=9, N0=6, K0=3)) == 0
+
+
+def _pack(flags=abi.PACK_F32F32, o=(4, 8), t=(16, 1), in_size=None):
+    p = abi.PackParams()
+    p.in_buffer, p.out_buffer = 0x10000, 0x20000
+    p.flags = flags
+    p.out_size0, p.out_size1, p.out_size2, p.out_size3 = o[0], o[1], t[0], t[1]
+    p.out_stride1 = t[0] * t[1]
+    p.out_stride0 = o[1] * p.out_stride1
+    p.in_size0, p.in_size1 = in_size or (o[0] * t[0], o[1] * t[1])
+    p.in_stride0, p.in_stride1 = p.in_size1, 1
+    return p
+
+
+def test_pack_validation_mirrors_reference():
+    # ukernel/pack.c:51-104
+    assert uk.pack_path(_pack()) == abi.PATH_FAST_COPY
+    assert uk.pack_path(_pack(o=(0, 3))) == abi.PATH_NONE
+    bad = [lambda p: setattr(p, "flags", 0x06), lambda p: setattr(p, "flags", p.flags | 0x400),
+           lambda p: setattr(p, "out_stride1", 17), lambda p: setattr(p, "in_size0", 65),
+           lambda p: setattr(p, "in_stride0", -1)]
+    for mutate in bad:
+        p = _pack()
+        mutate(p)
+        with pytest.raises(uk.UkernelError) as e:
+            uk.pack_path(p)
+        assert e.value.status == abi.INVALID_ARGUMENT
+    # a tile larger than the reference's 4096-byte temporary is rejected (pack.c:9,43-46)
+    with pytest.raises(uk.UkernelError):
+        uk.pack_path(_pack(t=(64, 32)))
+    assert uk.pack_path(_pack(t=(32, 32))) == abi.PATH_FAST_COPY
+
+
+def test_unpack_validation_mirrors_reference():
+    # ukernel/unpack.c:31-82
+    p = abi.UnpackParams()
+    p.in_buffer, p.out_buffer = 0x10000, 0x20000
+    p.flags = abi.UNPACK_I32I32
+    p.in_size0, p.in_size1, p.in_size2, p.in_size3 = 4, 4, 16, 16
+    p.in_stride1, p.in_stride0 = 256, 1024
+    p.out_size0, p.out_size1, p.out_stride0, p.out_stride1 = 64, 64, 64, 1
+    assert uk.unpack_path(p) == abi.PATH_FAST_COPY
+    p.flags = 0x02  # I8I8 exists for pack only (exported_bits.h:76)
+    with pytest.raises(uk.UkernelError):
+        uk.unpack_path(p)
+    p.flags = abi.UNPACK_I32I32
+    p.out_size0 = 65
+    with pytest.raises(uk.UkernelError):
+        uk.unpack_path(p)
+    p.out_size0 = 0
+    assert uk.unpack_path(p) == abi.PATH_NONE
+
+
+def test_query_tile_sizes():
+    # roles: LHS -> (M0,K0), RHS -> (N0,K0), RESULT -> (M0,N0)  (query_tile_sizes.c:43-63)
+    assert uk.query_tile_sizes_2d(0x0201) == (16, 2)
+    assert uk.query_tile_sizes_2d(0x0502) == (16, 2)
+    assert uk.query_tile_sizes_2d(0x0303) == (16, 16)
+    assert uk.query_tile_sizes_2d(0x0301) == (16, 1)
+    with pytest.raises(uk.UkernelError):
+        uk.query_tile_sizes_2d(0x0701)
+    with pytest.raises(uk.UkernelError):
+        uk.query_tile_sizes_2d(0x0204)
+
+
+def test_shard_params_partition_n():
+    full = _mmt4d(abi.MMT4D_BF16BF16F32, M=8, N=30, K=16)
+    covered = []
+    for world in (1, 2, 4, 8):
+        nb = 0
+        for r in range(world):
+            sh, begin = uk.shard_params(full, r, world, rhs_is_local=False, out_is_local=False)
+            assert begin == nb
+            assert sh.rhs_offset == full.rhs_offset + begin * full.rhs_stride0
+            assert sh.out_offset == full.out_offset + begin * 256
+            assert sh.out_stride0 == full.out_stride0 and sh.M == full.M and sh.K == full.K
+            nb += sh.N
+            sl, _ = uk.shard_params(full, r, world, rhs_is_local=True, out_is_local=True)
+            assert sl.rhs_offset == full.rhs_offset and sl.out_stride0 == sl.N * 256
+        assert nb == full.N
+        covered.append(world)
+    with pytest.raises(uk.UkernelError):
+        uk.shard_params(full, 2, 2)
+
+
+def test_status_strings():
+    assert lib.iree_uk_b200_status_string(0) == b"OK"
+    assert lib.iree_uk_b200_status_string(abi.DEVICE_TIMEOUT) == b"DEVICE_TIMEOUT"

@@ -1,0 +1,199 @@
+"""GPU parity: the CUDA library, called through the C ABI, against the CPU oracle on the
+reference tests' own case lists (tools/mmt4d_test.c:459-603, pack_test.c:137-241,
+unpack_test.c:118-216). Integers, pack and unpack: whole output allocation bit-exact
+(stride gaps and offset prefix included). Floats on the small-integer value ranges of
+tools/util.c:136-168 are exact too."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from iree_b200 import abi
+from oracle import cases
+
+import gpu_util as G
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device_status_clean():
+    yield
+    G.check_device_status()
+
+
+def _mmt4d_ids(tiles):
+    return ["t%x_%dx%dx%d" % t for t in tiles]
+
+
+@pytest.mark.parametrize("tile", cases.MMT4D_TILES + cases.MMT4D_TILES_EXTRA,
+                         ids=_mmt4d_ids(cases.MMT4D_TILES + cases.MMT4D_TILES_EXTRA))
+def test_mmt4d_reference_case_list(tile):
+    n = 0
+    for case in cases.all_mmt4d_cases([tile]):
+        got, _ = G.run_mmt4d_case(case)
+        want = G.oracle_mmt4d(case)
+        assert np.array_equal(got, want), case.label()
+        n += 1
+    assert n > 0
+
+
+@pytest.mark.parametrize("tile", [(abi.MMT4D_S8S8S32, 16, 16, 2), (abi.MMT4D_F16F16F32, 16, 16, 1),
+                                  (abi.MMT4D_BF16BF16F32, 16, 16, 2),
+                                  (abi.MMT4D_S8S8S32, 16, 16, 8), (abi.MMT4D_BF16BF16F32, 16, 16, 1)],
+                         ids=lambda t: "t%x_%dx%dx%d" % t)
+@pytest.mark.parametrize("shape", [(1, 1, 1), (8, 16, 64), (9, 17, 65), (3, 5, 7), (16, 32, 130),
+                                   (24, 40, 31), (1, 1, 1000)], ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_tensor_core_path_exact(tile, shape, accumulate):
+    """Aligned, tight cases that the tensor-core path serves; small-integer values make the
+    expected result exact for every accumulation order."""
+    t, M0, N0, K0 = tile
+    M, N, K = shape
+    case = cases.Mmt4dCase(t, M0, N0, K0, M, N, K, accumulate, seed=7, mode="exact", loose=False)
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    want = G.oracle_mmt4d(case)
+    assert np.array_equal(got, want), case.label()
+
+
+def test_mmt4d_tensor_core_loose_out_stride():
+    """A non-tight out_stride0 (multiple of 16 bytes) keeps the tensor-core path and must not
+    touch the gap between tile rows."""
+    case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 10, 9, 40, 0, seed=3, loose=False)
+    case.out_stride0 += 8
+    case.out_init = cases.random_elements("s32", case.out_offset + case.M * case.out_stride0,
+                                          np.random.default_rng(5))
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    assert np.array_equal(got, G.oracle_mmt4d(case))
+
+
+@pytest.mark.parametrize("t,M0,N0,K0,M,N,K,acc,tol", [
+    (abi.MMT4D_F16F16F32, 16, 16, 1, 16, 16, 512, 1, 1e-3),
+    (abi.MMT4D_BF16BF16F32, 16, 16, 2, 24, 32, 256, 0, 1e-3),
+    (abi.MMT4D_F16F16F32, 4, 6, 5, 5, 7, 13, 1, 1e-3),
+])
+def test_mmt4d_float_normal_values(t, M0, N0, K0, M, N, K, acc, tol):
+    """N(0,1) operands: relative Frobenius error <= 1e-3 against the oracle's f32
+    accumulation (the tolerance the headline configurations state)."""
+    case = cases.Mmt4dCase(t, M0, N0, K0, M, N, K, acc, seed=11, mode="normal", loose=False)
+    got, _ = G.run_mmt4d_case(case)
+    want = G.oracle_mmt4d(case)
+    err = cases.rel_frobenius(got.view(np.float32), want.view(np.float32))
+    assert err <= tol, err
+
+
+def test_mmt4d_s16u4_gemv_path():
+    for (M, N, K, acc) in [(1, 1, 1, 0), (1, 7, 33, 1), (3, 5, 64, 0), (1, 448, 512, 0)]:
+        case = cases.Mmt4dCase(abi.MMT4D_S16U4S32, 1, 32, 8, M, N, K, acc, seed=M + N, mode="normal",
+                               loose=False)
+        got, path = G.run_mmt4d_case(case)
+        assert path == abi.PATH_GEMV
+        assert np.array_equal(got, G.oracle_mmt4d(case)), (M, N, K, acc)
+
+
+def test_mmt4d_int_wraparound():
+    """int32 sums wrap modulo 2^32 like the reference's (extreme s8 values, long K, and an
+    initial accumulator near INT32_MAX)."""
+    case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 4096, 1, seed=1, loose=False)
+    case.lhs[:] = 0x80  # -128
+    case.rhs[:] = 0x80
+    case.out_init.view(np.int32)[:] = 2**31 - 5
+    want = G.oracle_mmt4d(case)
+    for ws in (True, False):
+        got, _ = G.run_mmt4d_case(case, use_workspace=ws)
+        assert np.array_equal(got, want), ws
+
+
+def test_mmt4d_int_overflow_inside_accumulator():
+    """A sum that leaves the int32 range while it is still being accumulated (K = 140000
+    products of -128 * -128) must wrap like the reference's, not saturate."""
+    case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 1, 1, 70000, 0, seed=1, loose=False)
+    case.lhs[:] = 0x80
+    case.rhs[:] = 0x80
+    want = G.oracle_mmt4d(case)
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("tile", cases.PACK_TILES, ids=lambda t: "t%x_%dx%d" % t)
+def test_pack_reference_case_list(tile):
+    paths = set()
+    for case in cases.all_pack_cases([tile]):
+        got, path = G.run_pack_case(case)
+        paths.add(path)
+        assert np.array_equal(got, G.oracle_pack(case)), vars(case)
+    assert paths
+
+
+@pytest.mark.parametrize("tile", cases.UNPACK_TILES, ids=lambda t: "t%x_%dx%d" % t)
+def test_unpack_reference_case_list(tile):
+    for case in cases.all_unpack_cases([tile]):
+        got, _ = G.run_unpack_case(case)
+        assert np.array_equal(got, G.oracle_unpack(case)), vars(case)
+
+
+@pytest.mark.parametrize("tile", cases.PACK_TILES, ids=lambda t: "t%x_%dx%d" % t)
+def test_pack_aligned_vector_paths(tile):
+    """Tight, 16-byte aligned cases (no random offsets) reach the vectorised branches."""
+    seed = 100
+    for outer in [(3, 2), (9, 33), (40, 70)]:
+        for ti in (0, 1):
+            for to in (0, 1):
+                for pad in cases.PAD_MODES:
+                    seed += 1
+                    case = cases.PackCase(tile[0], tile[1], tile[2], outer, ti, to, pad, seed,
+                                          loose=False)
+                    got, _ = G.run_pack_case(case)
+                    assert np.array_equal(got, G.oracle_pack(case)), vars(case)
+
+
+@pytest.mark.parametrize("tile", cases.UNPACK_TILES, ids=lambda t: "t%x_%dx%d" % t)
+def test_unpack_aligned_vector_paths(tile):
+    seed = 200
+    for outer in [(3, 2), (9, 33), (40, 70)]:
+        for ti in (0, 1):
+            for to in (0, 1):
+                for pad in cases.PAD_MODES:
+                    seed += 1
+                    case = cases.UnpackCase(tile[0], tile[1], tile[2], outer, ti, to, pad, seed,
+                                            loose=False)
+                    got, _ = G.run_unpack_case(case)
+                    assert np.array_equal(got, G.oracle_unpack(case)), vars(case)
+
+
+def test_generic_kernels_forced():
+    """IREE_UK_B200_FORCE_GENERIC routes every call to the one-thread-per-element kernels."""
+    os.environ["IREE_UK_B200_FORCE_GENERIC"] = "1"
+    try:
+        for case in cases.all_pack_cases([(abi.PACK_BF16BF16, 16, 2), (abi.PACK_F32F32, 3, 5)]):
+            got, path = G.run_pack_case(case)
+            assert path in (abi.PATH_GENERIC, abi.PATH_NONE)
+            assert np.array_equal(got, G.oracle_pack(case))
+        for case in cases.all_unpack_cases([(abi.UNPACK_I32I32, 16, 16), (abi.UNPACK_F16F16, 6, 7)]):
+            got, path = G.run_unpack_case(case)
+            assert path in (abi.PATH_GENERIC, abi.PATH_NONE)
+            assert np.array_equal(got, G.oracle_unpack(case))
+        case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 64, 1, seed=2, loose=False)
+        got, path = G.run_mmt4d_case(case)
+        assert path == abi.PATH_GENERIC
+        assert np.array_equal(got, G.oracle_mmt4d(case))
+    finally:
+        del os.environ["IREE_UK_B200_FORCE_GENERIC"]
+
+
+def test_rejected_parameters_launch_nothing():
+    from iree_b200 import ukernel as uk
+    case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 2, 2, 2, 0, loose=False)
+    lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
+    p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+    p.flags |= 0x800
+    with pytest.raises(uk.UkernelError) as e:
+        uk.mmt4d(p)
+    assert e.value.status == abi.INVALID_ARGUMENT
+    import torch
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), case.out_init)
