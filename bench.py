@@ -1,0 +1,373 @@
+#!/usr/bin/env python
+"""Headline benchmark: the N-sharded prefill GEMM as one mmt4d call per GPU.
+
+Workload (one "step" = one mmt4d call over the whole problem): mmt4d bf16bf16f32, logical
+M = 8192 tokens x K = 8192 x N = 28672 (a Llama-3-70B-shaped FFN up-projection), tiles
+16x16x2, i.e. LHS [512][4096][16][2], RHS [1792][4096][16][2], out f32 [512][1792][16][16].
+With G GPUs (one process per GPU, launched by torch.distributed.run) rank r owns RHS tile
+rows [r*N1/G, (r+1)*N1/G) and writes its own [512][N1/G][16][16] slab: no collective on the
+data path, the LHS is replicated. Inputs are synthetic (seeded N(0,1) activations, N(0,0.02)
+weights) and much larger than L2.
+
+One JSON line is printed by rank 0. `value` is whole-job TFLOP/s with inputs resident in
+HBM, timed with CUDA events on the launching stream, max over ranks. `e2e` is the same
+metric through the host-buffer path: pinned host LHS/RHS copied to the device, the C-ABI
+call, and the output slab copied back, all inside the timed region.
+
+`--impl reference` times the reference's own CPU ukernel (compiled under oracle/_ref, all
+host cores, M split over threads) on a bounded sample of the same workload.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M1, K1, N1 = 512, 4096, 1792
+M0, N0, K0 = 16, 16, 2
+WORKLOAD = "mmt4d_bf16bf16f32_8192x8192x28672_tiles16x16x2_llama3_70b_ffn_up_prefill"
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return json.load(f), "measured"
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY,
+                 "--format=csv,noheader,nounits", "-lms", "20"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxc, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                clocks.append(float(r[0]))
+                maxc = float(r[1])
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        # keep the samples taken under load (upper half of the observed clocks)
+        clocks.sort()
+        med = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": med, "sm_max_mhz": maxc, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+class CpuReference:
+    """The CPU reference (oracle/_ref when built, else the C port) on a bounded sample of the
+    workload: `rows` LHS tile rows, all N and K, tile rows split over all host threads."""
+
+    def __init__(self, max_rows):
+        import numpy as np
+
+        import oracle
+        from iree_b200 import abi
+        self.oracle, self.abi = oracle, abi
+        self.kind = "reference" if oracle.ref_available() else "port"
+        self.impl = "ref" if self.kind == "reference" else "oracle"
+        rng = np.random.default_rng(1234)
+
+        def bf16(n, scale):
+            out = np.empty(n, dtype=np.uint16)
+            step = 1 << 24
+            for i in range(0, n, step):
+                x = rng.standard_normal(min(step, n - i), dtype=np.float32) * np.float32(scale)
+                out[i:i + step] = (x.view(np.uint32) >> 16).astype(np.uint16)
+            return out
+
+        self.max_rows = max_rows
+        self.lhs = bf16(max_rows * K1 * M0 * K0, 1.0)
+        self.rhs = bf16(N1 * K1 * N0 * K0, 0.02)
+        self.out = np.zeros(max_rows * N1 * M0 * N0, dtype=np.float32)
+        self.threads = os.cpu_count() or 1
+
+    def run(self, rows):
+        """Seconds for one mmt4d over `rows` tile rows; also returns the threads used."""
+        abi = self.abi
+        rows = min(rows, self.max_rows)
+        p = abi.Mmt4dParams()
+        p.lhs_buffer, p.rhs_buffer = self.lhs.ctypes.data, self.rhs.ctypes.data
+        p.out_buffer = self.out.ctypes.data
+        p.M, p.N, p.K, p.M0, p.N0, p.K0 = rows, N1, K1, M0, N0, K0
+        p.lhs_stride0, p.rhs_stride0, p.out_stride0 = K1 * M0 * K0, K1 * N0 * K0, N1 * M0 * N0
+        p.flags = abi.MMT4D_BF16BF16F32
+        t0 = time.perf_counter()
+        used = self.oracle.mmt4d_threaded(p, self.threads, self.impl)
+        return time.perf_counter() - t0, used
+
+    def sized_rows(self, seconds):
+        """Tile rows (a multiple of the thread count) that take about `seconds`."""
+        dt, _ = self.run(self.threads)
+        rate_rows = self.threads / dt
+        rows = int(max(self.threads, min(self.max_rows, round(seconds * rate_rows))))
+        return max(self.threads, rows // self.threads * self.threads)
+
+
+def sample_flops(rows):
+    return 2.0 * (rows * M0) * (N1 * N0) * (K1 * K0)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    ref = CpuReference(M1)
+    rows = ref.sized_rows(1.5)  # about 1.5 s of host work per step
+    kind, used = ref.kind, ref.threads
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, used = ref.run(rows)
+        if i >= args.warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    value = sample_flops(rows) / sec / 1e12
+    sample = "M reduced to %d of %d LHS tile rows (all N, all K) per step" % (rows, M1)
+    line = {
+        "impl": "reference", "metric": "mmt4d_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": used, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-supplementary", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from iree_b200 import abi
+    from iree_b200 import ukernel as uk
+    from iree_b200._lib import lib
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU fallback"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    assert N1 % world == 0, "N1 must divide across ranks"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- synthetic inputs, generated directly in the tiled layouts ----
+    n_local = N1 // world
+    gen = torch.Generator(device="cuda").manual_seed(1234 + 4)
+    lhs = torch.randn(M1 * K1 * M0 * K0, generator=gen, device="cuda").to(torch.bfloat16)
+    gen_w = torch.Generator(device="cuda").manual_seed(99 + rank)
+    rhs = (torch.randn(n_local * K1 * N0 * K0, generator=gen_w, device="cuda") * 0.02).to(
+        torch.bfloat16)
+    out = torch.empty(M1 * n_local * M0 * N0, dtype=torch.float32, device="cuda")
+
+    full = abi.Mmt4dParams()
+    full.M, full.N, full.K, full.M0, full.N0, full.K0 = M1, N1, K1, M0, N0, K0
+    full.flags = abi.MMT4D_BF16BF16F32
+    full.lhs_buffer, full.rhs_buffer, full.out_buffer = lhs.data_ptr(), rhs.data_ptr(), out.data_ptr()
+    full.lhs_stride0, full.rhs_stride0 = K1 * M0 * K0, K1 * N0 * K0
+    full.out_stride0 = N1 * M0 * N0
+    p, n_begin = uk.shard_params(full, rank, world, rhs_is_local=True, out_is_local=True)
+    ws = torch.empty(max(uk.mmt4d_workspace_size(p), 1), dtype=torch.uint8, device="cuda")
+    path = uk.mmt4d_path(p, True)
+    assert path in (abi.PATH_TCGEN05, abi.PATH_TCGEN05_RETILE), "tensor-core path not selected"
+    stream = torch.cuda.current_stream()
+    launches_per_step = 3 if path == abi.PATH_TCGEN05_RETILE else 1
+
+    # ---- warm-up ----
+    for _ in range(args.warmup):
+        uk.mmt4d(p, stream, ws)
+    barrier()
+
+    # ---- spot check of the result against a plain fp32 matmul of the same tiles ----
+    def tile_rows(buf, i, count):
+        t = buf.view(-1, K1, 16, K0)[i:i + count].float()          # [c][K1][16][K0]
+        return t.permute(0, 2, 1, 3).reshape(count * 16, K1 * K0)  # [c*16][K]
+    a = tile_rows(lhs, M1 - 2, 2)
+    b = tile_rows(rhs, n_local - 2, 2)
+    want = a @ b.t()
+    got = out.view(M1, n_local, 16, 16)[M1 - 2:, n_local - 2:].permute(0, 2, 1, 3).reshape(32, 32)
+    spot_err = float((got - want).norm() / want.norm())
+    assert spot_err < 1e-3, "result check failed: relative error %g" % spot_err
+
+    # ---- timed region: resident inputs ----
+    sampler = ClockSampler(local_rank)
+    lib.iree_uk_b200_debug_kernel_timing(1)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    kernel_ms, prepass_ms = [], []
+    barrier()
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        uk.mmt4d(p, stream, ws)
+    ev1.record(stream)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = ev0.elapsed_time(ev1)
+    # per-kernel durations (events recorded inside the library around the main kernel)
+    a_ms, b_ms = C.c_float(0), C.c_float(0)
+    for _ in range(5):
+        uk.mmt4d(p, stream, ws)
+        lib.iree_uk_b200_debug_last_kernel_ms(C.addressof(a_ms), C.addressof(b_ms))
+        prepass_ms.append(a_ms.value)
+        kernel_ms.append(b_ms.value)
+    lib.iree_uk_b200_debug_kernel_timing(0)
+    st, detail = uk.device_status(stream)
+    assert st == 0, "device status %d (0x%x)" % (st, detail)
+
+    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    total_flops = 2.0 * (M1 * M0) * (N1 * N0) * (K1 * K0)
+    value = total_flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end: pinned host buffers, H2D + call + D2H inside the timed region ----
+    h_lhs = torch.empty(lhs.numel(), dtype=torch.bfloat16).pin_memory()
+    h_rhs = torch.empty(rhs.numel(), dtype=torch.bfloat16).pin_memory()
+    h_out = torch.empty(out.numel(), dtype=torch.float32).pin_memory()
+    h_lhs.copy_(lhs)
+    h_rhs.copy_(rhs)
+    h2d = (h_lhs.numel() + h_rhs.numel()) * 2
+    d2h = h_out.numel() * 4
+
+    def e2e_step():
+        lhs.copy_(h_lhs, non_blocking=True)
+        rhs.copy_(h_rhs, non_blocking=True)
+        uk.mmt4d(p, stream, ws)
+        h_out.copy_(out, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / args.e2e_steps
+    e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = read_peaks()
+    k_ms = sorted(kernel_ms)[len(kernel_ms) // 2]
+    local_flops = total_flops / world
+    achieved = local_flops / (k_ms * 1e-3) / 1e12
+    peak = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", 1400.0)))
+    roofline = {
+        "bound": "tensor", "kernel": "mmt4d_tc_kernel", "achieved": achieved, "peak": peak,
+        "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+        "peak_kind": "%s, cuBLAS bf16 sustained" % peak_kind,
+        "peak_burst": peaks.get("bf16_tflops"), "frac_of_spec_2250": achieved / 2250.0,
+        "kernel_ms": k_ms, "prepass_ms": sorted(prepass_ms)[len(prepass_ms) // 2],
+    }
+
+    cpu = None
+    if world == 1:
+        ref = CpuReference(256)
+        rows = ref.sized_rows(15.0)  # about 15 s of host work
+        dt, used = ref.run(rows)
+        kind = ref.kind
+        cpu = {"value": sample_flops(rows) / dt / 1e12, "unit": "TFLOP/s", "cores": used,
+               "kind": kind,
+               "sample": "M reduced to %d of %d LHS tile rows (all N, all K), one run" % (rows, M1)}
+
+    line = {
+        "metric": "mmt4d_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tiles": "M0=16,N0=16,K0=2",
+                   "sharding": "N1 split over %d rank(s), no data-path collective" % world,
+                   "l2": "inputs_larger_than_l2", "path": "tcgen05+retile" if launches_per_step == 3 else "tcgen05",
+                   "spot_check_rel_err": spot_err},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+    }
+    if world == 1 and not args.no_supplementary:
+        try:
+            from iree_b200 import supplementary
+            line["supplementary"] = supplementary.run(peaks)
+        except Exception as e:  # supplementary figures never block the headline line
+            line["supplementary"] = {"error": repr(e)}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

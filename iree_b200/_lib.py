@@ -53,3 +53,7 @@ for _name, (_res, _args) in SIGNATURES.items():
 # internal entry point (not in the public header): explicit operand-staging variant
 lib.iree_uk_b200_debug_mmt4d_variant.restype = C.c_int
 lib.iree_uk_b200_debug_mmt4d_variant.argtypes = [_P, _P, _sz, C.c_int, _P]
+lib.iree_uk_b200_debug_kernel_timing.restype = C.c_int
+lib.iree_uk_b200_debug_kernel_timing.argtypes = [C.c_int]
+lib.iree_uk_b200_debug_last_kernel_ms.restype = C.c_int
+lib.iree_uk_b200_debug_last_kernel_ms.argtypes = [_P, _P]

@@ -26,6 +26,11 @@ uint32_t* device_status_word() {
   return addr[dev];
 }
 
+KernelTiming& kernel_timing() {
+  static KernelTiming t;
+  return t;
+}
+
 namespace {
 
 enum class Mmt4dPath { None, Generic, Tc, TcRetile, Gemv, ZeroFill };
@@ -341,6 +346,34 @@ IREE_UK_B200_EXPORT int iree_uk_b200_debug_mmt4d_variant(const iree_uk_mmt4d_par
   if (!mmt4d_tc_eligible(params)) return IREE_UK_B200_UNSUPPORTED;
   return launch_mmt4d_tc(params, workspace, workspace_bytes, variant,
                          static_cast<cudaStream_t>(cu_stream));
+}
+
+// Internal, not declared in the public header: benchmark timing of the tensor-core path.
+// enable != 0 creates three CUDA events (once) and makes every later tensor-core mmt4d call
+// record them before the re-tile pre-pass, before the main kernel and after it.
+IREE_UK_B200_EXPORT int iree_uk_b200_debug_kernel_timing(int enable) {
+  KernelTiming& t = kernel_timing();
+  if (enable && !t.ev[0]) {
+    for (int i = 0; i < 3; ++i)
+      if (cudaEventCreate(&t.ev[i]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  }
+  t.enabled = enable != 0;
+  t.recorded = false;
+  return IREE_UK_B200_OK;
+}
+
+// Milliseconds of the last recorded call: pre-pass and main kernel. Synchronises on the events.
+IREE_UK_B200_EXPORT int iree_uk_b200_debug_last_kernel_ms(float* prepass_ms, float* main_ms) {
+  KernelTiming& t = kernel_timing();
+  if (!t.enabled || !t.recorded) return IREE_UK_B200_INVALID_ARGUMENT;
+  if (cudaEventSynchronize(t.ev[2]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  float a = 0.f, b = 0.f;
+  if (cudaEventElapsedTime(&a, t.ev[0], t.ev[1]) != cudaSuccess ||
+      cudaEventElapsedTime(&b, t.ev[1], t.ev[2]) != cudaSuccess)
+    return IREE_UK_B200_CUDA_ERROR;
+  if (prepass_ms) *prepass_ms = a;
+  if (main_ms) *main_ms = b;
+  return IREE_UK_B200_OK;
 }
 
 }  // extern "C"

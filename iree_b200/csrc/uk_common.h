@@ -74,6 +74,15 @@ inline int cuda_status(cudaError_t e) {
   return e == cudaSuccess ? IREE_UK_B200_OK : IREE_UK_B200_CUDA_ERROR;
 }
 
+// Optional kernel timing for benchmarks (off by default): when enabled, launchers that run a
+// pre-pass plus a main kernel record CUDA events between them on the launching stream.
+struct KernelTiming {
+  bool enabled = false;
+  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};  // before pre-pass, before main, after main
+  bool recorded = false;
+};
+KernelTiming& kernel_timing();
+
 // True when the environment variable is set to a non-empty value other than "0".
 bool env_flag(const char* name);
 

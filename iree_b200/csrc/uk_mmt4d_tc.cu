@@ -605,6 +605,8 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
 
   TcParams P;
   std::memset(&P, 0, sizeof P);
+  KernelTiming& timing = kernel_timing();
+  if (timing.enabled) cudaEventRecord(timing.ev[0], stream);
   const int bn = pick_bn(p->M, p->N);
   const int64_t kelems = p->K * p->K0;
   char* lhs = const_cast<char*>(static_cast<const char*>(p->lhs_buffer)) + p->lhs_offset * ti.es;
@@ -713,6 +715,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int grid = std::min(P.m_tiles * P.n_tiles, sms);
   cudaError_t e;
+  if (timing.enabled) cudaEventRecord(timing.ev[1], stream);
   if (ti.is_int) {
     e = cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
@@ -721,6 +724,10 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     e = cudaFuncSetAttribute(mmt4d_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
     mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
+  }
+  if (timing.enabled) {
+    cudaEventRecord(timing.ev[2], stream);
+    timing.recorded = true;
   }
   return cuda_status(cudaGetLastError());
 }

@@ -1,0 +1,134 @@
+"""Device-timed figures for the other configurations of the path (single GPU): the small
+s8s8s32 GEMM, an s8s8s32 GEMM at the prefill dimensions, the f16 GEMM with ACCUMULATE, the
+s16u4s32 decode GEMV, and the pack / unpack relayouts. Used by ``bench.py`` to report them
+beside the headline line; every figure is CUDA-event time per call with L2 flushed (a
+256 MiB buffer is rewritten) between calls whose working set would fit in L2.
+
+Bytes for pack / unpack count what is read plus what is written.
+"""
+import torch
+
+from . import abi
+from . import ukernel as uk
+
+
+def _time(fn, iters=10, warmup=3, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def _mmt4d_params(flags, M, N, K, M0, N0, K0, lhs, rhs, out):
+    from .abi import MMT4D_BITS
+    p = abi.Mmt4dParams()
+    p.lhs_buffer, p.rhs_buffer, p.out_buffer = lhs.data_ptr(), rhs.data_ptr(), out.data_ptr()
+    p.M, p.N, p.K, p.M0, p.N0, p.K0, p.flags = M, N, K, M0, N0, K0, flags
+    p.lhs_stride0, p.rhs_stride0, p.out_stride0 = K * M0 * K0, K * N0 * K0, N * M0 * N0
+    return p
+
+
+def _rand_bytes(n):
+    return torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
+
+
+def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None):
+    lb, rb, _ = abi.MMT4D_BITS[flags & 0xFF]
+    nl, nr = M * K * M0 * K0, N * K * N0 * K0
+    if float_dtype is not None:
+        lhs = torch.randn(nl, device="cuda").to(float_dtype)
+        rhs = torch.randn(nr, device="cuda").to(float_dtype)
+    else:
+        lhs, rhs = _rand_bytes(nl * lb // 8), _rand_bytes(nr * rb // 8)
+    out = torch.randn(M * N * M0 * N0, device="cuda") if float_dtype is not None else \
+        torch.zeros(M * N * M0 * N0, dtype=torch.int32, device="cuda")
+    p = _mmt4d_params(flags, M, N, K, M0, N0, K0, lhs, rhs, out)
+    nws = uk.mmt4d_workspace_size(p)
+    ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
+    path = uk.mmt4d_path(p, ws is not None)
+    med, best = _time(lambda: uk.mmt4d(p, workspace=ws), flush=flush)
+    ops = 2.0 * M * M0 * N * N0 * K * K0
+    res = {"ms": med, "ms_best": best, "path": path, "tops": ops / med / 1e9}
+    return name, res
+
+
+def run(peaks):
+    res = {}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
+
+    # mmt4d s8s8s32 1024^3 (latency-bound by size) and at the prefill dimensions
+    for name, args in [
+        ("mmt4d_s8s8s32_1024x1024x1024", (abi.MMT4D_S8S8S32, 64, 64, 512, 16, 16, 2)),
+        ("mmt4d_s8s8s32_8192x28672x8192", (abi.MMT4D_S8S8S32, 512, 1792, 4096, 16, 16, 2)),
+    ]:
+        k, r = _mmt4d_case(name, *args, peaks, flush if args[1] < 512 else None)
+        r["frac_of_2x_bf16_burst"] = r["tops"] / (2 * bf16_peak)
+        r["frac_of_spec_4500"] = r["tops"] / 4500.0
+        res[k] = r
+    k, r = _mmt4d_case("mmt4d_f16f16f32_acc_4096x4096x4096",
+                       abi.MMT4D_F16F16F32 | abi.MMT4D_ACCUMULATE, 256, 256, 4096, 16, 16, 1,
+                       peaks, None, torch.float16)
+    r["frac_of_bf16_burst"] = r["tops"] / bf16_peak
+    r["frac_of_spec_2250"] = r["tops"] / 2250.0
+    res[k] = r
+    # decode GEMV s16u4s32: bytes are the algorithmic figure (weights + vector + output)
+    k, r = _mmt4d_case("mmt4d_s16u4s32_gemv_1x14336x4096", abi.MMT4D_S16U4S32, 1, 448, 512, 1,
+                       32, 8, peaks, flush)
+    gemv_bytes = 448 * 512 * 128 + 512 * 16 + 448 * 32 * 4
+    r["gbs"] = gemv_bytes / r["ms"] / 1e6
+    r["frac_hbm"] = r["gbs"] / hbm
+    res[k] = r
+
+    # pack f32 8192x8192 -> [512][8192][16][1]; TRANSPOSE_INNER variant; RHS-style 0x301
+    n = 8192
+    src = torch.randn(n * n, device="cuda")
+    dst = torch.empty(n * n, device="cuda")
+    nbytes = 2.0 * n * n * 4
+
+    def pack_params(flags, o0, o1, t0, t1):
+        p = abi.PackParams()
+        p.in_buffer, p.out_buffer = src.data_ptr(), dst.data_ptr()
+        p.in_size0, p.in_size1, p.in_stride0, p.in_stride1 = n, n, n, 1
+        p.out_size0, p.out_size1, p.out_size2, p.out_size3 = o0, o1, t0, t1
+        p.out_stride1 = t0 * t1
+        p.out_stride0 = o1 * p.out_stride1
+        p.flags = flags
+        return p
+
+    for name, p in [
+        ("pack_f32_8192x8192_to_512x8192x16x1", pack_params(abi.PACK_F32F32, 512, 8192, 16, 1)),
+        ("pack_f32_transpose_inner_512x8192x1x16",
+         pack_params(abi.PACK_F32F32 | abi.PACK_TRANSPOSE_INNER, 512, 8192, 1, 16)),
+        ("pack_f32_rhs_0x301_512x8192x16x1",
+         pack_params(abi.PACK_F32F32 | abi.PACK_TRANSPOSE_INNER | abi.PACK_TRANSPOSE_OUTER, 512,
+                     8192, 16, 1)),
+    ]:
+        med, best = _time(lambda: uk.pack(p))
+        res[name] = {"ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
+                     "frac_hbm": nbytes / med / 1e6 / hbm, "path": uk.pack_path(p)}
+
+    # unpack i32 [512][512][16][16] -> 8192x8192
+    q = abi.UnpackParams()
+    q.in_buffer, q.out_buffer = src.data_ptr(), dst.data_ptr()
+    q.in_size0, q.in_size1, q.in_size2, q.in_size3 = 512, 512, 16, 16
+    q.in_stride1, q.in_stride0 = 256, 512 * 256
+    q.out_size0, q.out_size1, q.out_stride0, q.out_stride1 = n, n, n, 1
+    q.flags = abi.UNPACK_I32I32
+    med, best = _time(lambda: uk.unpack(q))
+    res["unpack_i32_512x512x16x16_to_8192x8192"] = {
+        "ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
+        "frac_hbm": nbytes / med / 1e6 / hbm, "path": uk.unpack_path(q)}
+    return res
