@@ -235,6 +235,37 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* para
                                               void* workspace, size_t workspace_bytes,
                                               void* cu_stream);
 
+/* Capacity of the library-owned scratch used by iree_uk_b200_mmt4d_static_scratch. */
+#define IREE_UK_B200_STATIC_SCRATCH_BYTES (32u << 20)
+
+/* mmt4d for call sites that have no way to obtain device memory of their own. It has no
+ * counterpart in the reference: there the ukernels need no scratch at all.
+ *
+ * Who needs it: a ukernel call that IREE emits sits inside an already-planned dispatch. The
+ * compiler has laid out every buffer ahead of time, the ukernel contract forbids allocating
+ * (ukernel/README.md:17-26), and at that point of the HAL command stream there is no
+ * allocator to ask and no place to call cudaMalloc from. Such a caller can pass neither a
+ * workspace nor allocate one, so with iree_uk_b200_mmt4d it would be stuck on the generic
+ * kernel. This entry point gives it the tensor-core path anyway: the re-tiled operand
+ * copies go into a fixed IREE_UK_B200_STATIC_SCRATCH_BYTES (32 MiB) array that is part of
+ * the library image in each GPU's memory (every GPU that loads the library holds those
+ * 32 MiB until the process exits). The call itself allocates nothing, on host or device.
+ *
+ * Same operation, arguments and results as iree_uk_b200_mmt4d_ws. Differences:
+ *  - a problem whose scratch need (iree_uk_b200_mmt4d_workspace_size) exceeds the array is
+ *    refused with IREE_UK_B200_WORKSPACE_TOO_SMALL and nothing is launched; it is never
+ *    silently served by a slower kernel;
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current). Make that first call during
+ *    set-up, before any stream capture is begun on that device;
+ *  - all calls on a device share the one array. Nothing in it has to start at zero (the
+ *    pre-pass rewrites every byte the main kernel reads, so the previous call's leftovers
+ *    are harmless), but two calls whose kernels can overlap on the GPU — different streams
+ *    without an ordering between them — race on it. Keep calls on one stream, or order
+ *    them with events. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_static_scratch(
+    const iree_uk_mmt4d_params_t* params, void* cu_stream);
+
 /* Flat-argument twin of iree_uk_mmt4d (ukernel/mmt4d.h:14-22, mmt4d.c:151-177) with the
  * workspace and the stream appended; `cpu_data` is kept in the list so a call site can be
  * substituted one for one. */

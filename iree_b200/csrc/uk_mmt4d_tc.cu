@@ -733,3 +733,51 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
 }
 
 }  // namespace uk
+
+// ---------------------------------------------------------------------------------------
+// mmt4d with library-owned scratch, for callers that cannot allocate
+// ---------------------------------------------------------------------------------------
+namespace uk {
+namespace {
+
+// Part of the library image on every device that loads it. In host code this name is only a
+// handle for cudaGetSymbolAddress, never a pointer to hand to a kernel.
+static __device__ __align__(256) unsigned char g_static_scratch[IREE_UK_B200_STATIC_SCRATCH_BYTES];
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+void* static_scratch_address() {
+  constexpr int kMaxDevices = 64;
+  static void* addr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch) != cudaSuccess)
+      return nullptr;
+    addr[dev] = p;
+  }
+  return addr[dev];
+}
+
+}  // namespace
+}  // namespace uk
+
+extern "C" int iree_uk_b200_mmt4d_static_scratch(const iree_uk_mmt4d_params_t* params,
+                                                 void* cu_stream) {
+  const int rc = uk::validate_mmt4d(params);
+  if (rc) return rc;
+  // Only the tensor-core path uses scratch; everything else goes the usual way.
+  const bool trivial = params->M == 0 || params->N == 0 || params->K == 0 ||
+                       params->M0 == 0 || params->N0 == 0 || params->K0 == 0;
+  if (trivial || uk::mmt4d_gemv_s16u4_eligible(params) || !uk::mmt4d_tc_eligible(params))
+    return iree_uk_b200_mmt4d(params, cu_stream);
+  if (uk::mmt4d_tc_workspace_size(params) > size_t(IREE_UK_B200_STATIC_SCRATCH_BYTES))
+    return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  void* scratch = uk::static_scratch_address();
+  if (!scratch) return IREE_UK_B200_CUDA_ERROR;
+  return iree_uk_b200_mmt4d_ws(params, scratch, size_t(IREE_UK_B200_STATIC_SCRATCH_BYTES),
+                               cu_stream);
+}
+

@@ -48,6 +48,19 @@ def mmt4d(params, stream=None, workspace=None):
                                          workspace.numel() * workspace.element_size(), s), "mmt4d")
 
 
+STATIC_SCRATCH_BYTES = 32 << 20
+
+
+def mmt4d_static_scratch(params, stream=None):
+    """mmt4d for callers that cannot allocate or pass device scratch: same results as
+    ``mmt4d(..., workspace=...)``, with the re-tiled operands kept in a 32 MiB array that
+    lives inside the library on each GPU. Raises WORKSPACE_TOO_SMALL when the problem needs
+    more than that. Calls that may overlap on the GPU share (and would race on) that array;
+    make the first call on a device before beginning any stream capture there."""
+    _check(lib.iree_uk_b200_mmt4d_static_scratch(C.addressof(params), _stream_handle(stream)),
+           "mmt4d_static_scratch")
+
+
 def mmt4d_path(params, with_workspace=True):
     """Which kernel serves the call (``abi.PATH_*``); raises on rejected parameters."""
     r = lib.iree_uk_b200_mmt4d_path(C.addressof(params), 1 if with_workspace else 0)
