@@ -1,0 +1,39 @@
+"""N-sharding of mmt4d across GPUs: one process per GPU, no data-path collective.
+
+mmt4d output tile columns j depend only on RHS tile row j (the j loop of
+runtime/src/iree/builtins/ukernel/mmt4d.c:84-98 only advances ``rhs_panel`` and
+``out_tile``), so GPU r of G owns RHS tile rows [r*N/G, (r+1)*N/G), receives the full LHS and
+writes its own [M][N/G][M0][N0] slab. The arithmetic lives in the C ABI
+(``iree_uk_b200_mmt4d_shard_params``); this module adds the optional replication of the output
+through ``torch.distributed`` (NCCL all-gather of the slabs, then the library's interleave
+kernel).
+"""
+from . import ukernel as uk
+
+
+def shard_bounds(n_tiles, rank, world):
+    """(first tile row, count) owned by ``rank``: contiguous, remainder on the first ranks —
+    the same split ``iree_uk_b200_mmt4d_shard_params`` computes."""
+    base, rem = divmod(n_tiles, world)
+    begin = rank * base + min(rank, rem)
+    return begin, base + (1 if rank < rem else 0)
+
+
+def local_params(full, rank, world, rhs_is_local=True, out_is_local=True):
+    """This rank's ``Mmt4dParams`` and its first owned tile row."""
+    return uk.shard_params(full, rank, world, rhs_is_local, out_is_local)
+
+
+def gather_output(slab, M, N, tile_elems, group=None, stream=None):
+    """Replicate the output: all-gather equal per-rank slabs [M][N/world][tile] (a CUDA
+    tensor) and interleave them into [M][N][tile]. Returns the full tensor."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    if N % world:
+        raise ValueError("gather_output needs N divisible by the world size")
+    gathered = torch.empty(world * slab.numel(), dtype=slab.dtype, device=slab.device)
+    dist.all_gather_into_tensor(gathered, slab.contiguous().view(-1), group=group)
+    full = torch.empty_like(gathered)
+    uk.interleave_slabs(gathered, full, M, N, tile_elems, slab.element_size(), world, stream)
+    return full

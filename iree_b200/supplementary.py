@@ -12,7 +12,12 @@ from . import abi
 from . import ukernel as uk
 
 
-def _time(fn, iters=10, warmup=3, flush=None):
+ITERS, WARMUP = 10, 3
+
+
+def _time(fn, iters=None, warmup=None, flush=None):
+    iters = ITERS if iters is None else iters
+    warmup = WARMUP if warmup is None else warmup
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -63,8 +68,14 @@ def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None
     return name, res
 
 
-def run(peaks):
+def run(peaks, only=None, custom=None):
+    """All supplementary configurations, or those whose name contains ``only``. ``custom`` =
+    (type name, M1, N1, K1) adds one tensor-core mmt4d of that size (used for profiling)."""
     res = {}
+
+    def want(name):
+        return only is None or only in name
+
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     hbm = float(peaks.get("hbm_gbs", 6650.0))
     bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
@@ -74,23 +85,35 @@ def run(peaks):
         ("mmt4d_s8s8s32_1024x1024x1024", (abi.MMT4D_S8S8S32, 64, 64, 512, 16, 16, 2)),
         ("mmt4d_s8s8s32_8192x28672x8192", (abi.MMT4D_S8S8S32, 512, 1792, 4096, 16, 16, 2)),
     ]:
+        if not want(name):
+            continue
         k, r = _mmt4d_case(name, *args, peaks, flush if args[1] < 512 else None)
         r["frac_of_2x_bf16_burst"] = r["tops"] / (2 * bf16_peak)
         r["frac_of_spec_4500"] = r["tops"] / 4500.0
         res[k] = r
-    k, r = _mmt4d_case("mmt4d_f16f16f32_acc_4096x4096x4096",
-                       abi.MMT4D_F16F16F32 | abi.MMT4D_ACCUMULATE, 256, 256, 4096, 16, 16, 1,
-                       peaks, None, torch.float16)
-    r["frac_of_bf16_burst"] = r["tops"] / bf16_peak
-    r["frac_of_spec_2250"] = r["tops"] / 2250.0
-    res[k] = r
+    if custom is not None:
+        tname, cm, cn, ck = custom
+        flags, k0, dt = {"bf16": (abi.MMT4D_BF16BF16F32, 2, torch.bfloat16),
+                         "f16": (abi.MMT4D_F16F16F32, 1, torch.float16),
+                         "s8": (abi.MMT4D_S8S8S32, 2, None)}[tname]
+        k, r = _mmt4d_case("mmt4d_%s_custom_%dx%dx%d" % (tname, cm, cn, ck), flags, cm, cn, ck,
+                           16, 16, k0, peaks, None, dt)
+        res[k] = r
+    if want("mmt4d_f16f16f32_acc_4096x4096x4096"):
+        k, r = _mmt4d_case("mmt4d_f16f16f32_acc_4096x4096x4096",
+                           abi.MMT4D_F16F16F32 | abi.MMT4D_ACCUMULATE, 256, 256, 4096, 16, 16, 1,
+                           peaks, None, torch.float16)
+        r["frac_of_bf16_burst"] = r["tops"] / bf16_peak
+        r["frac_of_spec_2250"] = r["tops"] / 2250.0
+        res[k] = r
     # decode GEMV s16u4s32: bytes are the algorithmic figure (weights + vector + output)
-    k, r = _mmt4d_case("mmt4d_s16u4s32_gemv_1x14336x4096", abi.MMT4D_S16U4S32, 1, 448, 512, 1,
-                       32, 8, peaks, flush)
-    gemv_bytes = 448 * 512 * 128 + 512 * 16 + 448 * 32 * 4
-    r["gbs"] = gemv_bytes / r["ms"] / 1e6
-    r["frac_hbm"] = r["gbs"] / hbm
-    res[k] = r
+    if want("mmt4d_s16u4s32_gemv_1x14336x4096"):
+        k, r = _mmt4d_case("mmt4d_s16u4s32_gemv_1x14336x4096", abi.MMT4D_S16U4S32, 1, 448, 512,
+                           1, 32, 8, peaks, flush)
+        gemv_bytes = 448 * 512 * 128 + 512 * 16 + 448 * 32 * 4
+        r["gbs"] = gemv_bytes / r["ms"] / 1e6
+        r["frac_hbm"] = r["gbs"] / hbm
+        res[k] = r
 
     # pack f32 8192x8192 -> [512][8192][16][1]; TRANSPOSE_INNER variant; RHS-style 0x301
     n = 8192
@@ -116,6 +139,8 @@ def run(peaks):
          pack_params(abi.PACK_F32F32 | abi.PACK_TRANSPOSE_INNER | abi.PACK_TRANSPOSE_OUTER, 512,
                      8192, 16, 1)),
     ]:
+        if not want(name):
+            continue
         med, best = _time(lambda: uk.pack(p))
         res[name] = {"ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
                      "frac_hbm": nbytes / med / 1e6 / hbm, "path": uk.pack_path(p)}
@@ -127,8 +152,42 @@ def run(peaks):
     q.in_stride1, q.in_stride0 = 256, 512 * 256
     q.out_size0, q.out_size1, q.out_stride0, q.out_stride1 = n, n, n, 1
     q.flags = abi.UNPACK_I32I32
-    med, best = _time(lambda: uk.unpack(q))
-    res["unpack_i32_512x512x16x16_to_8192x8192"] = {
-        "ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
-        "frac_hbm": nbytes / med / 1e6 / hbm, "path": uk.unpack_path(q)}
+    if want("unpack_i32_512x512x16x16_to_8192x8192"):
+        med, best = _time(lambda: uk.unpack(q))
+        res["unpack_i32_512x512x16x16_to_8192x8192"] = {
+            "ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
+            "frac_hbm": nbytes / med / 1e6 / hbm, "path": uk.unpack_path(q)}
     return res
+
+
+def main():
+    """``python -m iree_b200.supplementary [--only SUBSTR] [--mmt4d bf16,M1,N1,K1]
+    [--iters N] [--warmup N]``: prints one JSON object. Small, single-kernel runs of this
+    command are what the profiles under ``profiles/`` were captured from."""
+    import argparse
+    import json
+    import os
+    global ITERS, WARMUP
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None)
+    ap.add_argument("--mmt4d", default=None)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    a = ap.parse_args()
+    ITERS, WARMUP = a.iters, a.warmup
+    custom = None
+    if a.mmt4d:
+        t, m, n, k = a.mmt4d.split(",")
+        custom = (t, int(m), int(n), int(k))
+    peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                              "MEASURED_PEAKS.json")
+    try:
+        peaks = json.load(open(peaks_path))
+    except OSError:
+        peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    only = a.only if a.only is not None else ("\0" if custom else None)
+    print(json.dumps(run(peaks, only=only, custom=custom)))
+
+
+if __name__ == "__main__":
+    main()

@@ -197,3 +197,19 @@ def test_rejected_parameters_launch_nothing():
     import torch
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), case.out_init)
+
+
+def test_interleave_slabs_kernel():
+    """[world][M][N/world][tile] -> [M][N][tile], the step after an all-gather of slabs."""
+    import torch
+    from iree_b200 import ukernel as uk
+    world, M, N, tile = 4, 5, 12, 256
+    rng = np.random.default_rng(3)
+    gathered = rng.integers(-2**31, 2**31, size=(world, M, N // world, tile), dtype=np.int64)
+    gathered = gathered.astype(np.int32)
+    want = gathered.transpose(1, 0, 2, 3).reshape(M, N, tile)
+    g = torch.from_numpy(gathered).cuda()
+    out = torch.zeros(M * N * tile, dtype=torch.int32, device="cuda")
+    uk.interleave_slabs(g, out, M, N, tile, 4, world)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().reshape(M, N, tile), want)
