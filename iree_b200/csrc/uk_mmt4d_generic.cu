@@ -139,21 +139,36 @@ __global__ void __launch_bounds__(kGemvWarps * 32) mmt4d_gemv_s16u4_kernel(Gener
   const uint4* rhs = reinterpret_cast<const uint4*>(a.rhs + n1 * a.rhs_stride_b);
   const uint4* lhs = reinterpret_cast<const uint4*>(a.lhs + m * a.lhs_stride_b);
   int32_t acc[4] = {0, 0, 0, 0};
-  for (int64_t k = int64_t(warp) * 4 + kq; k < a.K; k += kGemvWarps * 4) {
-    const uint4 w = __ldg(rhs + k * 8 + ng);  // 4 n0 rows x 8 nibbles
-    const uint4 x = __ldg(lhs + k);           // 8 s16 of this k1
-    const uint32_t xs[4] = {x.x, x.y, x.z, x.w};
-    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+  constexpr int kUnroll = 4;  // independent 16-byte weight loads in flight per thread
+  constexpr int kStep = kGemvWarps * 4;
+  for (int64_t kb = int64_t(warp) * 4 + kq; kb < a.K; kb += kStep * kUnroll) {
+    uint4 wv[kUnroll], xv[kUnroll];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      int32_t s = 0;
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {  // byte h holds k0 = 2h (low nibble) and 2h+1 (high)
-        const uint32_t byte = (ws[r] >> (8 * h)) & 0xFFu;
-        const int32_t x0 = int16_t(xs[h] & 0xFFFFu), x1 = int16_t(xs[h] >> 16);
-        s += x0 * int32_t(byte & 0xFu) + x1 * int32_t(byte >> 4);
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t k = kb + int64_t(u) * kStep;
+      if (k < a.K) {
+        wv[u] = __ldg(rhs + k * 8 + ng);  // 4 n0 rows x 8 nibbles
+        xv[u] = __ldg(lhs + k);           // 8 s16 of this k1
+      } else {
+        wv[u] = make_uint4(0u, 0u, 0u, 0u);
+        xv[u] = make_uint4(0u, 0u, 0u, 0u);
       }
-      acc[r] += s;
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const uint32_t xs[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+      const uint32_t ws[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        int32_t s = 0;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {  // byte h holds k0 = 2h (low nibble) and 2h+1 (high)
+          const uint32_t byte = (ws[r] >> (8 * h)) & 0xFFu;
+          const int32_t x0 = int16_t(xs[h] & 0xFFFFu), x1 = int16_t(xs[h] >> 16);
+          s += x0 * int32_t(byte & 0xFu) + x1 * int32_t(byte >> 4);
+        }
+        acc[r] += s;
+      }
     }
   }
   // lanes with the same ng hold partial sums of the same 4 outputs

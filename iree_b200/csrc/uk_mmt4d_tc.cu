@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -50,6 +51,7 @@ struct OperandStage {
   int32_t kstep[3];   // coordinate = kb*kstep + tile*tstep + box*bstep
   int32_t tstep[3];
   int32_t bstep[3];
+  int32_t rstep[3];   // two-CTA kernel only: added once for the CTA of cluster rank 1
 };
 
 struct TcParams {
@@ -59,8 +61,10 @@ struct TcParams {
   uint32_t desc_hi_a, desc_hi_b;    // bits 32..63 of the shared-memory descriptors
   uint32_t desc_lbo_a, desc_lbo_b;  // leading byte offset >> 4
   uint32_t kadv_a, kadv_b;          // start-address advance per MMA along K, in 16-byte units
+  uint32_t kbox_units_a, kbox_units_b;  // 16-byte units between the K boxes of one stage
   uint32_t idesc;
-  int32_t mma_per_stage;
+  int32_t kboxes;       // K boxes per stage (1 or 2)
+  int32_t mma_per_box;  // tcgen05.mma per K box
   int32_t stage_bytes_a, stage_bytes_b;
   int32_t num_stages;
   int32_t num_kb;
@@ -71,6 +75,8 @@ struct TcParams {
   int64_t M1, N1;
   int32_t accumulate;
   int32_t out_is_int;
+  int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
+  uint32_t debug_flags;  // experiments only: 1 = no output stores, 2 = no TMEM reads, 4 = no TMA loads
   uint32_t* status;
 };
 
@@ -80,6 +86,21 @@ struct TcParams {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// One lane of a converged warp. The surrounding code stays warp-uniform, so descriptors,
+// coordinates and barrier addresses can live in uniform registers, which is what the TMA and
+// tcgen05 instructions take.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xFFFFFFFF;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -113,6 +134,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (*abort_flag || clock64() > deadline) return false;
   }
   return true;
+}
+
+// The same wait executed by a whole converged warp with one shared verdict.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag));
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -168,6 +194,78 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
 }
+// ---- two-CTA (cta_group::2) forms -------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory variable in the CTA of rank `rank` of this cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+// TMA load of one CTA of a pair; the completion bytes go to the mbarrier at `bar`, a
+// shared::cluster address that may belong to the peer CTA. No multicast.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                                 int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
+               : "memory");
+}
+template <bool IS_INT>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  if (IS_INT) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// Arrives on the mbarrier at the same shared-memory offset in every CTA of `cta_mask` once all
+// tcgen05.mma issued so far by this thread (for both CTAs of the pair) have completed.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+      "[%0], %1;" ::"r"(bar), "h"(cta_mask)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -200,6 +298,117 @@ enum : uint32_t {
   kStatusEpilogueTimeout = 1u << 2,
   kStatusDrainTimeout = 1u << 3,
 };
+
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t* r) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(r[0]),
+               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void ld_global_v8(const void* p, uint32_t (&r)[8]) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7])
+               : "l"(p)
+               : "memory");
+}
+
+// Epilogue of one accumulator tile for one warp: lanes own rows row0 .. row0+31 of the output
+// (row = m1*16 + m0), `chunks` groups of 16 columns starting at tile column n1_0. Each thread
+// moves one 64-byte row of a 16x16 output tile per chunk. All 32 lanes must call this.
+__device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0, int64_t row,
+                                              int64_t n1_0, int chunks) {
+  const int64_t m1 = row >> 4;
+  const int m0 = int(row & 15);
+  if (P.debug_flags & 2u) return;
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[16];
+    tmem_ld16(taddr0 + uint32_t(c * 16), r);
+    tmem_ld_wait();
+    const int64_t n1 = n1_0 + c;
+    if (m1 < P.M1 && n1 < P.N1 && !(P.debug_flags & 1u)) {
+      char* dst = P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4;
+      if (P.out_vec32) {
+        // 32-byte accesses: every store fills a whole 32-byte sector.
+        if (P.accumulate) {
+#pragma unroll
+          for (int v = 0; v < 2; ++v) {
+            uint32_t o[8];
+            ld_global_v8(dst + 32 * v, o);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              r[8 * v + j] = P.out_is_int
+                                 ? r[8 * v + j] + o[j]
+                                 : __float_as_uint(__uint_as_float(r[8 * v + j]) + __uint_as_float(o[j]));
+          }
+        }
+        st_global_v8(dst, &r[0]);
+        st_global_v8(dst + 32, &r[8]);
+      } else {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        if (P.accumulate) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint4 old = d4[v];
+            const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              r[4 * v + j] = P.out_is_int
+                                 ? r[4 * v + j] + o[j]
+                                 : __float_as_uint(__uint_as_float(r[4 * v + j]) + __uint_as_float(o[j]));
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          d4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+      }
+    }
+  }
+}
+
+// One stage's TMA loads for one operand. `c` holds the coordinates of box 0 for this k-block.
+template <bool PAIR>
+__device__ __forceinline__ void issue_operand_loads(const CUtensorMap* map, const OperandStage& st,
+                                                    uint32_t smem, uint32_t bar, const int (&c)[3]) {
+  for (int b = 0; b < st.nbox; ++b) {
+    const uint32_t dst = smem + uint32_t(b * st.box_bytes);
+    const int c0 = c[0] + b * st.bstep[0], c1 = c[1] + b * st.bstep[1], c2 = c[2] + b * st.bstep[2];
+    if (PAIR) tma_load_3d_pair(dst, map, bar, c0, c1, c2);
+    else tma_load_3d(dst, map, bar, c0, c1, c2);
+  }
+}
+
+// All tcgen05.mma of one stage. Everything but the two stage addresses is loop-invariant and
+// lives in registers of the single issuing thread.
+struct MmaIssue {
+  uint32_t lo_a, lo_b, hi_a, hi_b, kadv_a, kadv_b, kbox_a, kbox_b, idesc;
+  int kboxes, mma_per_box;
+};
+__device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
+  MmaIssue m;
+  m.lo_a = P.desc_lbo_a << 16; m.lo_b = P.desc_lbo_b << 16;
+  m.hi_a = P.desc_hi_a; m.hi_b = P.desc_hi_b;
+  m.kadv_a = P.kadv_a; m.kadv_b = P.kadv_b;
+  m.kbox_a = P.kbox_units_a; m.kbox_b = P.kbox_units_b;
+  m.idesc = P.idesc; m.kboxes = P.kboxes; m.mma_per_box = P.mma_per_box;
+  return m;
+}
+template <bool IS_INT, bool PAIR>
+__device__ __forceinline__ void issue_stage_mmas(const MmaIssue& m, uint32_t d_tmem, uint32_t a_units,
+                                                 uint32_t b_units, bool first_kblock) {
+  uint32_t acc = first_kblock ? 0u : 1u;
+  for (int kb = 0; kb < m.kboxes; ++kb) {
+    uint32_t au = a_units + uint32_t(kb) * m.kbox_a, bu = b_units + uint32_t(kb) * m.kbox_b;
+    for (int j = 0; j < m.mma_per_box; ++j) {
+      const uint64_t da = (uint64_t(m.hi_a) << 32) | uint64_t((au & 0x3FFFu) | m.lo_a);
+      const uint64_t db = (uint64_t(m.hi_b) << 32) | uint64_t((bu & 0x3FFFu) | m.lo_b);
+      if (PAIR) tc_mma_pair<IS_INT>(d_tmem, da, db, m.idesc, acc);
+      else tc_mma<IS_INT>(d_tmem, da, db, m.idesc, acc);
+      acc = 1u;
+      au += m.kadv_a;
+      bu += m.kadv_b;
+    }
+  }
+}
 
 // ---------------------------------------------------------------------------------------
 // the kernel
@@ -245,40 +454,45 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
-    if (lane == 0) {
+    {
       int stage = 0;
       uint32_t phase = 0;
       long long issued = 0;
       bool ok = true;
+      const OperandStage sa_st = P.sa, sb_st = P.sb;
+      const int num_kb = P.num_kb;
+      const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mt, nt;
         tile_coords(P, tile, &mt, &nt);
-        for (int kb = 0; kb < P.num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
-            atomicOr(P.status, kStatusProducerTimeout);
+        int ca[3] = {mt * sa_st.tstep[0], mt * sa_st.tstep[1], mt * sa_st.tstep[2]};
+        int cb[3] = {nt * sb_st.tstep[0], nt * sb_st.tstep[1], nt * sb_st.tstep[2]};
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_warp(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
+            if (lane == 0) atomicOr(P.status, kStatusProducerTimeout);
             abort_flag = 1;
             ok = false;
             break;
           }
           const uint32_t bar = smem_u32(&full_bar[stage]);
-          mbar_expect_tx(bar, stage_bytes);
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
-          const uint32_t sb = sa + uint32_t(P.stage_bytes_a);
-          for (int b = 0; b < P.sa.nbox; ++b)
-            tma_load_3d(sa + uint32_t(b * P.sa.box_bytes), &P.map_a, bar,
-                        kb * P.sa.kstep[0] + mt * P.sa.tstep[0] + b * P.sa.bstep[0],
-                        kb * P.sa.kstep[1] + mt * P.sa.tstep[1] + b * P.sa.bstep[1],
-                        kb * P.sa.kstep[2] + mt * P.sa.tstep[2] + b * P.sa.bstep[2]);
-          for (int b = 0; b < P.sb.nbox; ++b)
-            tma_load_3d(sb + uint32_t(b * P.sb.box_bytes), &P.map_b, bar,
-                        kb * P.sb.kstep[0] + nt * P.sb.tstep[0] + b * P.sb.bstep[0],
-                        kb * P.sb.kstep[1] + nt * P.sb.tstep[1] + b * P.sb.bstep[1],
-                        kb * P.sb.kstep[2] + nt * P.sb.tstep[2] + b * P.sb.bstep[2]);
+          if (elect_one()) {
+            if (P.debug_flags & 4u) {
+              mbar_arrive(bar);
+            } else {
+              mbar_expect_tx(bar, stage_bytes);
+              issue_operand_loads<false>(&P.map_a, sa_st, sa, bar, ca);
+              issue_operand_loads<false>(&P.map_b, sb_st, sa + a_bytes, bar, cb);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 3; ++i) { ca[i] += sa_st.kstep[i]; cb[i] += sb_st.kstep[i]; }
           ++issued;
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
-      if (!ok || *abortp) {
+      if ((!ok || *abortp) && lane == 0) {
         // Aborting: let this CTA's own copies land before its shared memory is released.
         const long long n = issued < S ? issued : S;
         for (long long i = 0; i < n; ++i) {
@@ -294,41 +508,41 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
+    {
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
+      const MmaIssue mi = make_mma_issue(P);
+      const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
+      const int num_kb = P.num_kb;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
-          atomicOr(P.status, kStatusMmaTimeout);
+        if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
+          if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
           abort_flag = 1;
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn);
-        for (int kb = 0; kb < P.num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&full_bar[stage]), phase, abortp)) {
-            atomicOr(P.status, kStatusMmaTimeout);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
+            if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
             abort_flag = 1;
             ok = false;
             break;
           }
           tc_fence_after();
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
-          const uint32_t sb = sa + uint32_t(P.stage_bytes_a);
-          const uint32_t a_units = sa >> 4, b_units = sb >> 4;
-          for (int j = 0; j < P.mma_per_stage; ++j) {
-            const uint64_t da = make_desc(a_units + uint32_t(j) * P.kadv_a, P.desc_lbo_a, P.desc_hi_a);
-            const uint64_t db = make_desc(b_units + uint32_t(j) * P.kadv_b, P.desc_lbo_b, P.desc_hi_b);
-            tc_mma<IS_INT>(d_tmem, da, db, P.idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          if (elect_one()) {
+            issue_stage_mmas<IS_INT, false>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs finish
+            if (kb == num_kb - 1) tc_commit(smem_u32(&tmem_full_bar[buf]));  // accumulator complete
           }
-          tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs finish
+          __syncwarp();
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(smem_u32(&tmem_full_bar[buf]));  // accumulator complete
         if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
       }
     }
@@ -392,6 +606,199 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// the two-CTA kernel (cta_group::2)
+// ---------------------------------------------------------------------------------------
+// A cluster of two CTAs on neighbouring SMs works on one 256 x BN tile. Each CTA stages its own
+// 128 rows of the LHS and its own half (BN/2 rows) of the RHS, so a CTA moves 2/3 of the bytes
+// per k-block that the one-CTA kernel moves for the same math; one tcgen05.mma issued by the
+// leader (cluster rank 0) drives both SMs' tensor cores, reads the RHS halves from both CTAs'
+// shared memory and accumulates 128 rows x BN columns in each CTA's TMEM. Barriers:
+//   full[s]       leader's only; armed by the leader's producer with the bytes of both CTAs;
+//                 both CTAs' TMA loads complete on it (the peer through a mapped address)
+//   empty[s]      one per CTA; the leader's tcgen05.commit arrives on both (multicast commit)
+//   tmem_full[b]  one per CTA; multicast commit after the last k-block of a tile
+//   tmem_empty[b] leader's only, 8 arrivals: the four epilogue warps of each CTA
+// No TMA load uses cluster multicast.
+template <bool IS_INT>
+__global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const uint32_t stage_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t stage_bytes = uint32_t(P.stage_bytes_a + P.stage_bytes_b);  // per CTA
+  const int S = P.num_stages;
+  const int num_tiles = P.m_tiles * P.n_tiles;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 8);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&tmem_slot), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything signals them remotely
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------------------
+    {
+      int stage = 0;
+      uint32_t phase = 0;
+      long long issued = 0;
+      bool ok = true;
+      const int r = int(rank);
+      const OperandStage sa_st = P.sa, sb_st = P.sb;
+      const int num_kb = P.num_kb;
+      const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int mt, nt;
+        tile_coords(P, tile, &mt, &nt);
+        int ca[3], cb[3];
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+          ca[i] = mt * sa_st.tstep[i] + r * sa_st.rstep[i];
+          cb[i] = nt * sb_st.tstep[i] + r * sb_st.rstep[i];
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_warp(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
+            if (lane == 0) atomicOr(P.status, kStatusProducerTimeout);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t own_bar = smem_u32(&full_bar[stage]);
+          const uint32_t bar = mapa_shared(own_bar, 0);
+          const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
+          if (elect_one()) {
+            if (P.debug_flags & 4u) {
+              if (leader) mbar_arrive(own_bar);
+            } else {
+              if (leader) mbar_expect_tx(own_bar, 2u * stage_bytes);
+              issue_operand_loads<true>(&P.map_a, sa_st, sa, bar, ca);
+              issue_operand_loads<true>(&P.map_b, sb_st, sa + a_bytes, bar, cb);
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 3; ++i) { ca[i] += sa_st.kstep[i]; cb[i] += sb_st.kstep[i]; }
+          ++issued;
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if ((!ok || *abortp) && leader && lane == 0) {
+        // Aborting: the leader's full barriers count the copies of both CTAs; let them land
+        // before either CTA's shared memory is released (the cluster barrier below orders the
+        // peer's exit after this).
+        const long long n = issued < S ? issued : S;
+        for (long long i = 0; i < n; ++i) {
+          const long long idx = issued - 1 - i;
+          const int s = int(idx % S);
+          const uint32_t par = uint32_t((idx / S) & 1);
+          const long long deadline = clock64() + kWaitCycles;
+          while (!mbar_try_wait(smem_u32(&full_bar[s]), par)) {
+            if (clock64() > deadline) { atomicOr(P.status, kStatusDrainTimeout); break; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader only) -------------------------------
+    if (leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool ok = true;
+      const MmaIssue mi = make_mma_issue(P);
+      const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
+      const int num_kb = P.num_kb;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
+          if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
+            if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
+          if (elect_one()) {
+            issue_stage_mmas<IS_INT, true>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            tc_commit_pair(smem_u32(&empty_bar[stage]), 3);  // both CTAs may refill the stage
+            if (kb == num_kb - 1) tc_commit_pair(smem_u32(&tmem_full_bar[buf]), 3);  // accumulators done
+          }
+          __syncwarp();
+          if (++stage == S) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (both CTAs) -------------------------------
+    const int q = warp & 3;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    const int chunks = P.bn >> 4;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      int mt, nt;
+      tile_coords(P, tile, &mt, &nt);
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp))) {
+        if (lane == 0) atomicOr(P.status, kStatusEpilogueTimeout);
+        abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = int64_t(mt) * 256 + int64_t(rank) * 128 + q * 32 + lane;
+      const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
+      epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[buf]), 0));
+      if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees TMEM or exits while its peer may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
   }
 }
 
@@ -497,6 +904,14 @@ int launch_retile(const char* src, int64_t src_stride_b, char* dst, int64_t dst_
 // host side: tensor maps, descriptors, launch
 // ---------------------------------------------------------------------------------------
 
+// Experiment knobs, honoured only when IREE_UK_B200_DEBUG is set in the environment.
+int debug_int(const char* name, int fallback) {
+  static const bool enabled = std::getenv("IREE_UK_B200_DEBUG") != nullptr;
+  if (!enabled) return fallback;
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -532,9 +947,47 @@ bool tc_type_info(uint32_t flags, TypeInfo* ti) {
   }
 }
 
-uint32_t make_idesc(const TypeInfo& ti, int n, bool mn_major) {
+uint32_t make_idesc(const TypeInfo& ti, int n, bool mn_major, int m = BM) {
   return (ti.cfmt << 4) | (ti.fmt << 7) | (ti.fmt << 10) | (uint32_t(mn_major) << 15) |
-         (uint32_t(mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+         (uint32_t(mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// Co-resident 2-CTA clusters of the pair kernel on the current device (0 on failure).
+template <bool IS_INT>
+int max_pair_clusters(size_t smem) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, mmt4d_tc2_kernel<IS_INT>, &cfg) != cudaSuccess) return 0;
+  return n;
+}
+
+// Accumulator width for the pair kernel: among the multiples of 32 columns up to 256, the one
+// that minimises (waves of 256 x bn tiles over `clusters` pairs) x bn, i.e. the estimated time.
+int pick_bn_pair(int64_t M1, int64_t N1, int clusters) {
+  {
+    const int bn = debug_int("IREE_UK_B200_DEBUG_PAIR_BN", 0);
+    if (bn >= 32 && bn <= 256 && bn % 32 == 0) return bn;
+  }
+  const int64_t m_tiles = (M1 * 16 + 255) / 256, cols = N1 * 16;
+  int best = 256;
+  int64_t best_cost = -1;
+  for (int bn = 256; bn >= 128; bn -= 32) {
+    const int64_t tiles = m_tiles * ((cols + bn - 1) / bn);
+    const int64_t waves = (tiles + clusters - 1) / clusters;
+    const int64_t cost = waves * (bn + 32);  // tile time: the MMAs plus a small fixed part
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
 }
 
 // Upper word of a shared-memory matrix descriptor: stride byte offset, version 1
@@ -546,6 +999,10 @@ uint32_t desc_hi(uint32_t sbo_bytes, uint32_t layout) {
 int64_t round_up(int64_t v, int64_t q) { return (v + q - 1) / q * q; }
 
 int pick_bn(int64_t M1, int64_t N1) {
+  {
+    const int bn = debug_int("IREE_UK_B200_DEBUG_BN", 0);
+    if (bn >= 16 && bn <= 256 && bn % 16 == 0) return bn;
+  }
   const int64_t m_tiles = (M1 + 7) / 8;
   for (int bn : {256, 128, 64}) {
     const int64_t n_tiles = (N1 * 16 + bn - 1) / bn;
@@ -596,6 +1053,15 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
   return size_t(round_up(p->M * 16 * pitch, 1024) + round_up(p->N * 16 * pitch, 1024));
 }
 
+namespace {
+// The two-CTA kernel works on 256-row tiles with at most 74 CTA pairs in flight; it pays once
+// there are enough 256 x 128 tiles to occupy every pair.
+bool pair_kernel_pays(const iree_uk_mmt4d_params_t* p) {
+  const int64_t m_tiles = (p->M * 16 + 255) / 256, n_tiles = (p->N * 16 + 127) / 128;
+  return p->M * 16 >= 256 && p->N * 16 >= 128 && m_tiles * n_tiles >= 74;
+}
+}  // namespace
+
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream) {
   TypeInfo ti;
@@ -607,14 +1073,22 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   std::memset(&P, 0, sizeof P);
   KernelTiming& timing = kernel_timing();
   if (timing.enabled) cudaEventRecord(timing.ev[0], stream);
-  const int bn = pick_bn(p->M, p->N);
+  int bn = pick_bn(p->M, p->N);
+  bool pair = false;
+  int pair_clusters = 0;
   const int64_t kelems = p->K * p->K0;
   char* lhs = const_cast<char*>(static_cast<const char*>(p->lhs_buffer)) + p->lhs_offset * ti.es;
   char* rhs = const_cast<char*>(static_cast<const char*>(p->rhs_buffer)) + p->rhs_offset * ti.es;
-  const int kblk_elems = 128 / ti.es;  // one 128-byte swizzle row of K per stage
+  const int kblk_elems = 128 / ti.es;  // one 128-byte swizzle row of K per TMA box
+  // Variant 0 = automatic: the two-CTA kernel when the problem gives every CTA pair work,
+  // the one-CTA kernel otherwise. 5 / 6 force the two-CTA / one-CTA kernel.
+  if (variant == 0) variant = pair_kernel_pays(p) ? 5 : 6;
+  // K boxes per stage: two for the two-CTA kernel (64 KB stages, half the barrier round trips
+  // per MMA), one for the one-CTA kernel (its stage is already 48 KB).
+  int kboxes = debug_int("IREE_UK_B200_DEBUG_KBOXES", variant == 5 ? 2 : 1) == 2 ? 2 : 1;
   const int mma_k = 32 / ti.es;        // K per tcgen05.mma: 16 (16-bit) or 32 (8-bit)
 
-  if (variant == 0) {
+  if (variant == 6) {
     const size_t need = mmt4d_tc_workspace_size(p);
     if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
     if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
@@ -635,16 +1109,61 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     if (!encode_map(&P.map_a, ti.tm_type, ws_a, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !encode_map(&P.map_b, ti.tm_type, ws_b, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
       return IREE_UK_B200_CUDA_ERROR;
-    P.sa = {1, BM * 128, {kblk_elems, 0, 0}, {0, BM, 0}, {0, 0, 0}};
-    P.sb = {1, bn * 128, {kblk_elems, 0, 0}, {0, bn, 0}, {0, 0, 0}};
+    P.sa = {kboxes, BM * 128, {kboxes * kblk_elems, 0, 0}, {0, BM, 0}, {kblk_elems, 0, 0}};
+    P.sb = {kboxes, bn * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}};
     P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
     P.desc_lbo_a = P.desc_lbo_b = 1;
     P.kadv_a = P.kadv_b = 2;  // 32 bytes of K per MMA inside the 128-byte swizzle row
+    P.kbox_units_a = uint32_t(BM * 128) >> 4;
+    P.kbox_units_b = uint32_t(bn * 128) >> 4;
     P.idesc = make_idesc(ti, bn, false);
-    P.mma_per_stage = 4;
-    P.stage_bytes_a = BM * 128;
-    P.stage_bytes_b = bn * 128;
-    P.num_kb = int((kelems + kblk_elems - 1) / kblk_elems);
+    P.kboxes = kboxes;
+    P.mma_per_box = 4;
+    P.stage_bytes_a = kboxes * BM * 128;
+    P.stage_bytes_b = kboxes * bn * 128;
+    P.num_kb = int((kelems + kboxes * kblk_elems - 1) / (kboxes * kblk_elems));
+  } else if (variant == 5) {
+    // Two-CTA kernel on the re-tiled K-major scratch: 256 x bn tile per CTA pair.
+    const size_t need = mmt4d_tc_workspace_size(p);
+    if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+    if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+    const size_t smem_probe = size_t(6) * (BM * 128 + 128 * 128) + 1024;
+    if (ti.is_int) cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
+    else cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
+    pair_clusters = ti.is_int ? max_pair_clusters<true>(smem_probe) : max_pair_clusters<false>(smem_probe);
+    if (pair_clusters < 1) return IREE_UK_B200_CUDA_ERROR;
+    bn = pick_bn_pair(p->M, p->N, pair_clusters);
+    const int64_t pitch = round_up(kelems * ti.es, 128);
+    char* ws_a = static_cast<char*>(ws);
+    char* ws_b = ws_a + round_up(p->M * 16 * pitch, 1024);
+    const int G = p->K0 * ti.es;
+    int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, pitch, p->M, p->K, G, stream);
+    if (rc) return rc;
+    rc = launch_retile(rhs, p->rhs_stride0 * ti.es, ws_b, pitch, p->N, p->K, G, stream);
+    if (rc) return rc;
+    const uint64_t da[3] = {uint64_t(kelems), uint64_t(p->M * 16), 1};
+    const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), 1};
+    const uint64_t sa[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->M * 16)};
+    const uint64_t sb[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->N * 16)};
+    const uint32_t ba[3] = {uint32_t(kblk_elems), BM, 1};
+    const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(bn / 2), 1};
+    if (!encode_map(&P.map_a, ti.tm_type, ws_a, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_map(&P.map_b, ti.tm_type, ws_b, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+      return IREE_UK_B200_CUDA_ERROR;
+    P.sa = {kboxes, BM * 128, {kboxes * kblk_elems, 0, 0}, {0, 2 * BM, 0}, {kblk_elems, 0, 0}, {0, BM, 0}};
+    P.sb = {kboxes, (bn / 2) * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}, {0, bn / 2, 0}};
+    P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
+    P.desc_lbo_a = P.desc_lbo_b = 1;
+    P.kadv_a = P.kadv_b = 2;
+    P.kbox_units_a = uint32_t(BM * 128) >> 4;
+    P.kbox_units_b = uint32_t((bn / 2) * 128) >> 4;
+    P.idesc = make_idesc(ti, bn, false, 2 * BM);
+    P.kboxes = kboxes;
+    P.mma_per_box = 4;
+    P.stage_bytes_a = kboxes * BM * 128;
+    P.stage_bytes_b = kboxes * (bn / 2) * 128;
+    P.num_kb = int((kelems + kboxes * kblk_elems - 1) / (kboxes * kblk_elems));
+    pair = true;
   } else {
     // MN-major, straight from a K0 = 1 16-bit operand (experimental variants 1..4).
     if (ti.es != 2 || p->K0 != 1 || variant < 1 || variant > 4) return IREE_UK_B200_UNSUPPORTED;
@@ -689,21 +1208,25 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
       P.stage_bytes_b = bn * kblk * 2;
     }
     P.idesc = make_idesc(ti, bn, true);
-    P.mma_per_stage = kblk / mma_k;
+    P.kboxes = 1;
+    P.mma_per_box = kblk / mma_k;
     P.num_kb = int((p->K + kblk - 1) / kblk);
   }
 
+  const int tile_m = pair ? 2 * BM : BM;
   P.bn = bn;
-  P.m_tiles = int((p->M * 16 + BM - 1) / BM);
+  P.m_tiles = int((p->M * 16 + tile_m - 1) / tile_m);
   P.n_tiles = int((p->N * 16 + bn - 1) / bn);
-  P.group_m = std::min(P.m_tiles, 16);
+  P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
   P.out = static_cast<char*>(p->out_buffer) + p->out_offset * 4;
   P.out_stride0 = p->out_stride0;
   P.M1 = p->M;
   P.N1 = p->N;
   P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
   P.out_is_int = ti.is_int ? 1 : 0;
+  P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * 4) % 32 == 0) ? 1 : 0;
   P.status = status;
+  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
 
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   const int smem_budget = 200 * 1024;
@@ -713,17 +1236,43 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = std::min(P.m_tiles * P.n_tiles, sms);
   cudaError_t e;
   if (timing.enabled) cudaEventRecord(timing.ev[1], stream);
-  if (ti.is_int) {
-    e = cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (pair) {
+    const int clusters = std::min(P.m_tiles * P.n_tiles, pair_clusters);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(2 * clusters), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (ti.is_int) {
+      e = cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<true>, P);
+    } else {
+      e = cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<false>, P);
+    }
     if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-    mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
   } else {
-    e = cudaFuncSetAttribute(mmt4d_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-    mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
+    const int grid = std::min(P.m_tiles * P.n_tiles, sms);
+    if (ti.is_int) {
+      e = cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
+    } else {
+      e = cudaFuncSetAttribute(mmt4d_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
+    }
   }
   if (timing.enabled) {
     cudaEventRecord(timing.ev[2], stream);

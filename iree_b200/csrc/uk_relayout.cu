@@ -7,7 +7,8 @@
 //    both the matrix side (row segments) and the tiled side (runs of whole tiles) are
 //    accessed as long contiguous runs with 16-byte vector instructions where alignment
 //    allows. The rectangle is kept in shared memory in matrix form [R0*T0 rows][R1*T1 cols]
-//    with an odd pitch (in 32-bit words) so that walking a column is bank-conflict free.
+//    with a 16-byte-aligned row pitch of 4 (mod 8) words. The tile shapes that carry real
+//    traffic get constant-shape instantiations whose index arithmetic folds to shifts.
 //
 // Semantics follow iree_uk_pack_p / iree_uk_unpack_p (ukernel/pack.c:254-322,
 // ukernel/unpack.c:190-257): opaque elements of 1, 2 or 4 bytes; padding writes the low
@@ -30,7 +31,7 @@ struct RelayoutArgs {
   uint32_t pad;                      // pack only: low bytes are the fill pattern
   // staged kernels only
   int32_t R0, R1;        // tiles per block along dim 0 / dim 1
-  int32_t pitch_words;   // shared-memory row pitch in 32-bit words (odd)
+  int32_t pitch_words;   // shared-memory row pitch in 32-bit words
   int32_t tile_fast_r0;  // 1: consecutive tiles of the tiled side walk dim 0 (outer transposed)
   int32_t vec_mat;       // 1: 16-byte vector access to the matrix side is legal
   int32_t vec_tiled;     // 1: 16-byte vector access to the tiled side is legal
@@ -81,204 +82,184 @@ __device__ __forceinline__ uint32_t splat_pad(uint32_t pad, int es) {
   return pad;
 }
 
-template <int ES>
-__global__ void __launch_bounds__(256) pack_staged_kernel(RelayoutArgs a) {
-  using E = typename ElemT<ES>::type;
-  extern __shared__ uint32_t smem_w[];
-  char* smem_b = reinterpret_cast<char*>(smem_w);
-  constexpr int NV = 16 / ES;  // elements per 16-byte vector
-
-  const int64_t b0 = blockIdx.x / a.nblk1, b1 = blockIdx.x - b0 * a.nblk1;
-  const int64_t tile0_base = b0 * a.R0, tile1_base = b1 * a.R1;
-  const int r0n = int(min(int64_t(a.R0), a.outer0 - tile0_base));  // tiles in this block
-  const int r1n = int(min(int64_t(a.R1), a.outer1 - tile1_base));
-  const int rows = r0n * a.T0, cols = r1n * a.T1;
-  const int64_t row_base = tile0_base * a.T0, col_base = tile1_base * a.T1;
-  const int pitch_b = a.pitch_words * 4;
-  const E padv = E(a.pad);
-
-  // ---- phase 1: matrix rows -> shared memory, padding filled in ----
-  if (a.vec_mat && (cols % NV) == 0) {
-    const int vpr = cols / NV;
-    const int nvec = rows * vpr;
-    const uint32_t padw = splat_pad(a.pad, ES);
-    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
-      const int r = vi / vpr, cv = vi - r * vpr;
-      const int64_t gi0 = row_base + r, gi1 = col_base + int64_t(cv) * NV;
-      uint32_t* sw = smem_w + r * a.pitch_words + cv * 4;
-      if (gi0 < a.mat_size0 && gi1 + NV <= a.mat_size1) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4*>(
-            a.src + (gi0 * a.mat_stride0 + gi1) * ES));
-        sw[0] = v.x; sw[1] = v.y; sw[2] = v.z; sw[3] = v.w;
-      } else if (gi0 >= a.mat_size0 || gi1 >= a.mat_size1) {
-        sw[0] = padw; sw[1] = padw; sw[2] = padw; sw[3] = padw;
-      } else {  // vector straddles the right edge
-        E* se = reinterpret_cast<E*>(sw);
-        for (int j = 0; j < NV; ++j)
-          se[j] = (gi1 + j < a.mat_size1)
-                      ? reinterpret_cast<const E*>(a.src)[gi0 * a.mat_stride0 + gi1 + j]
-                      : padv;
-      }
-    }
-  } else {
-    const int nel = rows * cols;
-    for (int ei = threadIdx.x; ei < nel; ei += blockDim.x) {
-      const int r = ei / cols, c = ei - r * cols;
-      const int64_t gi0 = row_base + r, gi1 = col_base + c;
-      E v = padv;
-      if (gi0 < a.mat_size0 && gi1 < a.mat_size1)
-        v = reinterpret_cast<const E*>(a.src)[gi0 * a.mat_stride0 + gi1 * a.mat_stride1];
-      *reinterpret_cast<E*>(smem_b + r * pitch_b + c * ES) = v;
-    }
-  }
-  __syncthreads();
-
-  // ---- phase 2: shared memory -> whole tiles, consecutive threads on consecutive bytes ----
-  const int tile_elems = a.T0 * a.T1;
-  const int ntiles = r0n * r1n;
-  // Inside a tile, the element with the unit stride is the "fast" one.
-  const bool fast_is_t1 = (a.inner_s1 == 1);
-  const int fastN = fast_is_t1 ? a.T1 : a.T0;  // extent of the unit-stride index
-  if (a.vec_tiled && (tile_elems % NV) == 0) {
-    const int tvec = tile_elems / NV;
-    const int nvec = ntiles * tvec;
-    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
-      const int tl = vi / tvec, v = vi - tl * tvec;
-      int r0, r1;
-      if (a.tile_fast_r0) { r1 = tl / r0n; r0 = tl - r1 * r0n; }
-      else { r0 = tl / r1n; r1 = tl - r0 * r1n; }
-      int e = v * NV;
-      int slow = e / fastN, fast = e - slow * fastN;
-      E vals[NV];
-#pragma unroll
-      for (int j = 0; j < NV; ++j) {
-        const int t0 = fast_is_t1 ? slow : fast, t1 = fast_is_t1 ? fast : slow;
-        vals[j] = *reinterpret_cast<const E*>(smem_b + (r0 * a.T0 + t0) * pitch_b +
-                                              (r1 * a.T1 + t1) * ES);
-        if (++fast == fastN) { fast = 0; ++slow; }
-      }
-      const int64_t te = (tile0_base + r0) * a.tiled_stride_o0 +
-                         (tile1_base + r1) * a.tiled_stride_o1 + e;
-      uint4 out;
-      if (ES == 4) {
-        out = make_uint4(vals[0], vals[1], vals[2], vals[3]);
-      } else {
-        uint32_t w[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t x = 0;
-#pragma unroll
-          for (int j = 0; j < 4 / ES; ++j) x |= uint32_t(vals[q * (4 / ES) + j]) << (8 * ES * j);
-          w[q] = x;
-        }
-        out = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-      *reinterpret_cast<uint4*>(a.dst + te * ES) = out;
-    }
-  } else {
-    const int nel = ntiles * tile_elems;
-    for (int ei = threadIdx.x; ei < nel; ei += blockDim.x) {
-      const int tl = ei / tile_elems, e = ei - tl * tile_elems;
-      int r0, r1;
-      if (a.tile_fast_r0) { r1 = tl / r0n; r0 = tl - r1 * r0n; }
-      else { r0 = tl / r1n; r1 = tl - r0 * r1n; }
-      const int slow = e / fastN, fast = e - slow * fastN;
-      const int t0 = fast_is_t1 ? slow : fast, t1 = fast_is_t1 ? fast : slow;
-      const E v = *reinterpret_cast<const E*>(smem_b + (r0 * a.T0 + t0) * pitch_b +
-                                              (r1 * a.T1 + t1) * ES);
-      const int64_t te = (tile0_base + r0) * a.tiled_stride_o0 +
-                         (tile1_base + r1) * a.tiled_stride_o1 + e;
-      reinterpret_cast<E*>(a.dst)[te] = v;
-    }
-  }
+// Shared-memory row pitch in 32-bit words for `cols_bytes` of payload: a multiple of 4 words
+// (rows stay 16-byte aligned for 128-bit shared-memory accesses) that is 4 modulo 8, so that
+// walking down a column touches 8 different bank groups before wrapping.
+__host__ __device__ constexpr int staged_pitch_words(int cols_bytes) {
+  int p = ((cols_bytes + 15) / 16) * 4;
+  return (p % 8 == 0) ? p + 4 : p;
 }
 
-template <int ES>
-__global__ void __launch_bounds__(256) unpack_staged_kernel(RelayoutArgs a) {
+// Compile-time shape of a staged kernel. kSpec = false: every quantity is read from the
+// arguments (any shape). kSpec = true: the tile and block shape are constants, the host has
+// checked that every block is full and that both sides allow 16-byte vectors, and index
+// arithmetic folds to shifts.
+struct RuntimeShape {
+  static constexpr bool kSpec = false;
+  static constexpr int T0 = 0, T1 = 0, R0 = 0, R1 = 0;
+  static constexpr bool kFastT1 = false, kTileFastR0 = false;
+};
+template <int T0_, int T1_, int R0_, int R1_, bool FAST_T1, bool TILE_FAST_R0>
+struct FixedShape {
+  static constexpr bool kSpec = true;
+  static constexpr int T0 = T0_, T1 = T1_, R0 = R0_, R1 = R1_;
+  static constexpr bool kFastT1 = FAST_T1, kTileFastR0 = TILE_FAST_R0;
+};
+
+template <int ES, bool IS_PACK, class Shape>
+__global__ void __launch_bounds__(256) relayout_staged_kernel(RelayoutArgs a) {
   using E = typename ElemT<ES>::type;
-  extern __shared__ uint32_t smem_w[];
+  extern __shared__ __align__(16) uint32_t smem_w[];
   char* smem_b = reinterpret_cast<char*>(smem_w);
-  constexpr int NV = 16 / ES;
+  constexpr int NV = 16 / ES;  // elements per 16-byte vector
+  constexpr bool kSpec = Shape::kSpec;
 
-  const int64_t b0 = blockIdx.x / a.nblk1, b1 = blockIdx.x - b0 * a.nblk1;
-  const int64_t tile0_base = b0 * a.R0, tile1_base = b1 * a.R1;
-  const int r0n = int(min(int64_t(a.R0), a.outer0 - tile0_base));
-  const int r1n = int(min(int64_t(a.R1), a.outer1 - tile1_base));
-  const int rows = r0n * a.T0, cols = r1n * a.T1;
-  const int64_t row_base = tile0_base * a.T0, col_base = tile1_base * a.T1;
-  const int pitch_b = a.pitch_words * 4;
-
-  // ---- phase 1: whole tiles -> shared memory (matrix form) ----
-  const int tile_elems = a.T0 * a.T1;
+  const int T0 = kSpec ? Shape::T0 : a.T0, T1 = kSpec ? Shape::T1 : a.T1;
+  const int R0 = kSpec ? Shape::R0 : a.R0, R1 = kSpec ? Shape::R1 : a.R1;
+  const bool fast_is_t1 = kSpec ? Shape::kFastT1 : (a.inner_s1 == 1);
+  const bool tile_fast_r0 = kSpec ? Shape::kTileFastR0 : (a.tile_fast_r0 != 0);
+  const unsigned nblk1 = unsigned(a.nblk1);
+  const unsigned b0 = blockIdx.x / nblk1, b1 = blockIdx.x - b0 * nblk1;
+  const int64_t tile0_base = int64_t(b0) * R0, tile1_base = int64_t(b1) * R1;
+  const int r0n = kSpec ? R0 : int(min(int64_t(R0), a.outer0 - tile0_base));  // tiles here
+  const int r1n = kSpec ? R1 : int(min(int64_t(R1), a.outer1 - tile1_base));
+  const int rows = r0n * T0, cols = r1n * T1;
+  const int64_t row_base = tile0_base * T0, col_base = tile1_base * T1;
+  const int pitch_words = kSpec ? staged_pitch_words(Shape::R1 * Shape::T1 * ES) : a.pitch_words;
+  const int pitch_b = pitch_words * 4;
+  const int tile_elems = T0 * T1;
   const int ntiles = r0n * r1n;
-  const bool fast_is_t1 = (a.inner_s1 == 1);
-  const int fastN = fast_is_t1 ? a.T1 : a.T0;
-  if (a.vec_tiled && (tile_elems % NV) == 0) {
-    const int tvec = tile_elems / NV;
-    const int nvec = ntiles * tvec;
-    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
-      const int tl = vi / tvec, v = vi - tl * tvec;
-      int r0, r1;
-      if (a.tile_fast_r0) { r1 = tl / r0n; r0 = tl - r1 * r0n; }
-      else { r0 = tl / r1n; r1 = tl - r0 * r1n; }
-      const int e = v * NV;
-      const int64_t te = (tile0_base + r0) * a.tiled_stride_o0 +
-                         (tile1_base + r1) * a.tiled_stride_o1 + e;
-      const uint4 in = __ldg(reinterpret_cast<const uint4*>(a.src + te * ES));
-      const uint32_t w[4] = {in.x, in.y, in.z, in.w};
-      int slow = e / fastN, fast = e - slow * fastN;
-#pragma unroll
-      for (int j = 0; j < NV; ++j) {
-        const int t0 = fast_is_t1 ? slow : fast, t1 = fast_is_t1 ? fast : slow;
-        const E val = E(w[(j * ES) / 4] >> (8 * ((j * ES) % 4)));
-        *reinterpret_cast<E*>(smem_b + (r0 * a.T0 + t0) * pitch_b + (r1 * a.T1 + t1) * ES) = val;
-        if (++fast == fastN) { fast = 0; ++slow; }
-      }
-    }
-  } else {
-    const int nel = ntiles * tile_elems;
-    for (int ei = threadIdx.x; ei < nel; ei += blockDim.x) {
-      const int tl = ei / tile_elems, e = ei - tl * tile_elems;
-      int r0, r1;
-      if (a.tile_fast_r0) { r1 = tl / r0n; r0 = tl - r1 * r0n; }
-      else { r0 = tl / r1n; r1 = tl - r0 * r1n; }
-      const int slow = e / fastN, fast = e - slow * fastN;
-      const int t0 = fast_is_t1 ? slow : fast, t1 = fast_is_t1 ? fast : slow;
-      const int64_t te = (tile0_base + r0) * a.tiled_stride_o0 +
-                         (tile1_base + r1) * a.tiled_stride_o1 + e;
-      *reinterpret_cast<E*>(smem_b + (r0 * a.T0 + t0) * pitch_b + (r1 * a.T1 + t1) * ES) =
-          reinterpret_cast<const E*>(a.src)[te];
-    }
-  }
-  __syncthreads();
+  const int fastN = fast_is_t1 ? T1 : T0;  // extent of the unit-stride index inside a tile
+  const bool vec_mat = kSpec || (a.vec_mat && (cols % NV) == 0);
+  const bool vec_tiled = kSpec || (a.vec_tiled && (tile_elems % NV) == 0);
+  // A 16-byte vector of a tile is also contiguous in the staged (matrix-form) rectangle when
+  // the tile's unit-stride index runs along the matrix row and a run is whole vectors.
+  const bool row_vectors = fast_is_t1 && ((T1 * ES) % 16 == 0);
+  const E padv = E(a.pad);
 
-  // ---- phase 2: shared memory -> matrix rows; nothing outside mat_size0 x mat_size1 ----
-  if (a.vec_mat && (cols % NV) == 0) {
-    const int vpr = cols / NV;
-    const int nvec = rows * vpr;
-    for (int vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
-      const int r = vi / vpr, cv = vi - r * vpr;
-      const int64_t gi0 = row_base + r, gi1 = col_base + int64_t(cv) * NV;
-      if (gi0 >= a.mat_size0 || gi1 >= a.mat_size1) continue;
-      const uint32_t* sw = smem_w + r * a.pitch_words + cv * 4;
-      if (gi1 + NV <= a.mat_size1) {
-        *reinterpret_cast<uint4*>(a.dst + (gi0 * a.mat_stride0 + gi1) * ES) =
-            make_uint4(sw[0], sw[1], sw[2], sw[3]);
-      } else {
-        const E* se = reinterpret_cast<const E*>(sw);
-        for (int j = 0; j < NV && gi1 + j < a.mat_size1; ++j)
-          reinterpret_cast<E*>(a.dst)[gi0 * a.mat_stride0 + gi1 + j] = se[j];
+  const char* mat_src = a.src;  // used when IS_PACK
+  char* mat_dst = a.dst;        // used when !IS_PACK
+  const char* tiled_src = a.src;
+  char* tiled_dst = a.dst;
+
+  // tile index inside the block -> (r0, r1); consecutive tiles are adjacent on the tiled side
+  auto tile_rc = [&](unsigned tl, int* r0, int* r1) {
+    if (tile_fast_r0) { *r1 = int(tl / unsigned(r0n)); *r0 = int(tl - unsigned(*r1) * unsigned(r0n)); }
+    else { *r0 = int(tl / unsigned(r1n)); *r1 = int(tl - unsigned(*r0) * unsigned(r1n)); }
+  };
+  auto smem_at = [&](int r0, int r1, int slow, int fast) -> char* {
+    const int t0 = fast_is_t1 ? slow : fast, t1 = fast_is_t1 ? fast : slow;
+    return smem_b + (r0 * T0 + t0) * pitch_b + (r1 * T1 + t1) * ES;
+  };
+
+  // ---- matrix side <-> shared memory: row segments ----
+  auto matrix_phase = [&]() {
+    if (vec_mat) {
+      const unsigned vpr = unsigned(cols) / NV;
+      const unsigned nvec = unsigned(rows) * vpr;
+      const uint32_t padw = splat_pad(a.pad, ES);
+      for (unsigned vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+        const unsigned r = vi / vpr, cv = vi - r * vpr;
+        const int64_t gi0 = row_base + r, gi1 = col_base + int64_t(cv) * NV;
+        uint4* sv = reinterpret_cast<uint4*>(smem_w + r * pitch_words + cv * 4);
+        if (IS_PACK) {
+          if (gi0 < a.mat_size0 && gi1 + NV <= a.mat_size1) {
+            *sv = __ldg(reinterpret_cast<const uint4*>(mat_src + (gi0 * a.mat_stride0 + gi1) * ES));
+          } else if (gi0 >= a.mat_size0 || gi1 >= a.mat_size1) {
+            *sv = make_uint4(padw, padw, padw, padw);
+          } else {  // vector straddles the right edge
+            E* se = reinterpret_cast<E*>(sv);
+            for (int j = 0; j < NV; ++j)
+              se[j] = (gi1 + j < a.mat_size1)
+                          ? reinterpret_cast<const E*>(mat_src)[gi0 * a.mat_stride0 + gi1 + j]
+                          : padv;
+          }
+        } else {
+          if (gi0 >= a.mat_size0 || gi1 >= a.mat_size1) continue;
+          if (gi1 + NV <= a.mat_size1) {
+            *reinterpret_cast<uint4*>(mat_dst + (gi0 * a.mat_stride0 + gi1) * ES) = *sv;
+          } else {
+            const E* se = reinterpret_cast<const E*>(sv);
+            for (int j = 0; j < NV && gi1 + j < a.mat_size1; ++j)
+              reinterpret_cast<E*>(mat_dst)[gi0 * a.mat_stride0 + gi1 + j] = se[j];
+          }
+        }
+      }
+    } else {
+      const unsigned nel = unsigned(rows) * unsigned(cols);
+      for (unsigned ei = threadIdx.x; ei < nel; ei += blockDim.x) {
+        const unsigned r = ei / unsigned(cols), c = ei - r * unsigned(cols);
+        const int64_t gi0 = row_base + r, gi1 = col_base + c;
+        E* sp = reinterpret_cast<E*>(smem_b + r * pitch_b + c * ES);
+        const bool inside = gi0 < a.mat_size0 && gi1 < a.mat_size1;
+        const int64_t me = gi0 * a.mat_stride0 + gi1 * a.mat_stride1;
+        if (IS_PACK) *sp = inside ? reinterpret_cast<const E*>(mat_src)[me] : padv;
+        else if (inside) reinterpret_cast<E*>(mat_dst)[me] = *sp;
       }
     }
-  } else {
-    const int nel = rows * cols;
-    for (int ei = threadIdx.x; ei < nel; ei += blockDim.x) {
-      const int r = ei / cols, c = ei - r * cols;
-      const int64_t gi0 = row_base + r, gi1 = col_base + c;
-      if (gi0 < a.mat_size0 && gi1 < a.mat_size1)
-        reinterpret_cast<E*>(a.dst)[gi0 * a.mat_stride0 + gi1 * a.mat_stride1] =
-            *reinterpret_cast<const E*>(smem_b + r * pitch_b + c * ES);
+  };
+
+  // ---- tiled side <-> shared memory: runs of whole tiles ----
+  auto tiled_phase = [&]() {
+    if (vec_tiled) {
+      const unsigned tvec = unsigned(tile_elems) / NV;
+      const unsigned nvec = unsigned(ntiles) * tvec;
+      for (unsigned vi = threadIdx.x; vi < nvec; vi += blockDim.x) {
+        const unsigned tl = vi / tvec, v = vi - tl * tvec;
+        int r0, r1;
+        tile_rc(tl, &r0, &r1);
+        const int e = int(v) * NV;
+        int slow = int(unsigned(e) / unsigned(fastN)), fast = e - slow * fastN;
+        const int64_t te = (tile0_base + r0) * a.tiled_stride_o0 +
+                           (tile1_base + r1) * a.tiled_stride_o1 + e;
+        if (row_vectors) {
+          uint4* sv = reinterpret_cast<uint4*>(smem_at(r0, r1, slow, fast));
+          if (IS_PACK) *reinterpret_cast<uint4*>(tiled_dst + te * ES) = *sv;
+          else *sv = __ldg(reinterpret_cast<const uint4*>(tiled_src + te * ES));
+        } else if (IS_PACK) {
+          uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            const uint32_t val = *reinterpret_cast<const E*>(smem_at(r0, r1, slow, fast));
+            w[(j * ES) / 4] |= val << (8 * ((j * ES) % 4));
+            if (++fast == fastN) { fast = 0; ++slow; }
+          }
+          *reinterpret_cast<uint4*>(tiled_dst + te * ES) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+          const uint4 in = __ldg(reinterpret_cast<const uint4*>(tiled_src + te * ES));
+          const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            *reinterpret_cast<E*>(smem_at(r0, r1, slow, fast)) =
+                E(w[(j * ES) / 4] >> (8 * ((j * ES) % 4)));
+            if (++fast == fastN) { fast = 0; ++slow; }
+          }
+        }
+      }
+    } else {
+      const unsigned nel = unsigned(ntiles) * unsigned(tile_elems);
+      for (unsigned ei = threadIdx.x; ei < nel; ei += blockDim.x) {
+        const unsigned tl = ei / unsigned(tile_elems), e = ei - tl * unsigned(tile_elems);
+        int r0, r1;
+        tile_rc(tl, &r0, &r1);
+        const int slow = int(e / unsigned(fastN)), fast = int(e) - slow * fastN;
+        const int64_t te = (tile0_base + r0) * a.tiled_stride_o0 +
+                           (tile1_base + r1) * a.tiled_stride_o1 + e;
+        E* sp = reinterpret_cast<E*>(smem_at(r0, r1, slow, fast));
+        if (IS_PACK) reinterpret_cast<E*>(tiled_dst)[te] = *sp;
+        else *sp = reinterpret_cast<const E*>(tiled_src)[te];
+      }
     }
+  };
+
+  if (IS_PACK) {
+    matrix_phase();  // matrix rows -> shared memory, padding filled in
+    __syncthreads();
+    tiled_phase();   // shared memory -> whole tiles
+  } else {
+    tiled_phase();   // whole tiles -> shared memory
+    __syncthreads();
+    matrix_phase();  // shared memory -> matrix rows; nothing outside mat_size0 x mat_size1
   }
 }
 
@@ -331,8 +312,7 @@ size_t plan_staged(RelayoutArgs* a, int es, const char* mat_base, const char* ti
   if (!a->tile_fast_r0) R0 = 1;
   if (R0 > a->outer0) R0 = a->outer0;
   const int64_t rows = R0 * a->T0, cols = R1 * a->T1;
-  int64_t pitch_words = (cols * es + 3) / 4;
-  if ((pitch_words & 1) == 0) pitch_words += 1;
+  const int64_t pitch_words = staged_pitch_words(int(cols * es));
   const int64_t smem = rows * pitch_words * 4;
   if (smem > 46 * 1024) return 0;
   a->R0 = int32_t(R0); a->R1 = int32_t(R1);
@@ -416,33 +396,87 @@ bool unpack_staged_eligible(const iree_uk_unpack_params_t* p) {
   return plan_staged(&a, es, a.dst, a.src) != 0;
 }
 
+namespace {
+
+// True when a launch with constant shape (T0, T1, R0, R1) is legal for the planned problem:
+// same tile, block shape overridden to the constants, all blocks full, vectors on both sides.
+template <class Shape>
+bool fits_fixed_shape(const RelayoutArgs& a, int es, const char* mat_base, const char* tiled_base) {
+  if (a.T0 != Shape::T0 || a.T1 != Shape::T1) return false;
+  if ((a.inner_s1 == 1) != Shape::kFastT1 && !(a.T0 == 1 || a.T1 == 1)) return false;
+  if ((a.tile_fast_r0 != 0) != Shape::kTileFastR0) return false;
+  if (a.outer0 % Shape::R0 || a.outer1 % Shape::R1) return false;
+  const int64_t tile_bytes = int64_t(a.T0) * a.T1 * es;
+  const bool vec_mat = a.mat_stride1 == 1 && aligned16(mat_base) && (a.mat_stride0 * es) % 16 == 0 &&
+                       (int64_t(Shape::R1) * Shape::T1 * es) % 16 == 0;
+  const bool vec_tiled = aligned16(tiled_base) && tile_bytes % 16 == 0 &&
+                         (a.tiled_stride_o0 * es) % 16 == 0 && (a.tiled_stride_o1 * es) % 16 == 0;
+  return vec_mat && vec_tiled &&
+         (a.outer0 / Shape::R0) * (a.outer1 / Shape::R1) <= 0x7FFFFFFF;
+}
+
+template <int ES, bool IS_PACK, class Shape>
+int launch_fixed(RelayoutArgs a, cudaStream_t stream) {
+  a.R0 = Shape::R0; a.R1 = Shape::R1;
+  a.nblk1 = a.outer1 / Shape::R1;
+  const int64_t blocks = a.nblk1 * (a.outer0 / Shape::R0);
+  constexpr int pitch = staged_pitch_words(Shape::R1 * Shape::T1 * ES);
+  constexpr size_t smem = size_t(Shape::R0) * Shape::T0 * pitch * 4;
+  static_assert(smem <= 48 * 1024, "fixed shape exceeds the default shared-memory limit");
+  relayout_staged_kernel<ES, IS_PACK, Shape><<<int(blocks), 256, smem, stream>>>(a);
+  return cuda_status(cudaGetLastError());
+}
+
+// Constant-shape instantiations for the tile shapes that carry real traffic (the tiles the
+// reference's x86-64 encoder picks, Codegen/ExternalInterfaces/CPUEncodingExternalModels.cpp:
+// 479-585): LHS-style 16xK0 tiles, RHS-style tiles packed with both transposes, and 16x16
+// accumulator tiles. (T0, T1) are extents along matrix rows / columns.
+using Pack16x1   = FixedShape<16, 1, 1, 256, false, false>;  // f32 [M][K] -> [M1][K1][16][1]
+using Pack16x2   = FixedShape<16, 2, 1, 256, true, false>;   // bf16/i8 [M][K] -> [M1][K1][16][2]
+using PackT1x16  = FixedShape<1, 16, 64, 4, true, true>;     // [K][N] -> [N1][K1][16][1], 0x300
+using PackT2x16  = FixedShape<2, 16, 32, 8, false, true>;    // [K][N] -> [N1][K1][16][2], 0x300
+using Tile16x16  = FixedShape<16, 16, 1, 16, true, false>;   // accumulator tiles
+
+template <int ES, bool IS_PACK>
+int launch_staged(RelayoutArgs& a, const char* mat_base, const char* tiled_base,
+                  cudaStream_t stream) {
+#define UK_TRY_FIXED(SHAPE)                                         \
+  if (fits_fixed_shape<SHAPE>(a, ES, mat_base, tiled_base))         \
+    return launch_fixed<ES, IS_PACK, SHAPE>(a, stream);
+  UK_TRY_FIXED(Pack16x1)
+  UK_TRY_FIXED(Pack16x2)
+  UK_TRY_FIXED(PackT1x16)
+  UK_TRY_FIXED(PackT2x16)
+  UK_TRY_FIXED(Tile16x16)
+#undef UK_TRY_FIXED
+  const size_t smem = plan_staged(&a, ES, mat_base, tiled_base);
+  if (!smem) return IREE_UK_B200_UNSUPPORTED;
+  const int64_t blocks = a.nblk1 * ((a.outer0 + a.R0 - 1) / a.R0);
+  relayout_staged_kernel<ES, IS_PACK, RuntimeShape><<<int(blocks), 256, smem, stream>>>(a);
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace
+
 int launch_pack_staged(const iree_uk_pack_params_t* p, cudaStream_t stream) {
   const int es = pack_elem_size(p->flags);
   RelayoutArgs a;
   pack_args(p, es, &a);
-  const size_t smem = plan_staged(&a, es, a.src, a.dst);
-  if (!smem) return IREE_UK_B200_UNSUPPORTED;
-  const int64_t blocks = a.nblk1 * ((a.outer0 + a.R0 - 1) / a.R0);
   switch (es) {
-    case 1: pack_staged_kernel<1><<<int(blocks), 256, smem, stream>>>(a); break;
-    case 2: pack_staged_kernel<2><<<int(blocks), 256, smem, stream>>>(a); break;
-    default: pack_staged_kernel<4><<<int(blocks), 256, smem, stream>>>(a); break;
+    case 1: return launch_staged<1, true>(a, a.src, a.dst, stream);
+    case 2: return launch_staged<2, true>(a, a.src, a.dst, stream);
+    default: return launch_staged<4, true>(a, a.src, a.dst, stream);
   }
-  return cuda_status(cudaGetLastError());
 }
 
 int launch_unpack_staged(const iree_uk_unpack_params_t* p, cudaStream_t stream) {
   const int es = unpack_elem_size(p->flags);
   RelayoutArgs a;
   unpack_args(p, es, &a);
-  const size_t smem = plan_staged(&a, es, a.dst, a.src);
-  if (!smem) return IREE_UK_B200_UNSUPPORTED;
-  const int64_t blocks = a.nblk1 * ((a.outer0 + a.R0 - 1) / a.R0);
   switch (es) {
-    case 2: unpack_staged_kernel<2><<<int(blocks), 256, smem, stream>>>(a); break;
-    default: unpack_staged_kernel<4><<<int(blocks), 256, smem, stream>>>(a); break;
+    case 2: return launch_staged<2, false>(a, a.dst, a.src, stream);
+    default: return launch_staged<4, false>(a, a.dst, a.src, stream);
   }
-  return cuda_status(cudaGetLastError());
 }
 
 // ---------------------------------------------------------------------------------------
