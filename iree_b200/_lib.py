@@ -58,3 +58,5 @@ lib.iree_uk_b200_debug_kernel_timing.restype = C.c_int
 lib.iree_uk_b200_debug_kernel_timing.argtypes = [C.c_int]
 lib.iree_uk_b200_debug_last_kernel_ms.restype = C.c_int
 lib.iree_uk_b200_debug_last_kernel_ms.argtypes = [_P, _P]
+lib.iree_uk_b200_debug_mean_kernel_ms.restype = C.c_int
+lib.iree_uk_b200_debug_mean_kernel_ms.argtypes = [_P, _P, _P]

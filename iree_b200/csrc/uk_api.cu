@@ -349,27 +349,54 @@ IREE_UK_B200_EXPORT int iree_uk_b200_debug_mmt4d_variant(const iree_uk_mmt4d_par
 }
 
 // Internal, not declared in the public header: benchmark timing of the tensor-core path.
-// enable != 0 creates three CUDA events (once) and makes every later tensor-core mmt4d call
-// record them before the re-tile pre-pass, before the main kernel and after it.
+// enable != 0 creates the CUDA events (once) and makes every later tensor-core mmt4d call
+// record three of them: before the re-tile pre-pass, before the main kernel and after it.
+// The last 64 calls are remembered.
 IREE_UK_B200_EXPORT int iree_uk_b200_debug_kernel_timing(int enable) {
   KernelTiming& t = kernel_timing();
-  if (enable && !t.ev[0]) {
-    for (int i = 0; i < 3; ++i)
-      if (cudaEventCreate(&t.ev[i]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  if (enable && !t.ev[0][0]) {
+    for (int c = 0; c < KernelTiming::kRing; ++c)
+      for (int i = 0; i < 3; ++i)
+        if (cudaEventCreate(&t.ev[c][i]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   }
   t.enabled = enable != 0;
-  t.recorded = false;
+  t.calls = 0;
   return IREE_UK_B200_OK;
 }
 
-// Milliseconds of the last recorded call: pre-pass and main kernel. Synchronises on the events.
+// Mean milliseconds of pre-pass and main kernel over the remembered calls (at most the last
+// 64 since timing was enabled); *count receives how many. Synchronises on the last event.
+IREE_UK_B200_EXPORT int iree_uk_b200_debug_mean_kernel_ms(float* prepass_ms, float* main_ms,
+                                                          int* count) {
+  KernelTiming& t = kernel_timing();
+  if (!t.enabled || t.calls == 0) return IREE_UK_B200_INVALID_ARGUMENT;
+  const long long n = t.calls < KernelTiming::kRing ? t.calls : KernelTiming::kRing;
+  double a = 0.0, b = 0.0;
+  for (long long i = 0; i < n; ++i) {
+    cudaEvent_t* e = t.ev[(t.calls - 1 - i) % KernelTiming::kRing];
+    if (cudaEventSynchronize(e[2]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+    float x = 0.f, y = 0.f;
+    if (cudaEventElapsedTime(&x, e[0], e[1]) != cudaSuccess ||
+        cudaEventElapsedTime(&y, e[1], e[2]) != cudaSuccess)
+      return IREE_UK_B200_CUDA_ERROR;
+    a += x;
+    b += y;
+  }
+  if (prepass_ms) *prepass_ms = float(a / n);
+  if (main_ms) *main_ms = float(b / n);
+  if (count) *count = int(n);
+  return IREE_UK_B200_OK;
+}
+
+// Milliseconds of the last recorded call: pre-pass and main kernel.
 IREE_UK_B200_EXPORT int iree_uk_b200_debug_last_kernel_ms(float* prepass_ms, float* main_ms) {
   KernelTiming& t = kernel_timing();
-  if (!t.enabled || !t.recorded) return IREE_UK_B200_INVALID_ARGUMENT;
-  if (cudaEventSynchronize(t.ev[2]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  if (!t.enabled || t.calls == 0) return IREE_UK_B200_INVALID_ARGUMENT;
+  cudaEvent_t* e = t.ev[(t.calls - 1) % KernelTiming::kRing];
+  if (cudaEventSynchronize(e[2]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   float a = 0.f, b = 0.f;
-  if (cudaEventElapsedTime(&a, t.ev[0], t.ev[1]) != cudaSuccess ||
-      cudaEventElapsedTime(&b, t.ev[1], t.ev[2]) != cudaSuccess)
+  if (cudaEventElapsedTime(&a, e[0], e[1]) != cudaSuccess ||
+      cudaEventElapsedTime(&b, e[1], e[2]) != cudaSuccess)
     return IREE_UK_B200_CUDA_ERROR;
   if (prepass_ms) *prepass_ms = a;
   if (main_ms) *main_ms = b;

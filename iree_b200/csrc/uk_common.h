@@ -77,9 +77,11 @@ inline int cuda_status(cudaError_t e) {
 // Optional kernel timing for benchmarks (off by default): when enabled, launchers that run a
 // pre-pass plus a main kernel record CUDA events between them on the launching stream.
 struct KernelTiming {
+  static constexpr int kRing = 64;  // calls remembered
   bool enabled = false;
-  cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};  // before pre-pass, before main, after main
-  bool recorded = false;
+  cudaEvent_t ev[kRing][3] = {};  // per call: before pre-pass, before main, after main
+  long long calls = 0;            // calls recorded since timing was enabled
+  cudaEvent_t* slot() { return ev[calls % kRing]; }
 };
 KernelTiming& kernel_timing();
 

@@ -126,9 +126,23 @@ __global__ void __launch_bounds__(256) mmt4d_zero_fill_kernel(char* out, int64_t
 // even k0]; the whole RHS row n1 is K*128 contiguous bytes. One block per (m, n1) pair
 // keeps 32 int32 sums; each lane streams 16 bytes (4 n0 rows of one k1) per step, four k1
 // per warp step, and the eight warps interleave along K. HBM-bound by construction: every
-// weight byte is read once with 16-byte loads.
+// weight byte is read once with 16-byte loads. The s16 x u4 products are computed exactly as
+// byte dot products: s16 = signed high byte * 256 + unsigned low byte, nibbles widened to
+// bytes, four dp4a per 8 weights, recombined as hi*256 + lo at the end.
 // ---------------------------------------------------------------------------------------
-constexpr int kGemvWarps = 8;
+constexpr int kGemvWarps = 16;
+
+__device__ __forceinline__ uint32_t dp4a_uu(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// a: four unsigned bytes, b: four signed bytes
+__device__ __forceinline__ int32_t dp4a_us(uint32_t a, uint32_t b, int32_t c) {
+  int32_t d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
 
 __global__ void __launch_bounds__(kGemvWarps * 32) mmt4d_gemv_s16u4_kernel(GenericArgs a) {
   __shared__ int32_t partial[kGemvWarps][32];
@@ -138,39 +152,47 @@ __global__ void __launch_bounds__(kGemvWarps * 32) mmt4d_gemv_s16u4_kernel(Gener
   const int ng = lane & 7;       // which group of 4 n0 rows
   const uint4* rhs = reinterpret_cast<const uint4*>(a.rhs + n1 * a.rhs_stride_b);
   const uint4* lhs = reinterpret_cast<const uint4*>(a.lhs + m * a.lhs_stride_b);
-  int32_t acc[4] = {0, 0, 0, 0};
-  constexpr int kUnroll = 4;  // independent 16-byte weight loads in flight per thread
+  uint32_t acc_lo[4] = {0u, 0u, 0u, 0u};
+  int32_t acc_hi[4] = {0, 0, 0, 0};
+  constexpr int kUnroll = 8;  // independent 16-byte weight loads in flight per thread
   constexpr int kStep = kGemvWarps * 4;
   for (int64_t kb = int64_t(warp) * 4 + kq; kb < a.K; kb += kStep * kUnroll) {
     uint4 wv[kUnroll], xv[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
+      // Unconditional loads (index clamped, weights zeroed afterwards) so that all kUnroll
+      // loads are issued before the first use.
       const int64_t k = kb + int64_t(u) * kStep;
-      if (k < a.K) {
-        wv[u] = __ldg(rhs + k * 8 + ng);  // 4 n0 rows x 8 nibbles
-        xv[u] = __ldg(lhs + k);           // 8 s16 of this k1
-      } else {
-        wv[u] = make_uint4(0u, 0u, 0u, 0u);
-        xv[u] = make_uint4(0u, 0u, 0u, 0u);
-      }
+      const bool valid = k < a.K;
+      const int64_t kc = valid ? k : 0;
+      wv[u] = __ldg(rhs + kc * 8 + ng);  // 4 n0 rows x 8 nibbles
+      xv[u] = __ldg(lhs + kc);           // 8 s16 of this k1
+      if (!valid) wv[u] = make_uint4(0u, 0u, 0u, 0u);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const uint32_t xs[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+      // x = hi*256 + lo with hi the signed high byte and lo the unsigned low byte, so
+      // sum(w*x) = 256*sum(w*hi) + sum(w*lo): byte dot products (dp4a) instead of 16-bit
+      // multiplies. Even / odd k0 are separated because a weight byte holds k0 = 2h in its low
+      // nibble and k0 = 2h+1 in its high nibble.
+      const uint32_t e01 = __byte_perm(xv[u].x, xv[u].y, 0x5140);  // lo x0, lo x2, hi x0, hi x2
+      const uint32_t e23 = __byte_perm(xv[u].z, xv[u].w, 0x5140);
+      const uint32_t o01 = __byte_perm(xv[u].x, xv[u].y, 0x7362);  // lo x1, lo x3, hi x1, hi x3
+      const uint32_t o23 = __byte_perm(xv[u].z, xv[u].w, 0x7362);
+      const uint32_t xe_lo = __byte_perm(e01, e23, 0x5410), xe_hi = __byte_perm(e01, e23, 0x7632);
+      const uint32_t xo_lo = __byte_perm(o01, o23, 0x5410), xo_hi = __byte_perm(o01, o23, 0x7632);
       const uint32_t ws[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        int32_t s = 0;
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {  // byte h holds k0 = 2h (low nibble) and 2h+1 (high)
-          const uint32_t byte = (ws[r] >> (8 * h)) & 0xFFu;
-          const int32_t x0 = int16_t(xs[h] & 0xFFFFu), x1 = int16_t(xs[h] >> 16);
-          s += x0 * int32_t(byte & 0xFu) + x1 * int32_t(byte >> 4);
-        }
-        acc[r] += s;
+        const uint32_t w_even = ws[r] & 0x0F0F0F0Fu, w_odd = (ws[r] >> 4) & 0x0F0F0F0Fu;
+        acc_lo[r] = dp4a_uu(w_even, xe_lo, dp4a_uu(w_odd, xo_lo, acc_lo[r]));
+        acc_hi[r] = dp4a_us(w_even, xe_hi, dp4a_us(w_odd, xo_hi, acc_hi[r]));
       }
     }
   }
+  int32_t acc[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) acc[r] = int32_t(acc_lo[r] + (uint32_t(acc_hi[r]) << 8));
   // lanes with the same ng hold partial sums of the same 4 outputs
 #pragma unroll
   for (int r = 0; r < 4; ++r) {

@@ -806,15 +806,15 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
 // re-tile: mmt4d panels [tile][K1][16][K0] -> row-major [tile*16 + r][K1*K0] scratch
 // ---------------------------------------------------------------------------------------
 // G = K0 * element bytes is the granule that stays contiguous; per tile row the kernel
-// transposes a [K1][16] matrix of granules into [16][K1]. A block moves 256/G k1 steps of
-// one tile row (4 KB) through shared memory: contiguous 16-byte loads, 16-byte stores of
-// 256-byte row segments. The shared-memory pitch per k1 is 16*G + 4 bytes so that walking
+// transposes a [K1][16] matrix of granules into [16][K1]. A block moves 1024/G k1 steps of
+// one tile row (16 KB) through shared memory: contiguous 16-byte loads, 16-byte stores of
+// 1 KB row segments, four of each in flight per thread. The shared-memory pitch per k1 is 16*G + 4 bytes so that walking
 // k1 at a fixed row is bank-conflict free.
 template <int G>
 __global__ void __launch_bounds__(256) retile_kernel(const char* __restrict__ src,
                                                      int64_t src_stride_b, char* __restrict__ dst,
                                                      int64_t dst_pitch_b, int64_t K1, int kchunks) {
-  constexpr int KC = 256 / G;             // k1 steps per block
+  constexpr int KC = 1024 / G;            // k1 steps per block: 16 KB in, 16 rows x 1 KB out
   constexpr int PITCH = 16 * G + 4;       // bytes per k1 in shared memory
   constexpr int GV = 16 / G;              // granules per 16-byte vector
   __shared__ __align__(16) unsigned char sm[KC * PITCH];
@@ -825,6 +825,7 @@ __global__ void __launch_bounds__(256) retile_kernel(const char* __restrict__ sr
   const char* sp = src + tile * src_stride_b + k_base * (16 * G);
   // load: kn * 16 granules contiguous = kn * G vectors of 16 bytes
   const int nvec = kn * G;
+#pragma unroll 4
   for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
     const uint4 x = __ldg(reinterpret_cast<const uint4*>(sp) + v);
     const int byte = v * 16;
@@ -834,12 +835,13 @@ __global__ void __launch_bounds__(256) retile_kernel(const char* __restrict__ sr
   }
   __syncthreads();
   // store: 16 rows x kn granules; a thread builds 16 bytes = GV consecutive k1 of one row
-  // Lane mapping: 4 consecutive vectors of a row (64 bytes), then the next row; keeps the
-  // shared-memory reads spread over banks and the global stores in 64-byte pieces.
+  // Lane mapping: 8 consecutive vectors of a row (128 bytes), then the next row; keeps the
+  // shared-memory reads spread over banks and the global stores in 128-byte pieces.
   const int vec_per_row = (kn + GV - 1) / GV;
-  const int vec_per_row4 = (vec_per_row + 3) & ~3;
-  for (int v = threadIdx.x; v < 16 * vec_per_row4; v += blockDim.x) {
-    const int r = (v >> 2) & 15, kv = ((v >> 6) << 2) | (v & 3);
+  const int vec_per_row8 = (vec_per_row + 7) & ~7;
+#pragma unroll 4
+  for (int v = threadIdx.x; v < 16 * vec_per_row8; v += blockDim.x) {
+    const int r = (v >> 3) & 15, kv = ((v >> 7) << 3) | (v & 7);
     if (kv >= vec_per_row) continue;
     const int k0 = kv * GV;
     char* dp = dst + (tile * 16 + r) * dst_pitch_b + (k_base + k0) * G;
@@ -885,7 +887,7 @@ __global__ void __launch_bounds__(256) retile_kernel(const char* __restrict__ sr
 int launch_retile(const char* src, int64_t src_stride_b, char* dst, int64_t dst_pitch_b,
                   int64_t tiles, int64_t K1, int G, cudaStream_t stream) {
   if (tiles <= 0 || K1 <= 0) return IREE_UK_B200_OK;
-  const int KC = 256 / G;
+  const int KC = 1024 / G;
   const int64_t kchunks = (K1 + KC - 1) / KC;
   const int64_t blocks = tiles * kchunks;
   if (blocks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
@@ -1072,7 +1074,8 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   TcParams P;
   std::memset(&P, 0, sizeof P);
   KernelTiming& timing = kernel_timing();
-  if (timing.enabled) cudaEventRecord(timing.ev[0], stream);
+  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  if (tev) cudaEventRecord(tev[0], stream);
   int bn = pick_bn(p->M, p->N);
   bool pair = false;
   int pair_clusters = 0;
@@ -1237,7 +1240,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaError_t e;
-  if (timing.enabled) cudaEventRecord(timing.ev[1], stream);
+  if (tev) cudaEventRecord(tev[1], stream);
   if (pair) {
     const int clusters = std::min(P.m_tiles * P.n_tiles, pair_clusters);
     cudaLaunchConfig_t cfg = {};
@@ -1274,9 +1277,9 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
       mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
     }
   }
-  if (timing.enabled) {
-    cudaEventRecord(timing.ev[2], stream);
-    timing.recorded = true;
+  if (tev) {
+    cudaEventRecord(tev[2], stream);
+    ++timing.calls;
   }
   return cuda_status(cudaGetLastError());
 }
