@@ -248,7 +248,7 @@ def main():
     path = uk.mmt4d_path(p, True)
     assert path in (abi.PATH_TCGEN05, abi.PATH_TCGEN05_RETILE), "tensor-core path not selected"
     stream = torch.cuda.current_stream()
-    launches_per_step = 3 if path == abi.PATH_TCGEN05_RETILE else 1
+    launches_per_step = 2 if path == abi.PATH_TCGEN05_RETILE else 1
 
     # ---- warm-up ----
     for _ in range(args.warmup):
@@ -369,7 +369,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "tiles": "M0=16,N0=16,K0=2",
                    "sharding": "N1 split over %d rank(s), no data-path collective" % world,
-                   "l2": "inputs_larger_than_l2", "path": "tcgen05+retile" if launches_per_step == 3 else "tcgen05",
+                   "l2": "inputs_larger_than_l2", "path": "tcgen05+retile" if launches_per_step == 2 else "tcgen05",
                    "spot_check_rel_err": spot_err},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps},

@@ -810,16 +810,29 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
 // one tile row (16 KB) through shared memory: contiguous 16-byte loads, 16-byte stores of
 // 1 KB row segments, four of each in flight per thread. The shared-memory pitch per k1 is 16*G + 4 bytes so that walking
 // k1 at a fixed row is bank-conflict free.
+struct RetileOperand {
+  const char* src;       // first panel
+  int64_t src_stride_b;  // bytes between panels (tile rows)
+  char* dst;             // row-major scratch
+  int64_t blocks;        // tile rows x k chunks
+};
+
+// Both operands of a mmt4d call in one launch: blocks [0, a.blocks) re-tile the LHS, the rest
+// the RHS.
 template <int G>
-__global__ void __launch_bounds__(256) retile_kernel(const char* __restrict__ src,
-                                                     int64_t src_stride_b, char* __restrict__ dst,
+__global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOperand opb,
                                                      int64_t dst_pitch_b, int64_t K1, int kchunks) {
+  const bool is_a = int64_t(blockIdx.x) < opa.blocks;
+  const char* __restrict__ src = is_a ? opa.src : opb.src;
+  const int64_t src_stride_b = is_a ? opa.src_stride_b : opb.src_stride_b;
+  char* __restrict__ dst = is_a ? opa.dst : opb.dst;
+  const int64_t block = is_a ? int64_t(blockIdx.x) : int64_t(blockIdx.x) - opa.blocks;
   constexpr int KC = 1024 / G;            // k1 steps per block: 16 KB in, 16 rows x 1 KB out
   constexpr int PITCH = 16 * G + 4;       // bytes per k1 in shared memory
   constexpr int GV = 16 / G;              // granules per 16-byte vector
   __shared__ __align__(16) unsigned char sm[KC * PITCH];
-  const int64_t tile = blockIdx.x / kchunks;
-  const int chunk = int(blockIdx.x - tile * kchunks);
+  const int64_t tile = block / kchunks;
+  const int chunk = int(block - tile * kchunks);
   const int64_t k_base = int64_t(chunk) * KC;
   const int kn = int(min(int64_t(KC), K1 - k_base));
   const char* sp = src + tile * src_stride_b + k_base * (16 * G);
@@ -884,19 +897,22 @@ __global__ void __launch_bounds__(256) retile_kernel(const char* __restrict__ sr
   }
 }
 
-int launch_retile(const char* src, int64_t src_stride_b, char* dst, int64_t dst_pitch_b,
-                  int64_t tiles, int64_t K1, int G, cudaStream_t stream) {
-  if (tiles <= 0 || K1 <= 0) return IREE_UK_B200_OK;
+int launch_retile(const char* lhs, int64_t lhs_stride_b, char* dst_a, int64_t tiles_a,
+                  const char* rhs, int64_t rhs_stride_b, char* dst_b, int64_t tiles_b,
+                  int64_t dst_pitch_b, int64_t K1, int G, cudaStream_t stream) {
+  if (K1 <= 0 || tiles_a + tiles_b <= 0) return IREE_UK_B200_OK;
   const int KC = 1024 / G;
   const int64_t kchunks = (K1 + KC - 1) / KC;
-  const int64_t blocks = tiles * kchunks;
+  const RetileOperand a = {lhs, lhs_stride_b, dst_a, tiles_a * kchunks};
+  const RetileOperand b = {rhs, rhs_stride_b, dst_b, tiles_b * kchunks};
+  const int64_t blocks = a.blocks + b.blocks;
   if (blocks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
   switch (G) {
-    case 1: retile_kernel<1><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
-    case 2: retile_kernel<2><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
-    case 4: retile_kernel<4><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
-    case 8: retile_kernel<8><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
-    case 16: retile_kernel<16><<<int(blocks), 256, 0, stream>>>(src, src_stride_b, dst, dst_pitch_b, K1, int(kchunks)); break;
+    case 1: retile_kernel<1><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
+    case 2: retile_kernel<2><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
+    case 4: retile_kernel<4><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
+    case 8: retile_kernel<8><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
+    case 16: retile_kernel<16><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
     default: return IREE_UK_B200_UNSUPPORTED;
   }
   return cuda_status(cudaGetLastError());
@@ -1099,9 +1115,8 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     char* ws_a = static_cast<char*>(ws);
     char* ws_b = ws_a + round_up(p->M * 16 * pitch, 1024);
     const int G = p->K0 * ti.es;
-    int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, pitch, p->M, p->K, G, stream);
-    if (rc) return rc;
-    rc = launch_retile(rhs, p->rhs_stride0 * ti.es, ws_b, pitch, p->N, p->K, G, stream);
+    const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, p->M, rhs,
+                                 p->rhs_stride0 * ti.es, ws_b, p->N, pitch, p->K, G, stream);
     if (rc) return rc;
     const uint64_t da[3] = {uint64_t(kelems), uint64_t(p->M * 16), 1};
     const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), 1};
@@ -1140,9 +1155,8 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     char* ws_a = static_cast<char*>(ws);
     char* ws_b = ws_a + round_up(p->M * 16 * pitch, 1024);
     const int G = p->K0 * ti.es;
-    int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, pitch, p->M, p->K, G, stream);
-    if (rc) return rc;
-    rc = launch_retile(rhs, p->rhs_stride0 * ti.es, ws_b, pitch, p->N, p->K, G, stream);
+    const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, p->M, rhs,
+                                 p->rhs_stride0 * ti.es, ws_b, p->N, pitch, p->K, G, stream);
     if (rc) return rc;
     const uint64_t da[3] = {uint64_t(kelems), uint64_t(p->M * 16), 1};
     const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), 1};
