@@ -50,6 +50,8 @@ int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path)
   if (p->K == 0 || p->K0 == 0) { *path = Mmt4dPath::ZeroFill; return 0; }
   const bool force_generic = env_flag("IREE_UK_B200_FORCE_GENERIC");
   if (!force_generic) {
+    // s16u4s32: the tensor-core path once there are rows to fill a tile, else the GEMV.
+    if (have_ws && p->M >= 32 && mmt4d_tc_s16u4_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
     if (mmt4d_gemv_s16u4_eligible(p)) { *path = Mmt4dPath::Gemv; return 0; }
     if (have_ws && mmt4d_tc_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
   }
@@ -149,6 +151,8 @@ uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t fl
   const int es = type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 ? 1 : 2;
   const int g = K0 * es;
   if (tc_type && M0 == 16 && N0 == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16))
+    return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 && M0 == 1 && N0 == 32 && K0 == 8)
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   return 0;
 }
@@ -343,7 +347,7 @@ IREE_UK_B200_EXPORT int iree_uk_b200_debug_mmt4d_variant(const iree_uk_mmt4d_par
                                                          int variant, void* cu_stream) {
   const int rc = validate_mmt4d(params);
   if (rc) return rc;
-  if (!mmt4d_tc_eligible(params)) return IREE_UK_B200_UNSUPPORTED;
+  if (!mmt4d_tc_eligible(params) && !mmt4d_tc_s16u4_eligible(params)) return IREE_UK_B200_UNSUPPORTED;
   return launch_mmt4d_tc(params, workspace, workspace_bytes, variant,
                          static_cast<cudaStream_t>(cu_stream));
 }

@@ -49,6 +49,8 @@ bool mmt4d_gemv_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
 
 // Tensor-core path. `variant` selects the operand staging layout (see uk_mmt4d_tc.cu).
 bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p);
+// s16u4s32 1x32x8 with enough rows to fill tensor-core tiles (two byte planes x u8 weights).
+bool mmt4d_tc_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream);

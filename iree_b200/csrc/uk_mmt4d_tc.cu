@@ -63,6 +63,8 @@ struct TcParams {
   uint32_t kadv_a, kadv_b;          // start-address advance per MMA along K, in 16-byte units
   uint32_t kbox_units_a, kbox_units_b;  // 16-byte units between the K boxes of one stage
   uint32_t idesc;
+  uint32_t idesc2;      // dual-LHS mode: instruction descriptor of the second (low-byte) MMA
+  int32_t dual;         // s16u4s32: two LHS planes (signed high / unsigned low bytes) per stage
   int32_t kboxes;       // K boxes per stage (1 or 2)
   int32_t mma_per_box;  // tcgen05.mma per K box
   int32_t stage_bytes_a, stage_bytes_b;
@@ -365,6 +367,37 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
   }
 }
 
+// Epilogue of the dual-LHS mode: the output is row-major (M0 = 1): lane owns output row `row`,
+// `chunks` groups of 16 columns starting at column col0; value = (hi << 8) + lo (+ old).
+__device__ __forceinline__ void epilogue_rows_dual(const TcParams& P, uint32_t taddr_hi,
+                                                   uint32_t taddr_lo, int64_t row, int64_t col0,
+                                                   int chunks) {
+  if (P.debug_flags & 2u) return;
+  const int64_t ncols = P.N1 * 32;
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t h[16], r[16];
+    tmem_ld16(taddr_hi + uint32_t(c * 16), h);
+    tmem_ld16(taddr_lo + uint32_t(c * 16), r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r[j] += h[j] << 8;
+    const int64_t col = col0 + c * 16;
+    if (row < P.M1 && col < ncols && !(P.debug_flags & 1u)) {
+      uint4* d4 = reinterpret_cast<uint4*>(P.out + (row * P.out_stride0 + col) * 4);
+      if (P.accumulate) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 old = d4[v];
+          r[4 * v + 0] += old.x; r[4 * v + 1] += old.y; r[4 * v + 2] += old.z; r[4 * v + 3] += old.w;
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        d4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+    }
+  }
+}
+
 // One stage's TMA loads for one operand. `c` holds the coordinates of box 0 for this k-block.
 template <bool PAIR>
 __device__ __forceinline__ void issue_operand_loads(const CUtensorMap* map, const OperandStage& st,
@@ -380,8 +413,8 @@ __device__ __forceinline__ void issue_operand_loads(const CUtensorMap* map, cons
 // All tcgen05.mma of one stage. Everything but the two stage addresses is loop-invariant and
 // lives in registers of the single issuing thread.
 struct MmaIssue {
-  uint32_t lo_a, lo_b, hi_a, hi_b, kadv_a, kadv_b, kbox_a, kbox_b, idesc;
-  int kboxes, mma_per_box;
+  uint32_t lo_a, lo_b, hi_a, hi_b, kadv_a, kadv_b, kbox_a, kbox_b, idesc, idesc2;
+  int kboxes, mma_per_box, dual;
 };
 __device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
   MmaIssue m;
@@ -390,8 +423,29 @@ __device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
   m.kadv_a = P.kadv_a; m.kadv_b = P.kadv_b;
   m.kbox_a = P.kbox_units_a; m.kbox_b = P.kbox_units_b;
   m.idesc = P.idesc; m.kboxes = P.kboxes; m.mma_per_box = P.mma_per_box;
+  m.idesc2 = P.idesc2; m.dual = P.dual;
   return m;
 }
+// Dual-LHS stage (s16u4s32): shared memory holds [high-byte plane | low-byte plane | RHS]; each K
+// slice feeds two MMAs that share the RHS descriptor and accumulate into two TMEM regions
+// (d_tmem and d_tmem + bn), recombined as hi*256 + lo by the epilogue.
+__device__ __forceinline__ void issue_stage_mmas_dual(const MmaIssue& m, uint32_t d_hi, uint32_t d_lo,
+                                                      uint32_t a_units, uint32_t b_units,
+                                                      bool first_kblock) {
+  uint32_t acc = first_kblock ? 0u : 1u;
+  uint32_t au = a_units, bu = b_units;
+  for (int j = 0; j < m.mma_per_box; ++j) {
+    const uint64_t da_hi = (uint64_t(m.hi_a) << 32) | uint64_t((au & 0x3FFFu) | m.lo_a);
+    const uint64_t da_lo = (uint64_t(m.hi_a) << 32) | uint64_t(((au + m.kbox_a) & 0x3FFFu) | m.lo_a);
+    const uint64_t db = (uint64_t(m.hi_b) << 32) | uint64_t((bu & 0x3FFFu) | m.lo_b);
+    tc_mma<true>(d_hi, da_hi, db, m.idesc, acc);
+    tc_mma<true>(d_lo, da_lo, db, m.idesc2, acc);
+    acc = 1u;
+    au += m.kadv_a;
+    bu += m.kadv_b;
+  }
+}
+
 template <bool IS_INT, bool PAIR>
 __device__ __forceinline__ void issue_stage_mmas(const MmaIssue& m, uint32_t d_tmem, uint32_t a_units,
                                                  uint32_t b_units, bool first_kblock) {
@@ -524,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn);
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn * (mi.dual ? 2 : 1));
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
             if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
@@ -535,7 +589,10 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           tc_fence_after();
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
           if (elect_one()) {
-            issue_stage_mmas<IS_INT, false>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            if (IS_INT && mi.dual)
+              issue_stage_mmas_dual(mi, d_tmem, d_tmem + uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            else
+              issue_stage_mmas<IS_INT, false>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs finish
             if (kb == num_kb - 1) tc_commit(smem_u32(&tmem_full_bar[buf]));  // accumulator complete
           }
@@ -563,36 +620,13 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
         break;
       }
       tc_fence_after();
-      const int64_t m1 = int64_t(mt) * (BM / 16) + (m_local >> 4);
-      const int m0 = m_local & 15;
-      const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
-      for (int c = 0; c < chunks; ++c) {
-        uint32_t r[16];
-        tmem_ld16(taddr0 + uint32_t(c * 16), r);
-        tmem_ld_wait();
-        const int64_t n1 = int64_t(nt) * chunks + c;
-        if (m1 < P.M1 && n1 < P.N1) {
-          uint4* dst = reinterpret_cast<uint4*>(
-              P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4);
-          if (P.accumulate) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const uint4 old = dst[v];
-              if (P.out_is_int) {
-                r[4 * v + 0] += old.x; r[4 * v + 1] += old.y;
-                r[4 * v + 2] += old.z; r[4 * v + 3] += old.w;
-              } else {
-                r[4 * v + 0] = __float_as_uint(__uint_as_float(r[4 * v + 0]) + __uint_as_float(old.x));
-                r[4 * v + 1] = __float_as_uint(__uint_as_float(r[4 * v + 1]) + __uint_as_float(old.y));
-                r[4 * v + 2] = __float_as_uint(__uint_as_float(r[4 * v + 2]) + __uint_as_float(old.z));
-                r[4 * v + 3] = __float_as_uint(__uint_as_float(r[4 * v + 3]) + __uint_as_float(old.w));
-              }
-            }
-          }
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            dst[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-        }
+      const int64_t row = int64_t(mt) * BM + m_local;
+      if (P.dual) {
+        const uint32_t t_hi = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * 2 * P.bn);
+        epilogue_rows_dual(P, t_hi, t_hi + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
+      } else {
+        const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
+        epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks);
       }
       tc_fence_before();
       __syncwarp();
@@ -919,6 +953,71 @@ int launch_retile(const char* lhs, int64_t lhs_stride_b, char* dst_a, int64_t ti
 }
 
 // ---------------------------------------------------------------------------------------
+// s16u4s32 pre-pass: byte planes for the LHS, byte-wide row-major weights for the RHS
+// ---------------------------------------------------------------------------------------
+// x = hi*256 + lo exactly, with hi the signed high byte and lo the unsigned low byte of the
+// s16, so sum(x*w) = 256*sum(hi*w) + sum(lo*w): two 8-bit tensor-core products. The LHS
+// [M][K1][1][8] (row-major M x K s16) becomes two row-major byte planes.
+__global__ void __launch_bounds__(256) split_s16_kernel(const char* __restrict__ lhs,
+                                                        int64_t lhs_stride_b, char* __restrict__ hi,
+                                                        char* __restrict__ lo, int64_t pitch_b,
+                                                        int64_t M, int64_t K1) {
+  const int64_t total = M * K1;
+  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t row = i / K1, k1 = i - row * K1;
+    const uint4 x = __ldg(reinterpret_cast<const uint4*>(lhs + row * lhs_stride_b) + k1);
+    const uint2 l = make_uint2(__byte_perm(x.x, x.y, 0x6420), __byte_perm(x.z, x.w, 0x6420));
+    const uint2 h = make_uint2(__byte_perm(x.x, x.y, 0x7531), __byte_perm(x.z, x.w, 0x7531));
+    *reinterpret_cast<uint2*>(lo + row * pitch_b + k1 * 8) = l;
+    *reinterpret_cast<uint2*>(hi + row * pitch_b + k1 * 8) = h;
+  }
+}
+
+// RHS [N1][K1][32][8 x u4] (tile = 128 bytes, low nibble = even k0) -> row-major u8
+// [N1*32][K1*8]. A block widens 64 k1 steps of one tile row through shared memory: contiguous
+// 16-byte loads, 16-byte stores of 512-byte row segments.
+__global__ void __launch_bounds__(256) unpack_u4_kernel(const char* __restrict__ rhs,
+                                                        int64_t rhs_stride_b, char* __restrict__ dst,
+                                                        int64_t pitch_b, int64_t K1, int kchunks) {
+  constexpr int KC = 64, PITCH = KC * 8 + 16;
+  __shared__ __align__(16) unsigned char sm[32 * PITCH];
+  const int64_t n1 = blockIdx.x / kchunks;
+  const int chunk = int(blockIdx.x - n1 * kchunks);
+  const int64_t k_base = int64_t(chunk) * KC;
+  const int kn = int(min(int64_t(KC), K1 - k_base));
+  const uint4* src = reinterpret_cast<const uint4*>(rhs + n1 * rhs_stride_b + k_base * 128);
+#pragma unroll 2
+  for (int v = threadIdx.x; v < kn * 8; v += blockDim.x) {
+    const int k = v >> 3, g = v & 7;
+    const uint4 w = __ldg(src + v);
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint32_t even = ws[r] & 0x0F0F0F0Fu, odd = (ws[r] >> 4) & 0x0F0F0F0Fu;
+      // bytes k0 = 0..7 in order: even0, odd0, even1, odd1, ...
+      const uint2 o = make_uint2(__byte_perm(even, odd, 0x5140), __byte_perm(even, odd, 0x7362));
+      *reinterpret_cast<uint2*>(sm + (4 * g + r) * PITCH + k * 8) = o;
+    }
+  }
+  __syncthreads();
+  const int row_bytes = kn * 8;
+  const int vec_per_row = row_bytes / 16;
+  for (int v = threadIdx.x; v < 32 * vec_per_row; v += blockDim.x) {
+    const int n0 = v / vec_per_row, kv = v - n0 * vec_per_row;
+    *reinterpret_cast<uint4*>(dst + (n1 * 32 + n0) * pitch_b + k_base * 8 + kv * 16) =
+        *reinterpret_cast<const uint4*>(sm + n0 * PITCH + kv * 16);
+  }
+  if (row_bytes & 15) {  // odd number of k1 in the last chunk: the final 8 bytes of each row
+    if (threadIdx.x < 32) {
+      const int n0 = threadIdx.x;
+      *reinterpret_cast<uint2*>(dst + (n1 * 32 + n0) * pitch_b + k_base * 8 + vec_per_row * 16) =
+          *reinterpret_cast<const uint2*>(sm + n0 * PITCH + vec_per_row * 16);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // host side: tensor maps, descriptors, launch
 // ---------------------------------------------------------------------------------------
 
@@ -1047,6 +1146,124 @@ bool encode_map(CUtensorMap* map, CUtensorMapDataType type, void* base, const ui
 
 }  // namespace
 
+// ---- s16u4s32 (M0 = 1, N0 = 32, K0 = 8) on the tensor cores ----------------------------------
+
+bool mmt4d_tc_s16u4_eligible(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) != IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) return false;
+  if (p->M0 != 1 || p->N0 != 32 || p->K0 != 8 || p->K < 1 || p->M < 1 || p->N < 1) return false;
+  const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * 2);
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset / 2);
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * 4);
+  if ((lhs | rhs | out) & 15) return false;
+  if ((p->lhs_stride0 * 2) % 16 || (p->rhs_stride0 / 2) % 16 || (p->out_stride0 * 4) % 16) return false;
+  if ((p->M + 127) / 128 * ((p->N + 0) / 1 + 1) > 0x3FFFFFFF) return false;
+  return true;
+}
+
+namespace {
+
+struct S16U4Layout {
+  int64_t pitch, plane_bytes, w_bytes;
+};
+S16U4Layout s16u4_layout(const iree_uk_mmt4d_params_t* p) {
+  S16U4Layout l;
+  l.pitch = round_up(p->K * 8, 128);
+  l.plane_bytes = round_up(p->M * l.pitch, 1024);
+  l.w_bytes = round_up(p->N * 32 * l.pitch, 1024);
+  return l;
+}
+
+int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes,
+                          cudaStream_t stream) {
+  if (!mmt4d_tc_s16u4_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
+  uint32_t* status = device_status_word();
+  if (!status) return IREE_UK_B200_CUDA_ERROR;
+  const S16U4Layout l = s16u4_layout(p);
+  if (!ws || ws_bytes < size_t(2 * l.plane_bytes + l.w_bytes)) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+  KernelTiming& timing = kernel_timing();
+  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  if (tev) cudaEventRecord(tev[0], stream);
+
+  const char* lhs = static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * 2;
+  const char* rhs = static_cast<const char*>(p->rhs_buffer) + p->rhs_offset / 2;
+  char* hi = static_cast<char*>(ws);
+  char* lo = hi + l.plane_bytes;
+  char* w8 = lo + l.plane_bytes;
+  {
+    const int64_t total = p->M * p->K;
+    const int64_t blocks = std::min<int64_t>((total + 255) / 256, 148 * 16);
+    split_s16_kernel<<<int(blocks), 256, 0, stream>>>(lhs, p->lhs_stride0 * 2, hi, lo, l.pitch, p->M, p->K);
+    const int64_t kchunks = (p->K + 63) / 64;
+    if (p->N * kchunks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
+    unpack_u4_kernel<<<int(p->N * kchunks), 256, 0, stream>>>(rhs, p->rhs_stride0 / 2, w8, l.pitch,
+                                                            p->K, int(kchunks));
+    if (cudaGetLastError() != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  }
+
+  TcParams P;
+  std::memset(&P, 0, sizeof P);
+  const int64_t kbytes = p->K * 8, ncols = p->N * 32;
+  const int bn = int(std::min<int64_t>(128, ncols));
+  const uint64_t da[3] = {uint64_t(kbytes), uint64_t(p->M), 2};
+  const uint64_t db[3] = {uint64_t(kbytes), uint64_t(ncols), 1};
+  const uint64_t sa[2] = {uint64_t(l.pitch), uint64_t(l.plane_bytes)};
+  const uint64_t sb[2] = {uint64_t(l.pitch), uint64_t(l.pitch) * uint64_t(ncols)};
+  const uint32_t ba[3] = {128, BM, 1};
+  const uint32_t bb[3] = {128, uint32_t(bn), 1};
+  if (!encode_map(&P.map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, hi, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_map(&P.map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, w8, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+    return IREE_UK_B200_CUDA_ERROR;
+  P.sa = {2, BM * 128, {128, 0, 0}, {0, BM, 0}, {0, 0, 1}};  // box 0: high plane, box 1: low plane
+  P.sb = {1, bn * 128, {128, 0, 0}, {0, bn, 0}, {0, 0, 0}};
+  P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
+  P.desc_lbo_a = P.desc_lbo_b = 1;
+  P.kadv_a = P.kadv_b = 2;
+  P.kbox_units_a = uint32_t(BM * 128) >> 4;  // distance from the high to the low plane tile
+  P.kbox_units_b = 0;
+  // accumulate s32; LHS high bytes signed, low bytes unsigned; weights unsigned
+  const uint32_t common = (2u << 4) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+  P.idesc = common | (1u << 7);
+  P.idesc2 = common;
+  P.dual = 1;
+  P.kboxes = 1;
+  P.mma_per_box = 4;
+  P.stage_bytes_a = 2 * BM * 128;
+  P.stage_bytes_b = bn * 128;
+  P.num_kb = int((kbytes + 127) / 128);
+  P.bn = bn;
+  P.m_tiles = int((p->M + BM - 1) / BM);
+  P.n_tiles = int((ncols + bn - 1) / bn);
+  P.group_m = std::min(P.m_tiles, 16);
+  P.out = static_cast<char*>(p->out_buffer) + p->out_offset * 4;
+  P.out_stride0 = p->out_stride0;
+  P.M1 = p->M;
+  P.N1 = p->N;
+  P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
+  P.out_is_int = 1;
+  P.status = status;
+  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
+  const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
+  P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (tev) cudaEventRecord(tev[1], stream);
+  if (cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           int(smem)) != cudaSuccess)
+    return IREE_UK_B200_CUDA_ERROR;
+  const int grid = std::min(P.m_tiles * P.n_tiles, sms);
+  mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
+  if (tev) {
+    cudaEventRecord(tev[2], stream);
+    ++timing.calls;
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace
+
 bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti)) return false;
@@ -1064,6 +1281,11 @@ bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
 }
 
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) {
+    if (p->M0 != 1 || p->N0 != 32 || p->K0 != 8 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
+    const S16U4Layout l = s16u4_layout(p);
+    return size_t(2 * l.plane_bytes + l.w_bytes);
+  }
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti)) return 0;
   if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
@@ -1082,6 +1304,8 @@ bool pair_kernel_pays(const iree_uk_mmt4d_params_t* p) {
 
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
+    return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || !mmt4d_tc_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
   uint32_t* status = device_status_word();

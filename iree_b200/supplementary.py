@@ -142,6 +142,12 @@ def run(peaks, only=None, custom=None):
         r["frac_of_bf16_burst"] = r["tops"] / bf16_peak
         r["frac_of_spec_2250"] = r["tops"] / 2250.0
         res[k] = r
+    # s16u4s32 with many rows (prefill-shaped): two 8-bit tensor-core products per s16 x u4
+    if want("mmt4d_s16u4s32_prefill_8192x14336x4096"):
+        k, r = _mmt4d_case("mmt4d_s16u4s32_prefill_8192x14336x4096", abi.MMT4D_S16U4S32, 8192,
+                           448, 512, 1, 32, 8, peaks, None)
+        r["frac_of_2x_bf16_burst_counting_both_byte_products"] = 2 * r["tops"] / (2 * bf16_peak)
+        res[k] = r
     # decode GEMV s16u4s32: bytes are the algorithmic figure (weights + vector + output)
     if want("mmt4d_s16u4s32_gemv_1x14336x4096"):
         k, r = _mmt4d_case("mmt4d_s16u4s32_gemv_1x14336x4096", abi.MMT4D_S16U4S32, 1, 448, 512,

@@ -99,6 +99,11 @@ def test_mmt4d_info_and_workspace_size():
     assert uk.mmt4d_info(16, 16, 2, abi.MMT4D_BF16BF16F32) == 1
     assert uk.mmt4d_info(9, 6, 3, abi.MMT4D_S8S8S32) == 0
     assert uk.mmt4d_info(16, 16, 1, abi.MMT4D_F32F32F32) == 0
+    assert uk.mmt4d_info(1, 32, 8, abi.MMT4D_S16U4S32) == 1
+    big = _mmt4d(abi.MMT4D_S16U4S32, M=64, N=4, K=8, M0=1, N0=32, K0=8)
+    assert uk.mmt4d_path(big) == abi.PATH_TCGEN05_RETILE
+    assert uk.mmt4d_path(big, with_workspace=False) == abi.PATH_GEMV
+    assert uk.mmt4d_workspace_size(big) == 2 * 64 * 128 + 4 * 32 * 128
     p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
     # row-major copies of both operands, 128-byte row pitch
     assert uk.mmt4d_workspace_size(p) == (512 + 1792) * 16 * 4096 * 2 * 2

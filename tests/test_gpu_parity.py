@@ -94,6 +94,24 @@ def test_mmt4d_s16u4_gemv_path():
         assert np.array_equal(got, G.oracle_mmt4d(case)), (M, N, K, acc)
 
 
+@pytest.mark.parametrize("shape", [(32, 4, 16), (128, 8, 64), (200, 7, 33), (129, 5, 1),
+                                   (256, 448, 40)], ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_s16u4_tensor_core_path(shape, accumulate):
+    """s16u4s32 1x32x8 with many rows: signed-high / unsigned-low byte planes against u8 weights
+    on the tensor cores, recombined as hi*256 + lo. Full-range s16 values, bit-exact."""
+    M, N, K = shape
+    case = cases.Mmt4dCase(abi.MMT4D_S16U4S32, 1, 32, 8, M, N, K, accumulate, seed=M + K,
+                           mode="normal", loose=False)
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    assert np.array_equal(got, G.oracle_mmt4d(case)), shape
+    # the same problem without scratch runs the weight-streaming kernel and agrees
+    got2, path2 = G.run_mmt4d_case(case, use_workspace=False)
+    assert path2 == abi.PATH_GEMV
+    assert np.array_equal(got2, got)
+
+
 def test_mmt4d_int_wraparound():
     """int32 sums wrap modulo 2^32 like the reference's (extreme s8 values, long K, and an
     initial accumulator near INT32_MAX)."""
