@@ -277,6 +277,25 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_flat(
     int32_t K0, uint32_t flags, const uint64_t* cpu_data, void* workspace,
     size_t workspace_bytes, void* cu_stream);
 
+/* Device bytes iree_uk_b200_mmt4d_host needs for `params` (device copies of both operands and
+ * of the output, plus the tensor-core scratch of one chunk); 0 when the parameters are rejected. */
+IREE_UK_B200_EXPORT size_t
+iree_uk_b200_mmt4d_host_arena_size(const iree_uk_mmt4d_params_t* params);
+
+/* iree_uk_mmt4d_p (ukernel/mmt4d.c:115-141) with the reference's own calling convention for
+ * the buffers: lhs_buffer, rhs_buffer and out_buffer are HOST pointers, as in the reference.
+ * The operands are copied to the device, the contraction runs on the kernels of this library
+ * and the result is copied back into out_buffer; the RHS tile rows are processed in up to 8
+ * chunks so that host-to-device copies, kernels and device-to-host copies overlap. All device
+ * memory is the caller's `device_arena` (256-byte aligned, at least
+ * iree_uk_b200_mmt4d_host_arena_size bytes, in use until the work has completed). The call
+ * returns once everything is enqueued; out_buffer is complete when work enqueued on `cu_stream`
+ * after this call runs (or after synchronising it). Host buffers should be page-locked, or the
+ * copies will not overlap. Uses three internal streams per device, created on first use. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_host(const iree_uk_mmt4d_params_t* params,
+                                                void* device_arena, size_t arena_bytes,
+                                                void* cu_stream);
+
 /* Replaces iree_uk_mmt4d_info (ukernel/mmt4d.h:25-27, mmt4d.c:143-149): bit 0 is set when
  * a tensor-core (tcgen05) kernel exists for this (types, M0, N0, K0). */
 IREE_UK_B200_EXPORT uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0,

@@ -44,7 +44,6 @@ int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path)
   if (p->M == 0 || p->N == 0 || (p->K == 0 && acc)) { *path = Mmt4dPath::None; return 0; }
   Mmt4dTypes t;
   mmt4d_types(p->flags, &t);
-  if (elem_bits(t.out) != 32) return IREE_UK_B200_UNSUPPORTED;  // f16/bf16 outputs: not served yet
   // A zero-sized inner tile addresses no output element.
   if (p->M0 == 0 || p->N0 == 0) { *path = Mmt4dPath::None; return 0; }
   if (p->K == 0 || p->K0 == 0) { *path = Mmt4dPath::ZeroFill; return 0; }

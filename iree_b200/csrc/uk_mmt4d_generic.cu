@@ -108,6 +108,52 @@ __global__ void __launch_bounds__(256) mmt4d_generic_kernel(GenericArgs a) {
   }
 }
 
+// f16f16f16 / bf16bf16bf16 (ukernel/mmt4d_tile_generic.c:226-286, :316-376): without
+// SKIP_INTERMEDIATE_ROUNDINGS the accumulator is 16-bit and rounded (to nearest even) after
+// every multiply-add; with it the sum stays in f32 and is rounded once at the end. Multiply
+// and add are separate roundings, as in the reference's portable code.
+template <bool IS_BF16>
+__global__ void __launch_bounds__(256) mmt4d_generic_out16_kernel(GenericArgs a, int skip_round) {
+  auto to_f32 = [](uint16_t v) -> float {
+    if (IS_BF16) return __uint_as_float(uint32_t(v) << 16);
+    return __half2float(__ushort_as_half(v));
+  };
+  auto from_f32 = [](float f) -> uint16_t {
+    if (IS_BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    return __half_as_ushort(__float2half_rn(f));
+  };
+  const int64_t tile_elems = int64_t(a.M0) * a.N0;
+  const int64_t total = a.M * a.N * tile_elems;
+  const int64_t lhs_k_step = int64_t(a.M0) * a.K0, rhs_k_step = int64_t(a.N0) * a.K0;
+  for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total;
+       idx += int64_t(gridDim.x) * blockDim.x) {
+    const int64_t tile = idx / tile_elems;
+    const int32_t e = int32_t(idx - tile * tile_elems);
+    const int64_t i = tile / a.N, j = tile - i * a.N;
+    const int32_t i0 = e / a.N0, j0 = e - i0 * a.N0;
+    const uint16_t* lp = reinterpret_cast<const uint16_t*>(a.lhs + i * a.lhs_stride_b);
+    const uint16_t* rp = reinterpret_cast<const uint16_t*>(a.rhs + j * a.rhs_stride_b);
+    uint16_t* op = reinterpret_cast<uint16_t*>(a.out) + i * a.out_stride0 + j * tile_elems + e;
+    uint16_t acc16 = a.accumulate ? *op : uint16_t(0);
+    float acc32 = to_f32(acc16);
+    int64_t le = int64_t(i0) * a.K0, re = int64_t(j0) * a.K0;
+    for (int64_t k = 0; k < a.K; ++k) {
+      for (int32_t k0 = 0; k0 < a.K0; ++k0) {
+        const float prod = __fmul_rn(to_f32(lp[le + k0]), to_f32(rp[re + k0]));
+        if (skip_round) {
+          acc32 = __fadd_rn(acc32, prod);
+        } else {
+          acc16 = from_f32(__fadd_rn(to_f32(acc16), prod));
+        }
+      }
+      le += lhs_k_step;
+      re += rhs_k_step;
+    }
+    *op = skip_round ? from_f32(acc32) : acc16;
+  }
+}
+
+template <typename T>
 __global__ void __launch_bounds__(256) mmt4d_zero_fill_kernel(char* out, int64_t out_stride0,
                                                               int64_t M, int64_t row_elems) {
   // K == 0 without ACCUMULATE: every addressed out tile becomes zero, stride gaps are left
@@ -116,7 +162,7 @@ __global__ void __launch_bounds__(256) mmt4d_zero_fill_kernel(char* out, int64_t
   for (int64_t idx = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; idx < total;
        idx += int64_t(gridDim.x) * blockDim.x) {
     const int64_t i = idx / row_elems, c = idx - i * row_elems;
-    reinterpret_cast<uint32_t*>(out)[i * out_stride0 + c] = 0u;
+    reinterpret_cast<T*>(out)[i * out_stride0 + c] = T(0);
   }
 }
 
@@ -252,7 +298,19 @@ int launch_mmt4d_generic(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
     case IREE_UK_FLAG_MMT4D_TYPE_S16U4S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S16U4S32>(a, stream);
     case IREE_UK_FLAG_MMT4D_TYPE_S16S8S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S16S8S32>(a, stream);
     case IREE_UK_FLAG_MMT4D_TYPE_S8S4S32: return launch_generic_typed<IREE_UK_FLAG_MMT4D_TYPE_S8S4S32>(a, stream);
-    default: return IREE_UK_B200_UNSUPPORTED;  // 16-bit-output triples: not served yet
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F16:
+    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16BF16: {
+      const int64_t total = a.M * a.N * a.M0 * a.N0;
+      if (total <= 0) return IREE_UK_B200_OK;
+      const int64_t blocks = std::min<int64_t>((total + 255) / 256, 148 * 64);
+      const int skip = (p->flags & IREE_UK_FLAG_MMT4D_SKIP_INTERMEDIATE_ROUNDINGS) ? 1 : 0;
+      if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_F16F16F16)
+        mmt4d_generic_out16_kernel<false><<<int(blocks), 256, 0, stream>>>(a, skip);
+      else
+        mmt4d_generic_out16_kernel<true><<<int(blocks), 256, 0, stream>>>(a, skip);
+      return cuda_status(cudaGetLastError());
+    }
+    default: return IREE_UK_B200_UNSUPPORTED;
   }
 }
 
@@ -261,12 +319,14 @@ int launch_mmt4d_zero_fill(const iree_uk_mmt4d_params_t* p, cudaStream_t stream)
   if (!fill_args(p, &a)) return IREE_UK_B200_INVALID_ARGUMENT;
   Mmt4dTypes t;
   mmt4d_types(p->flags, &t);
-  if (elem_bits(t.out) != 32) return IREE_UK_B200_UNSUPPORTED;
   const int64_t row_elems = a.N * a.M0 * a.N0;
   const int64_t total = a.M * row_elems;
   if (total <= 0) return IREE_UK_B200_OK;
   const int64_t blocks = std::min<int64_t>((total + 255) / 256, 148 * 16);
-  mmt4d_zero_fill_kernel<<<int(blocks), 256, 0, stream>>>(a.out, a.out_stride0, a.M, row_elems);
+  if (elem_bits(t.out) == 32)
+    mmt4d_zero_fill_kernel<uint32_t><<<int(blocks), 256, 0, stream>>>(a.out, a.out_stride0, a.M, row_elems);
+  else
+    mmt4d_zero_fill_kernel<uint16_t><<<int(blocks), 256, 0, stream>>>(a.out, a.out_stride0, a.M, row_elems);
   return cuda_status(cudaGetLastError());
 }
 

@@ -48,6 +48,21 @@ def mmt4d(params, stream=None, workspace=None):
                                          workspace.numel() * workspace.element_size(), s), "mmt4d")
 
 
+def mmt4d_host_arena_size(params):
+    """Device bytes ``mmt4d_host`` needs for ``params`` (host pointers)."""
+    return int(lib.iree_uk_b200_mmt4d_host_arena_size(C.addressof(params)))
+
+
+def mmt4d_host(params, arena, stream=None):
+    """``iree_uk_mmt4d_p`` with HOST buffers in ``params`` (the reference's own convention):
+    copies in, computes on the device, copies the result back, pipelined over chunks of RHS tile
+    rows. ``arena``: a torch uint8 CUDA tensor of at least ``mmt4d_host_arena_size(params)``
+    bytes. Asynchronous: synchronise the stream before reading the output."""
+    _check(lib.iree_uk_b200_mmt4d_host(C.addressof(params), arena.data_ptr(),
+                                       arena.numel() * arena.element_size(),
+                                       _stream_handle(stream)), "mmt4d_host")
+
+
 STATIC_SCRATCH_BYTES = 32 << 20
 
 

@@ -110,6 +110,8 @@ MMT4D_KINDS = {
     abi.MMT4D_S8S8S32: ("s8", "s8", "s32"),
     abi.MMT4D_F16F16F32: ("f16", "f16", "f32"),
     abi.MMT4D_BF16BF16F32: ("bf16", "bf16", "f32"),
+    abi.MMT4D_F16F16F16: ("f16", "f16", "f16"),
+    abi.MMT4D_BF16BF16BF16: ("bf16", "bf16", "bf16"),
     abi.MMT4D_S16S16S32: ("s16", "s16", "s32"),
     abi.MMT4D_S16U4S32: ("s16", "u4", "s32"),
     abi.MMT4D_S16S8S32: ("s16", "s8", "s32"),
@@ -131,6 +133,14 @@ MMT4D_TILES = [
     (abi.MMT4D_S8S8S32, 8, 8, 2), (abi.MMT4D_F16F16F32, 8, 8, 1),
     (abi.MMT4D_S8S8S32, 16, 16, 2), (abi.MMT4D_F16F16F32, 16, 16, 1),
     (abi.MMT4D_BF16BF16F32, 16, 16, 2), (abi.MMT4D_S16U4S32, 1, 32, 8),
+]
+# 16-bit-output triples: (type | extra flags, M0, N0, K0), mmt4d_test.c:552-554,583-596; the
+# x86 paths exist only with SKIP_INTERMEDIATE_ROUNDINGS.
+MMT4D_TILES_16BIT_OUT = [
+    (abi.MMT4D_F16F16F16, 3, 5, 8), (abi.MMT4D_BF16BF16BF16, 2, 9, 3),
+    (abi.MMT4D_F16F16F16 | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS, 8, 8, 1),
+    (abi.MMT4D_F16F16F16 | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS, 16, 16, 1),
+    (abi.MMT4D_BF16BF16BF16 | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS, 16, 16, 2),
 ]
 # Further triples the generic kernel serves (mmt4d_test.c:545-551).
 MMT4D_TILES_EXTRA = [
@@ -164,6 +174,8 @@ class Mmt4dCase:
 
     def __init__(self, type_flag, M0, N0, K0, M, N, K, accumulate, seed=0, mode="exact",
                  loose=True, extra_flags=0):
+        extra_flags |= type_flag & ~0xFF
+        type_flag &= 0xFF
         self.kinds = MMT4D_KINDS[type_flag]
         lb, rb, ob = (KIND_BITS[k] for k in self.kinds)
         self.bits = (lb, rb, ob)
@@ -354,6 +366,8 @@ def all_mmt4d_cases(tiles=None, shapes=None, mode="exact"):
     for type_flag, M0, N0, K0 in (tiles or MMT4D_TILES):
         for m0 in narrowed_m0(M0):
             for (M, N, K) in (shapes or MMT4D_SHAPES):
+                if (type_flag & 0xFF) == abi.MMT4D_BF16BF16BF16 and K == 1000:
+                    K = 100  # max_reduction_size for bf16 outputs, mmt4d_test.c:453-454
                 for acc in (0, 1):
                     seed += 1
                     yield Mmt4dCase(type_flag, m0, N0, K0, M, N, K, acc, seed, mode)

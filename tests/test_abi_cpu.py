@@ -87,10 +87,10 @@ def test_mmt4d_early_outs_and_paths():
     p.lhs_offset = 1
     assert uk.mmt4d_path(p) == abi.PATH_GENERIC
     assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F32F32F32, K0=1)) == abi.PATH_GENERIC
-    # 16-bit-output triples are valid for the reference but not served here
-    with pytest.raises(uk.UkernelError) as e:
-        uk.mmt4d_path(_mmt4d(abi.MMT4D_F16F16F16, K0=1))
-    assert e.value.status == abi.UNSUPPORTED
+    # 16-bit-output triples run on the generic kernel
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F16F16F16, K0=1)) == abi.PATH_GENERIC
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_BF16BF16BF16 | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS,
+                                K=0)) == abi.PATH_ZERO_FILL
 
 
 def test_mmt4d_info_and_workspace_size():

@@ -39,6 +39,19 @@ def test_mmt4d_reference_case_list(tile):
     assert n > 0
 
 
+@pytest.mark.parametrize("tile", cases.MMT4D_TILES_16BIT_OUT,
+                         ids=lambda t: "t%x_%dx%dx%d" % t)
+def test_mmt4d_16bit_output_triples(tile):
+    """f16f16f16 / bf16bf16bf16 with and without SKIP_INTERMEDIATE_ROUNDINGS on the reference
+    tests' shapes and small-integer values: bit-exact, rounding after every step included."""
+    n = 0
+    for case in cases.all_mmt4d_cases([tile]):
+        got, _ = G.run_mmt4d_case(case)
+        assert np.array_equal(got, G.oracle_mmt4d(case)), case.label()
+        n += 1
+    assert n > 0
+
+
 @pytest.mark.parametrize("tile", [(abi.MMT4D_S8S8S32, 16, 16, 2), (abi.MMT4D_F16F16F32, 16, 16, 1),
                                   (abi.MMT4D_BF16BF16F32, 16, 16, 2),
                                   (abi.MMT4D_S8S8S32, 16, 16, 8), (abi.MMT4D_BF16BF16F32, 16, 16, 1)],
@@ -231,3 +244,30 @@ def test_interleave_slabs_kernel():
     uk.interleave_slabs(g, out, M, N, tile, 4, world)
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy().reshape(M, N, tile), want)
+
+
+@pytest.mark.parametrize("spec", [
+    (abi.MMT4D_S8S8S32, 16, 16, 2, 24, 40, 64, 1, "exact"),
+    (abi.MMT4D_BF16BF16F32, 16, 16, 2, 9, 17, 33, 0, "exact"),
+    (abi.MMT4D_S16U4S32, 1, 32, 8, 40, 9, 16, 1, "normal"),
+    (abi.MMT4D_S8S8S32, 9, 6, 3, 5, 7, 13, 1, "exact"),
+    (abi.MMT4D_F16F16F16, 3, 5, 8, 5, 3, 4, 0, "exact"),
+    (abi.MMT4D_S8S8S32, 16, 16, 2, 3, 5, 0, 0, "exact"),
+], ids=lambda s: "t%x_%dx%dx%d_%dx%dx%d" % s[:7])
+def test_mmt4d_host_buffers(spec):
+    """The host-pointer entry point (the reference's own calling convention): loose strides and
+    offsets on the host side, chunked and pipelined on the device, whole host output buffer
+    bit-identical to the oracle's."""
+    import torch
+    from iree_b200 import ukernel as uk
+    t, M0, N0, K0, M, N, K, acc, mode = spec
+    case = cases.Mmt4dCase(t, M0, N0, K0, M, N, K, acc, seed=41, mode=mode, loose=True)
+    want = G.oracle_mmt4d(case)
+    lhs = torch.from_numpy(case.lhs.copy()).pin_memory()
+    rhs = torch.from_numpy(case.rhs.copy()).pin_memory()
+    out = torch.from_numpy(case.out_init.copy()).pin_memory()
+    p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+    arena = torch.empty(max(uk.mmt4d_host_arena_size(p), 256), dtype=torch.uint8, device="cuda")
+    uk.mmt4d_host(p, arena)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.numpy(), want)

@@ -46,7 +46,8 @@ def test_oracle_matches_reference_mmt4d_case_list():
     """Whole-buffer equality on tools/mmt4d_test.c's shapes x tiles x narrowed M0 x
     accumulate, against both the ISA-specific and the portable reference code paths."""
     n = 0
-    for c in cases.all_mmt4d_cases(cases.MMT4D_TILES + cases.MMT4D_TILES_EXTRA):
+    for c in cases.all_mmt4d_cases(cases.MMT4D_TILES + cases.MMT4D_TILES_EXTRA +
+                                   cases.MMT4D_TILES_16BIT_OUT):
         want = c.out_init.copy()
         oracle.mmt4d(c.params(c.lhs, c.rhs, want))
         for feat in ("host", "none"):
