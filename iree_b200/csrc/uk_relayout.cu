@@ -13,6 +13,9 @@
 // Semantics follow iree_uk_pack_p / iree_uk_unpack_p (ukernel/pack.c:254-322,
 // ukernel/unpack.c:190-257): opaque elements of 1, 2 or 4 bytes; padding writes the low
 // element-size bytes of padding_value; unpack never writes outside out_size0 x out_size1.
+#include <algorithm>
+#include <cstdlib>
+
 #include "uk_common.h"
 
 namespace uk {
