@@ -882,6 +882,38 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOp
   }
   __syncthreads();
   // store: 16 rows x kn granules; a thread builds 16 bytes = GV consecutive k1 of one row
+  if (G == 2) {
+    // 2-byte granules: a 32-bit shared-memory word holds one k of two neighbouring rows, so a
+    // thread reads 8 words (8 k) and emits the 16-byte vectors of both rows: half the
+    // shared-memory loads of the one-row-at-a-time scheme below.
+    const int full = kn / GV;  // whole vectors per row
+    const int full8 = (full + 7) & ~7;
+#pragma unroll 2
+    for (int v = threadIdx.x; v < 8 * full8; v += blockDim.x) {
+      const int rp = (v >> 3) & 7, kv = ((v >> 6) << 3) | (v & 7);
+      if (kv >= full) continue;
+      const int k0 = kv * GV;
+      uint32_t x[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        x[j] = *reinterpret_cast<const uint32_t*>(sm + (k0 + j) * PITCH + rp * 4);
+      uint4 even, odd;
+      even.x = __byte_perm(x[0], x[1], 0x5410); odd.x = __byte_perm(x[0], x[1], 0x7632);
+      even.y = __byte_perm(x[2], x[3], 0x5410); odd.y = __byte_perm(x[2], x[3], 0x7632);
+      even.z = __byte_perm(x[4], x[5], 0x5410); odd.z = __byte_perm(x[4], x[5], 0x7632);
+      even.w = __byte_perm(x[6], x[7], 0x5410); odd.w = __byte_perm(x[6], x[7], 0x7632);
+      char* dp = dst + (tile * 16 + 2 * rp) * dst_pitch_b + (k_base + k0) * G;
+      *reinterpret_cast<uint4*>(dp) = even;
+      *reinterpret_cast<uint4*>(dp + dst_pitch_b) = odd;
+    }
+    const int rem = kn - full * GV;  // trailing k of a ragged last chunk
+    for (int e = threadIdx.x; e < 16 * rem; e += blockDim.x) {
+      const int r = e / rem, k = full * GV + (e - r * rem);
+      *reinterpret_cast<uint16_t*>(dst + (tile * 16 + r) * dst_pitch_b + (k_base + k) * G) =
+          *reinterpret_cast<const uint16_t*>(sm + k * PITCH + r * G);
+    }
+    return;
+  }
   // Lane mapping: 8 consecutive vectors of a row (128 bytes), then the next row; keeps the
   // shared-memory reads spread over banks and the global stores in 128-byte pieces.
   const int vec_per_row = (kn + GV - 1) / GV;
