@@ -53,6 +53,9 @@ int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path)
     if (have_ws && p->M >= 32 && mmt4d_tc_s16u4_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
     if (mmt4d_gemv_s16u4_eligible(p)) { *path = Mmt4dPath::Gemv; return 0; }
     if (have_ws && mmt4d_tc_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
+    // Without scratch, a 16-bit K0 = 1 operand ([tile][K1][16]) can still be read by TMA as an
+    // MN-major tensor-core operand; K0 = 2 operands cannot and fall to the generic kernel.
+    if (!have_ws && mmt4d_tc_direct_eligible(p)) { *path = Mmt4dPath::Tc; return 0; }
   }
   *path = Mmt4dPath::Generic;
   return 0;
@@ -80,6 +83,7 @@ int run_mmt4d(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, bool h
     case Mmt4dPath::ZeroFill: return launch_mmt4d_zero_fill(p, stream);
     case Mmt4dPath::Gemv: return launch_mmt4d_gemv_s16u4(p, stream);
     case Mmt4dPath::TcRetile: return launch_mmt4d_tc(p, ws, ws_bytes, kTcVariantDefault, stream);
+    case Mmt4dPath::Tc: return launch_mmt4d_tc(p, nullptr, 0, kTcVariantDirect, stream);
     default: return launch_mmt4d_generic(p, stream);
   }
 }

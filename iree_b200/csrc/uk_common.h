@@ -55,6 +55,9 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream);
 constexpr int kTcVariantDefault = 0;
+constexpr int kTcVariantDirect = 3;  // MN-major, 32-byte swizzle, straight from the operand
+// f16f16f32 / bf16bf16f32 with M0 = N0 = 16 and K0 = 1: served by the tensor cores without scratch.
+bool mmt4d_tc_direct_eligible(const iree_uk_mmt4d_params_t* p);
 
 int launch_pack_generic(const iree_uk_pack_params_t* p, cudaStream_t stream);
 int launch_unpack_generic(const iree_uk_unpack_params_t* p, cudaStream_t stream);

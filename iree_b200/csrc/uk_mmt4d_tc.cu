@@ -78,7 +78,8 @@ struct TcParams {
   int32_t accumulate;
   int32_t out_is_int;
   int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
-  uint32_t debug_flags;  // experiments only: 1 = no output stores, 2 = no TMEM reads, 4 = no TMA loads
+  uint32_t debug_flags;  // experiments only: 1 = no output stores, 2 = no TMEM reads, 4 = no TMA
+                         // loads, 8 = the producer never fills a stage (exercises the bounded waits)
   uint32_t* status;
 };
 
@@ -530,7 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           }
           const uint32_t bar = smem_u32(&full_bar[stage]);
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
-          if (elect_one()) {
+          const bool starve = (P.debug_flags & 8u) != 0;  // test hook: nothing ever arrives
+          if (!starve && elect_one()) {
             if (P.debug_flags & 4u) {
               mbar_arrive(bar);
             } else {
@@ -542,7 +544,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           __syncwarp();
 #pragma unroll
           for (int i = 0; i < 3; ++i) { ca[i] += sa_st.kstep[i]; cb[i] += sb_st.kstep[i]; }
-          ++issued;
+          if (!starve) ++issued;
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
       }
@@ -1310,6 +1312,11 @@ bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
     return false;
   if ((p->M + 7) / 8 * ((p->N + 3) / 4) > 0x3FFFFFFF) return false;
   return true;
+}
+
+bool mmt4d_tc_direct_eligible(const iree_uk_mmt4d_params_t* p) {
+  TypeInfo ti;
+  return tc_type_info(p->flags, &ti) && ti.es == 2 && p->K0 == 1 && mmt4d_tc_eligible(p);
 }
 
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {

@@ -81,6 +81,9 @@ def test_mmt4d_early_outs_and_paths():
     assert uk.mmt4d_path(_mmt4d(K=0)) == abi.PATH_ZERO_FILL
     # without a workspace the tensor-core path is not taken
     assert uk.mmt4d_path(_mmt4d(), with_workspace=False) == abi.PATH_GENERIC
+    # ... except for 16-bit K0 = 1 operands, which TMA can stage as they are
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F16F16F32, K0=1), with_workspace=False) == abi.PATH_TCGEN05
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_BF16BF16F32, K0=2), with_workspace=False) == abi.PATH_GENERIC
     # odd tile shapes and misaligned operands go to the generic kernel
     assert uk.mmt4d_path(_mmt4d(M0=9, N0=6, K0=3)) == abi.PATH_GENERIC
     p = _mmt4d()

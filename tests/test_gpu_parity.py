@@ -271,3 +271,55 @@ def test_mmt4d_host_buffers(spec):
     uk.mmt4d_host(p, arena)
     torch.cuda.synchronize()
     assert np.array_equal(out.numpy(), want)
+
+
+@pytest.mark.parametrize("t", [abi.MMT4D_F16F16F32, abi.MMT4D_BF16BF16F32], ids=["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 1, 1), (8, 16, 64), (9, 17, 65), (24, 40, 31), (16, 32, 200)],
+                         ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_tensor_core_without_workspace(t, shape, accumulate):
+    """16-bit operands with K0 = 1 reach the tensor cores with no scratch at all: TMA stages
+    the [tile][K1][16] panels as MN-major operands."""
+    M, N, K = shape
+    case = cases.Mmt4dCase(t, 16, 16, 1, M, N, K, accumulate, seed=17, mode="exact", loose=False)
+    got, path = G.run_mmt4d_case(case, use_workspace=False)
+    assert path == abi.PATH_TCGEN05
+    assert np.array_equal(got, G.oracle_mmt4d(case)), case.label()
+
+
+def test_bounded_waits_report_a_timeout_instead_of_hanging():
+    """Failure detection without faulting the GPU: a test hook makes the TMA producer never fill
+    a stage, so the MMA warp's wait on the full barrier runs out (about a second); the kernel
+    must record the timeout, return, leave the context usable, and the next call must be
+    correct. Runs in a child process because the hook is read from the environment."""
+    import subprocess
+    import sys
+    code = r"""
+import os, sys
+os.environ["IREE_UK_B200_DEBUG"] = "1"
+os.environ["IREE_UK_B200_DEBUG_FLAGS"] = "8"
+sys.path.insert(0, %r)
+import numpy as np, torch
+import oracle
+from oracle import cases
+from iree_b200 import abi, ukernel as uk
+case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 64, 0, seed=5, loose=False)
+def run():
+    lhs, rhs, out = (torch.from_numpy(x).cuda() for x in (case.lhs, case.rhs, case.out_init))
+    p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+    ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda")
+    assert uk.mmt4d_path(p, True) == abi.PATH_TCGEN05_RETILE
+    uk.mmt4d(p, workspace=ws)
+    st, detail = uk.device_status()
+    return st, detail, out.cpu().numpy()
+st, detail, _ = run()
+assert st == abi.DEVICE_TIMEOUT and detail != 0, (st, detail)
+os.environ["IREE_UK_B200_DEBUG_FLAGS"] = "0"
+st, detail, got = run()
+assert st == abi.OK and detail == 0, (st, detail)
+want = case.out_init.copy(); oracle.mmt4d(case.params(case.lhs, case.rhs, want))
+assert np.array_equal(got, want)
+print("TIMEOUT_REPORTED_AND_RECOVERED")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
+    assert "TIMEOUT_REPORTED_AND_RECOVERED" in r.stdout, r.stdout + r.stderr
