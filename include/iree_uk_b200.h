@@ -277,6 +277,43 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_flat(
     int32_t K0, uint32_t flags, const uint64_t* cpu_data, void* workspace,
     size_t workspace_bytes, void* cu_stream);
 
+/* Row-major matmul: the chain of iree_uk_e2e_matmul (ukernel/tools/e2e_matmul_benchmark.c:173-300:
+ * pack LHS, pack RHS with TRANSPOSE_INNER|TRANSPOSE_OUTER, pack the accumulator, mmt4d, unpack)
+ * as one operation on row-major operands, with no packed copy of the LHS or of the result.
+ * lhs is [M][K], rhs is [K][N], out is [M][N]; M, N, K count ELEMENTS; offsets and strides are
+ * in elements of the respective buffer; padding is zero as in the chain. `flags` is one of the
+ * tensor-core type triples (IREE_UK_FLAG_MMT4D_TYPE_S8S8S32, _F16F16F32, _BF16BF16F32),
+ * optionally | IREE_UK_FLAG_MMT4D_ACCUMULATE (out holds the accumulator on entry). The result
+ * equals that of the chain for any tile sizes: exactly for s8s8s32, up to the order of the f32
+ * additions for the float triples. */
+typedef struct iree_uk_b200_matmul_params_t {
+  const void* lhs_buffer;
+  iree_uk_index_t lhs_offset;
+  iree_uk_index_t lhs_stride0;
+  const void* rhs_buffer;
+  iree_uk_index_t rhs_offset;
+  iree_uk_index_t rhs_stride0;
+  void* out_buffer;
+  iree_uk_index_t out_offset;
+  iree_uk_index_t out_stride0;
+  iree_uk_index_t M;
+  iree_uk_index_t N;
+  iree_uk_index_t K;
+  uint32_t flags;
+} iree_uk_b200_matmul_params_t;
+
+/* Scratch bytes iree_uk_b200_matmul needs (a K-major copy of the RHS, and room for a copy of
+ * the LHS that is used only when the LHS base or row pitch is not 16-byte aligned); 0 when the
+ * parameters are rejected. */
+IREE_UK_B200_EXPORT size_t
+iree_uk_b200_matmul_workspace_size(const iree_uk_b200_matmul_params_t* params);
+
+/* Enqueues the matmul on `cu_stream`. `workspace`: 256-byte aligned device memory of at least
+ * iree_uk_b200_matmul_workspace_size bytes, in use until the work has completed. */
+IREE_UK_B200_EXPORT int iree_uk_b200_matmul(const iree_uk_b200_matmul_params_t* params,
+                                            void* workspace, size_t workspace_bytes,
+                                            void* cu_stream);
+
 /* Device bytes iree_uk_b200_mmt4d_host needs for `params` (device copies of both operands and
  * of the output, plus the tensor-core scratch of one chunk); 0 when the parameters are rejected. */
 IREE_UK_B200_EXPORT size_t

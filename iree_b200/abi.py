@@ -75,6 +75,17 @@ class Mmt4dParams(C.Structure):
     ]
 
 
+class MatmulParams(C.Structure):
+    """iree_uk_b200_matmul_params_t: row-major lhs [M][K], rhs [K][N], out [M][N]."""
+    _fields_ = [
+        ("lhs_buffer", C.c_void_p), ("lhs_offset", index_t), ("lhs_stride0", index_t),
+        ("rhs_buffer", C.c_void_p), ("rhs_offset", index_t), ("rhs_stride0", index_t),
+        ("out_buffer", C.c_void_p), ("out_offset", index_t), ("out_stride0", index_t),
+        ("M", index_t), ("N", index_t), ("K", index_t),
+        ("flags", C.c_uint32),
+    ]
+
+
 class PackParams(C.Structure):
     """iree_uk_pack_params_t (136 bytes)."""
     _fields_ = [

@@ -160,6 +160,55 @@ uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t fl
   return 0;
 }
 
+static int validate_matmul(const iree_uk_b200_matmul_params_t* p, int* es) {
+  if (!p) return IREE_UK_B200_INVALID_ARGUMENT;
+  if (p->flags & ~(IREE_UK_FLAG_MMT4D_TYPE_MASK | IREE_UK_FLAG_MMT4D_ACCUMULATE))
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  switch (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) {
+    case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: *es = 1; break;
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32:
+    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32: *es = 2; break;
+    default: return IREE_UK_B200_UNSUPPORTED;
+  }
+  if (p->M < 0 || p->N < 0 || p->K < 0) return IREE_UK_B200_INVALID_ARGUMENT;
+  if (p->lhs_stride0 < p->K || p->rhs_stride0 < p->N || p->out_stride0 < p->N)
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  if (p->M && p->N && !p->out_buffer) return IREE_UK_B200_INVALID_ARGUMENT;
+  if (p->M && p->N && p->K && (!p->lhs_buffer || !p->rhs_buffer)) return IREE_UK_B200_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(p->out_buffer) & 3) ||
+      (reinterpret_cast<uintptr_t>(p->lhs_buffer) & (*es - 1)) ||
+      (reinterpret_cast<uintptr_t>(p->rhs_buffer) & (*es - 1)))
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  return IREE_UK_B200_OK;
+}
+
+size_t iree_uk_b200_matmul_workspace_size(const iree_uk_b200_matmul_params_t* params) {
+  int es = 0;
+  if (validate_matmul(params, &es)) return 0;
+  return matmul_workspace_size(params->flags, params->M, params->N, params->K);
+}
+
+int iree_uk_b200_matmul(const iree_uk_b200_matmul_params_t* params, void* workspace,
+                        size_t workspace_bytes, void* cu_stream) {
+  int es = 0;
+  const int rc = validate_matmul(params, &es);
+  if (rc) return rc;
+  const iree_uk_b200_matmul_params_t& p = *params;
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  if (p.M == 0 || p.N == 0) return IREE_UK_B200_OK;
+  char* out = static_cast<char*>(p.out_buffer) + p.out_offset * 4;
+  if (p.K == 0) {
+    // an empty reduction: the accumulator is kept, or the result is zero
+    if (p.flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) return IREE_UK_B200_OK;
+    return cudaMemset2DAsync(out, size_t(p.out_stride0) * 4, 0, size_t(p.N) * 4, size_t(p.M),
+                             stream) == cudaSuccess ? IREE_UK_B200_OK : IREE_UK_B200_CUDA_ERROR;
+  }
+  return launch_matmul_rowmajor(
+      p.flags, static_cast<const char*>(p.lhs_buffer) + p.lhs_offset * es, p.lhs_stride0 * es,
+      static_cast<const char*>(p.rhs_buffer) + p.rhs_offset * es, p.rhs_stride0 * es, out,
+      p.out_stride0, p.M, p.N, p.K, workspace, workspace_bytes, stream);
+}
+
 int iree_uk_b200_mmt4d_path(const iree_uk_mmt4d_params_t* params, int with_workspace) {
   Mmt4dPath path;
   const int rc = select_mmt4d(params, with_workspace != 0, &path);

@@ -54,6 +54,12 @@ bool mmt4d_tc_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream);
+// Row-major matmul on the tensor-core kernels (lhs [M][K], rhs [K][N], out [M][N] 32-bit);
+// pitches in bytes, out_stride0 in elements.
+size_t matmul_workspace_size(uint32_t flags, int64_t M, int64_t N, int64_t K);
+int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b, const char* rhs,
+                           int64_t rhs_pitch_b, char* out, int64_t out_stride0, int64_t M, int64_t N,
+                           int64_t K, void* ws, size_t ws_bytes, cudaStream_t stream);
 constexpr int kTcVariantDefault = 0;
 constexpr int kTcVariantDirect = 3;  // MN-major, 32-byte swizzle, straight from the operand
 // f16f16f32 / bf16bf16f32 with M0 = N0 = 16 and K0 = 1: served by the tensor cores without scratch.

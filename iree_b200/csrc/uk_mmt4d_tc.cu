@@ -34,6 +34,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "uk_common.h"
 
@@ -78,6 +79,9 @@ struct TcParams {
   int32_t accumulate;
   int32_t out_is_int;
   int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
+  int32_t out_row_major; // fused matmul: the output is a row-major rows x cols matrix
+  int32_t out_vec16;     // row-major output rows may be accessed with 16-byte vectors
+  int64_t rows, cols;    // extent of the row-major output
   uint32_t debug_flags;  // experiments only: 1 = no output stores, 2 = no TMEM reads, 4 = no TMA
                          // loads, 8 = the producer never fills a stage (exercises the bounded waits)
   uint32_t* status;
@@ -315,14 +319,60 @@ __device__ __forceinline__ void ld_global_v8(const void* p, uint32_t (&r)[8]) {
                : "memory");
 }
 
+// Row-major output (fused matmul): lane owns output row `row`, `chunks` groups of 16 columns
+// from column col0. Whole, aligned groups use 16-byte accesses; ragged or unaligned ones are
+// written element by element, never past `cols`. All 32 lanes must call this.
+__device__ __forceinline__ void epilogue_rows_rowmajor(const TcParams& P, uint32_t taddr0,
+                                                       int64_t row, int64_t col0, int chunks) {
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[16];
+    tmem_ld16(taddr0 + uint32_t(c * 16), r);
+    tmem_ld_wait();
+    const int64_t col = col0 + c * 16;
+    if (row >= P.rows || col >= P.cols || (P.debug_flags & 1u)) continue;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(P.out) + row * P.out_stride0 + col;
+    if (P.out_vec16 && col + 16 <= P.cols) {
+      uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        if (P.accumulate) {
+          const uint4 old = d4[v];
+          const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            r[4 * v + j] = P.out_is_int
+                               ? r[4 * v + j] + o[j]
+                               : __float_as_uint(__uint_as_float(r[4 * v + j]) + __uint_as_float(o[j]));
+        }
+        d4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (col + j < P.cols) {
+          uint32_t v = r[j];
+          if (P.accumulate)
+            v = P.out_is_int ? v + dst[j]
+                             : __float_as_uint(__uint_as_float(v) + __uint_as_float(dst[j]));
+          dst[j] = v;
+        }
+      }
+    }
+  }
+}
+
 // Epilogue of one accumulator tile for one warp: lanes own rows row0 .. row0+31 of the output
 // (row = m1*16 + m0), `chunks` groups of 16 columns starting at tile column n1_0. Each thread
 // moves one 64-byte row of a 16x16 output tile per chunk. All 32 lanes must call this.
 __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0, int64_t row,
                                               int64_t n1_0, int chunks) {
+  if (P.debug_flags & 2u) return;
+  if (P.out_row_major) {
+    epilogue_rows_rowmajor(P, taddr0, row, n1_0 * 16, chunks);
+    return;
+  }
   const int64_t m1 = row >> 4;
   const int m0 = int(row & 15);
-  if (P.debug_flags & 2u) return;
   for (int c = 0; c < chunks; ++c) {
     uint32_t r[16];
     tmem_ld16(taddr0 + uint32_t(c * 16), r);
@@ -1609,4 +1659,214 @@ extern "C" int iree_uk_b200_mmt4d_static_scratch(const iree_uk_mmt4d_params_t* p
   return iree_uk_b200_mmt4d_ws(params, scratch, size_t(IREE_UK_B200_STATIC_SCRATCH_BYTES),
                                cu_stream);
 }
+
+// ---------------------------------------------------------------------------------------
+// fused row-major matmul: what pack -> mmt4d -> unpack computes, without the packed copies
+// ---------------------------------------------------------------------------------------
+namespace uk {
+namespace {
+
+// [K][N] row-major -> [N][K] row-major with a pitch, through a 64 x 64 shared-memory tile.
+template <int ES>
+__global__ void __launch_bounds__(256) transpose_kn_kernel(const char* __restrict__ src,
+                                                           int64_t src_pitch_b, char* __restrict__ dst,
+                                                           int64_t dst_pitch_b, int64_t K, int64_t N) {
+  using E = typename std::conditional<ES == 1, uint8_t, uint16_t>::type;
+  constexpr int T = 64;
+  __shared__ E tile[T][T + 2 * (4 / ES) + 0];  // [n][k], padded
+  const int64_t k_base = int64_t(blockIdx.y) * T, n_base = int64_t(blockIdx.x) * T;
+  for (int e = threadIdx.x; e < T * T; e += blockDim.x) {
+    const int k = e / T, n = e - k * T;
+    const int64_t gk = k_base + k, gn = n_base + n;
+    tile[n][k] = (gk < K && gn < N) ? *reinterpret_cast<const E*>(src + gk * src_pitch_b + gn * ES)
+                                     : E(0);
+  }
+  __syncthreads();
+  constexpr int NV = 16 / ES;       // elements per 16-byte vector
+  constexpr int VPR = T / NV;       // vectors per tile row
+  for (int v = threadIdx.x; v < T * VPR; v += blockDim.x) {
+    const int n = v / VPR, kv = v - n * VPR;
+    const int64_t gn = n_base + n, gk = k_base + int64_t(kv) * NV;
+    if (gn >= N || gk >= K) continue;
+    char* dp = dst + gn * dst_pitch_b + gk * ES;
+    if (gk + NV <= K) {
+      uint32_t w[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t x = 0;
+#pragma unroll
+        for (int j = 0; j < 4 / ES; ++j) x |= uint32_t(tile[n][kv * NV + q * (4 / ES) + j]) << (8 * ES * j);
+        w[q] = x;
+      }
+      *reinterpret_cast<uint4*>(dp) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int j = 0; j < NV && gk + j < K; ++j) reinterpret_cast<E*>(dp)[j] = tile[n][kv * NV + j];
+    }
+  }
+}
+
+struct MatmulLayout {
+  int64_t pitch, rhs_t_bytes, lhs_copy_bytes;
+};
+MatmulLayout matmul_layout(int64_t M, int64_t N, int64_t K, int es) {
+  MatmulLayout l;
+  l.pitch = round_up(K * es, 128);
+  l.rhs_t_bytes = round_up(N * l.pitch, 1024);
+  l.lhs_copy_bytes = round_up(M * l.pitch, 1024);
+  return l;
+}
+
+}  // namespace
+
+size_t matmul_workspace_size(uint32_t flags, int64_t M, int64_t N, int64_t K) {
+  TypeInfo ti;
+  if (!tc_type_info(flags, &ti) || M < 1 || N < 1 || K < 1) return 0;
+  const MatmulLayout l = matmul_layout(M, N, K, ti.es);
+  return size_t(l.rhs_t_bytes + l.lhs_copy_bytes);
+}
+
+// lhs [M][K] (row pitch lhs_pitch_b), rhs [K][N] (row pitch rhs_pitch_b), out [M][N] 32-bit.
+int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b, const char* rhs,
+                           int64_t rhs_pitch_b, char* out, int64_t out_stride0, int64_t M, int64_t N,
+                           int64_t K, void* ws, size_t ws_bytes, cudaStream_t stream) {
+  TypeInfo ti;
+  if (!tc_type_info(flags, &ti)) return IREE_UK_B200_UNSUPPORTED;
+  if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
+  const MatmulLayout l = matmul_layout(M, N, K, ti.es);
+  if (!ws || ws_bytes < size_t(l.rhs_t_bytes + l.lhs_copy_bytes)) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+  uint32_t* status = device_status_word();
+  if (!status) return IREE_UK_B200_CUDA_ERROR;
+  KernelTiming& timing = kernel_timing();
+  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  if (tev) cudaEventRecord(tev[0], stream);
+
+  // RHS: transposed once into K-major rows. LHS: used in place when TMA can address it,
+  // else copied with a TMA-friendly pitch.
+  char* rhs_t = static_cast<char*>(ws);
+  char* lhs_copy = rhs_t + l.rhs_t_bytes;
+  {
+    dim3 grid(unsigned((N + 63) / 64), unsigned((K + 63) / 64));
+    if (grid.y > 65535) return IREE_UK_B200_UNSUPPORTED;
+    if (ti.es == 1) transpose_kn_kernel<1><<<grid, 256, 0, stream>>>(rhs, rhs_pitch_b, rhs_t, l.pitch, K, N);
+    else transpose_kn_kernel<2><<<grid, 256, 0, stream>>>(rhs, rhs_pitch_b, rhs_t, l.pitch, K, N);
+    if (cudaGetLastError() != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  }
+  const char* a_ptr = lhs;
+  int64_t a_pitch = lhs_pitch_b;
+  if ((reinterpret_cast<uintptr_t>(lhs) & 15) || (lhs_pitch_b & 15)) {
+    if (cudaMemcpy2DAsync(lhs_copy, size_t(l.pitch), lhs, size_t(lhs_pitch_b), size_t(K * ti.es),
+                          size_t(M), cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+      return IREE_UK_B200_CUDA_ERROR;
+    a_ptr = lhs_copy;
+    a_pitch = l.pitch;
+  }
+
+  TcParams P;
+  std::memset(&P, 0, sizeof P);
+  const int kblk_elems = 128 / ti.es;
+  // tile counts in units of the 16-row tiles the schedulers reason in
+  const int64_t M1 = (M + 15) / 16, N1 = (N + 15) / 16;
+  const bool want_pair = M >= 256 && N >= 128 && ((M + 255) / 256) * ((N + 127) / 128) >= 74;
+  bool pair = false;
+  int pair_clusters = 0, bn = pick_bn(M1, N1), kboxes = 1;
+  if (want_pair) {
+    const size_t smem_probe = size_t(6) * (BM * 128 + 128 * 128) + 1024;
+    if (ti.is_int) cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
+    else cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
+    pair_clusters = ti.is_int ? max_pair_clusters<true>(smem_probe) : max_pair_clusters<false>(smem_probe);
+    if (pair_clusters >= 1) {
+      pair = true;
+      kboxes = 2;
+      bn = pick_bn_pair(M1, N1, pair_clusters);
+    }
+  }
+  const int b_rows = pair ? bn / 2 : bn;  // RHS rows one CTA stages
+  const uint64_t da[3] = {uint64_t(K), uint64_t(M), 1};
+  const uint64_t db[3] = {uint64_t(K), uint64_t(N), 1};
+  const uint64_t sa[2] = {uint64_t(a_pitch), uint64_t(a_pitch) * uint64_t(M)};
+  const uint64_t sb[2] = {uint64_t(l.pitch), uint64_t(l.pitch) * uint64_t(N)};
+  const uint32_t ba[3] = {uint32_t(kblk_elems), BM, 1};
+  const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(b_rows), 1};
+  if (!encode_map(&P.map_a, ti.tm_type, const_cast<char*>(a_ptr), da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_map(&P.map_b, ti.tm_type, rhs_t, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+    return IREE_UK_B200_CUDA_ERROR;
+  const int tile_m = pair ? 2 * BM : BM;
+  P.sa = {kboxes, BM * 128, {kboxes * kblk_elems, 0, 0}, {0, tile_m, 0}, {kblk_elems, 0, 0}, {0, BM, 0}};
+  P.sb = {kboxes, b_rows * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}, {0, b_rows, 0}};
+  P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
+  P.desc_lbo_a = P.desc_lbo_b = 1;
+  P.kadv_a = P.kadv_b = 2;
+  P.kbox_units_a = uint32_t(BM * 128) >> 4;
+  P.kbox_units_b = uint32_t(b_rows * 128) >> 4;
+  P.idesc = make_idesc(ti, bn, false, tile_m);
+  P.kboxes = kboxes;
+  P.mma_per_box = 4;
+  P.stage_bytes_a = kboxes * BM * 128;
+  P.stage_bytes_b = kboxes * b_rows * 128;
+  P.num_kb = int((K + kboxes * kblk_elems - 1) / (kboxes * kblk_elems));
+  P.bn = bn;
+  P.m_tiles = int((M + tile_m - 1) / tile_m);
+  P.n_tiles = int((N + bn - 1) / bn);
+  P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
+  P.out = out;
+  P.out_stride0 = out_stride0;
+  P.M1 = M1;
+  P.N1 = N1;
+  P.rows = M;
+  P.cols = N;
+  P.out_row_major = 1;
+  P.out_vec16 = ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (out_stride0 * 4) % 16 == 0) ? 1 : 0;
+  P.accumulate = (flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
+  P.out_is_int = ti.is_int ? 1 : 0;
+  P.status = status;
+  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
+  const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
+  P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
+  if (tev) cudaEventRecord(tev[1], stream);
+  cudaError_t e;
+  if (pair) {
+    const int clusters = std::min(P.m_tiles * P.n_tiles, pair_clusters);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(2 * clusters), 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (ti.is_int) {
+      if (cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<true>, P);
+    } else {
+      if (cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<false>, P);
+    }
+    if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  } else {
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int grid = std::min(P.m_tiles * P.n_tiles, sms);
+    if (ti.is_int) {
+      if (cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
+    } else {
+      if (cudaFuncSetAttribute(mmt4d_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+      mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
+    }
+  }
+  if (tev) {
+    cudaEventRecord(tev[2], stream);
+    ++timing.calls;
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace uk
 

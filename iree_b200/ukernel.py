@@ -63,6 +63,21 @@ def mmt4d_host(params, arena, stream=None):
                                        _stream_handle(stream)), "mmt4d_host")
 
 
+def matmul_workspace_size(params):
+    """Scratch bytes ``matmul`` needs for ``params`` (an ``abi.MatmulParams``)."""
+    return int(lib.iree_uk_b200_matmul_workspace_size(C.addressof(params)))
+
+
+def matmul(params, workspace, stream=None):
+    """Row-major matmul with the results of the reference's pack -> mmt4d -> unpack chain
+    (``ukernel/tools/e2e_matmul_benchmark.c:173-300``), on the tensor-core kernels and without
+    packed copies of the LHS or the result. ``workspace``: a torch uint8 CUDA tensor of at least
+    ``matmul_workspace_size(params)`` bytes."""
+    _check(lib.iree_uk_b200_matmul(C.addressof(params), workspace.data_ptr(),
+                                   workspace.numel() * workspace.element_size(),
+                                   _stream_handle(stream)), "matmul")
+
+
 STATIC_SCRATCH_BYTES = 32 << 20
 
 

@@ -189,3 +189,62 @@ def mmt4d_threaded(p, threads, impl="ref"):
     with ThreadPoolExecutor(len(jobs)) as ex:
         list(ex.map(lambda q: mmt4d(q, impl), jobs))
     return len(jobs)
+
+
+def matmul_chain(lhs, rhs, acc, type_flag, M0, N0, K0, impl="oracle"):
+    """Row-major matmul through the chain of ukernel/tools/e2e_matmul_benchmark.c:173-300:
+    pack the LHS, pack the RHS with TRANSPOSE_INNER | TRANSPOSE_OUTER, pack the accumulator
+    (when ``acc`` is given, which also sets ACCUMULATE), mmt4d, unpack; padding is zero.
+    ``lhs`` [M][K], ``rhs`` [K][N] and ``acc`` [M][N] are C-contiguous numpy arrays whose
+    item sizes match the type triple (int8 / uint16 bit patterns for f16 and bf16; int32 or
+    float32 for ``acc``). Returns the [M][N] result."""
+    import numpy as np
+    pack_in = {abi.MMT4D_S8S8S32: abi.PACK_I8I8, abi.MMT4D_F16F16F32: abi.PACK_F16F16,
+               abi.MMT4D_BF16BF16F32: abi.PACK_BF16BF16}[type_flag]
+    is_int = type_flag == abi.MMT4D_S8S8S32
+    pack_out = abi.PACK_I32I32 if is_int else abi.PACK_F32F32
+    unpack_out = abi.UNPACK_I32I32 if is_int else abi.UNPACK_F32F32
+    out_dtype = np.int32 if is_int else np.float32
+    M, K = lhs.shape
+    K2, N = rhs.shape
+    assert K == K2
+    M1, N1, K1 = -(-M // M0), -(-N // N0), -(-K // K0)
+    packed_lhs = np.zeros(M1 * K1 * M0 * K0, dtype=lhs.dtype)
+    packed_rhs = np.zeros(N1 * K1 * N0 * K0, dtype=rhs.dtype)
+    packed_out = np.zeros(M1 * N1 * M0 * N0, dtype=out_dtype)
+    result = np.zeros((M, N), dtype=out_dtype)
+
+    def pack_params(src, dst, flags, s0, s1, o0, o1, t0, t1):
+        p = abi.PackParams()
+        p.in_buffer, p.out_buffer = src.ctypes.data, dst.ctypes.data
+        p.in_size0, p.in_size1, p.in_stride0, p.in_stride1 = s0, s1, s1, 1
+        p.out_size0, p.out_size1, p.out_size2, p.out_size3 = o0, o1, t0, t1
+        p.out_stride1 = t0 * t1
+        p.out_stride0 = o1 * t0 * t1
+        p.padding_value, p.flags = 0, flags
+        return p
+
+    lhs, rhs = np.ascontiguousarray(lhs), np.ascontiguousarray(rhs)
+    pack(pack_params(lhs, packed_lhs, pack_in, M, K, M1, K1, M0, K0), impl)
+    pack(pack_params(rhs, packed_rhs,
+                     pack_in | abi.PACK_TRANSPOSE_INNER | abi.PACK_TRANSPOSE_OUTER,
+                     K, N, N1, K1, N0, K0), impl)
+    flags = type_flag
+    if acc is not None:
+        acc = np.ascontiguousarray(acc.astype(out_dtype, copy=False))
+        pack(pack_params(acc, packed_out, pack_out, M, N, M1, N1, M0, N0), impl)
+        flags |= abi.MMT4D_ACCUMULATE
+    q = abi.Mmt4dParams()
+    q.lhs_buffer, q.rhs_buffer, q.out_buffer = (packed_lhs.ctypes.data, packed_rhs.ctypes.data,
+                                                packed_out.ctypes.data)
+    q.M, q.N, q.K, q.M0, q.N0, q.K0, q.flags = M1, N1, K1, M0, N0, K0, flags
+    q.lhs_stride0, q.rhs_stride0, q.out_stride0 = K1 * M0 * K0, K1 * N0 * K0, N1 * M0 * N0
+    mmt4d(q, impl)
+    u = abi.UnpackParams()
+    u.in_buffer, u.out_buffer = packed_out.ctypes.data, result.ctypes.data
+    u.in_size0, u.in_size1, u.in_size2, u.in_size3 = M1, N1, M0, N0
+    u.in_stride1, u.in_stride0 = M0 * N0, N1 * M0 * N0
+    u.out_size0, u.out_size1, u.out_stride0, u.out_stride1 = M, N, N, 1
+    u.flags = unpack_out
+    unpack(u, impl)
+    return result

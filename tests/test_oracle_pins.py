@@ -105,3 +105,21 @@ def test_threaded_driver_matches_single_call():
         oracle.mmt4d(c.params(c.lhs, c.rhs, a))
         oracle.mmt4d_threaded(c.params(c.lhs, c.rhs, b), 4, impl="oracle")
         assert np.array_equal(a, b)
+
+
+def test_matmul_chain_restatement_against_reference_and_plain_matmul():
+    """The pack -> mmt4d -> unpack chain (ukernel/tools/e2e_matmul_benchmark.c:173-300) on the
+    oracle equals the same chain on the compiled reference and a plain integer matmul, for
+    several tile sizes including ones that need padding."""
+    rng = np.random.default_rng(5)
+    M, N, K = 45, 70, 37
+    a = rng.integers(-128, 128, (M, K), dtype=np.int8)
+    b = rng.integers(-128, 128, (K, N), dtype=np.int8)
+    c = rng.integers(-1000, 1000, (M, N), dtype=np.int32)
+    want = a.astype(np.int32) @ b.astype(np.int32) + c
+    impls = ["oracle"] + (["ref"] if oracle.ref_available() else [])
+    for impl in impls:
+        for tile in [(16, 16, 2), (8, 8, 4), (7, 3, 5)]:
+            got = oracle.matmul_chain(a, b, c, abi.MMT4D_S8S8S32, *tile, impl=impl)
+            assert np.array_equal(got, want), (impl, tile)
+    assert np.array_equal(oracle.matmul_chain(a, b, None, abi.MMT4D_S8S8S32, 16, 16, 2), want - c)
