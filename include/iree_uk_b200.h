@@ -235,6 +235,45 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* para
                                               void* workspace, size_t workspace_bytes,
                                               void* cu_stream);
 
+/* Most peer output buffers one call of iree_uk_b200_mmt4d_ws_peers can store to. */
+#define IREE_UK_B200_MAX_PEERS 16
+
+/* mmt4d fused with the replication of its output: every output tile is stored to
+ * params->out_buffer and, from the same kernel, to `num_peers` further buffers that usually
+ * live on other GPUs (NVLink peer memory), so that an N-sharded mmt4d (each GPU owning a range
+ * of RHS tile rows, ukernel/mmt4d.c:84-98) leaves the whole [M][N][M0][N0] result on every GPU
+ * without a separate all-gather. peer_out_buffers[i] stands for params->out_buffer in copy i:
+ * out_offset and out_stride0 apply to it unchanged. The pointers must be valid on the current
+ * device (see iree_uk_b200_peer_open) and have params->out_buffer's alignment modulo 32 bytes.
+ * ACCUMULATE reads the old values from params->out_buffer only. The stores to a peer are
+ * complete when this GPU's stream reaches the end of the call; the peer must not read them
+ * before it has synchronised with this GPU (a barrier among the ranks, or an event).
+ * Served only by the tensor-core kernels (s8s8s32, f16f16f32, bf16bf16f32 with 16x16 tiles and
+ * scratch): any other problem returns IREE_UK_B200_UNSUPPORTED and launches nothing. No
+ * counterpart in the reference, whose ukernels are single-device. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws_peers(const iree_uk_mmt4d_params_t* params,
+                                                    const void* const* peer_out_buffers,
+                                                    int num_peers, void* workspace,
+                                                    size_t workspace_bytes, void* cu_stream);
+
+/* What one process hands to another (same machine) so that the other can address this
+ * process's device buffer: a CUDA IPC handle of the allocation plus the buffer's offset in it. */
+typedef struct iree_uk_b200_peer_handle_t {
+  unsigned char ipc[64];
+  uint64_t offset;
+} iree_uk_b200_peer_handle_t;
+
+/* Fills `handle` for `device_ptr` (memory of the current device obtained from cudaMalloc,
+ * directly or through an allocator built on it). */
+IREE_UK_B200_EXPORT int iree_uk_b200_peer_export(const void* device_ptr,
+                                                 iree_uk_b200_peer_handle_t* handle);
+/* Maps another process's buffer into this process for the current device (peer access is
+ * enabled as needed). Each handle may be open once per process at a time. */
+IREE_UK_B200_EXPORT int iree_uk_b200_peer_open(const iree_uk_b200_peer_handle_t* handle,
+                                               void** device_ptr);
+/* Unmaps a pointer returned by iree_uk_b200_peer_open, once no enqueued work uses it. */
+IREE_UK_B200_EXPORT int iree_uk_b200_peer_close(void* device_ptr);
+
 /* Capacity of the library-owned scratch used by iree_uk_b200_mmt4d_static_scratch. */
 #define IREE_UK_B200_STATIC_SCRATCH_BYTES (32u << 20)
 

@@ -86,6 +86,11 @@ class MatmulParams(C.Structure):
     ]
 
 
+class PeerHandle(C.Structure):
+    """iree_uk_b200_peer_handle_t: CUDA IPC handle of an allocation + offset of the buffer."""
+    _fields_ = [("ipc", C.c_ubyte * 64), ("offset", C.c_uint64)]
+
+
 class PackParams(C.Structure):
     """iree_uk_pack_params_t (136 bytes)."""
     _fields_ = [

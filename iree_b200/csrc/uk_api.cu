@@ -2,6 +2,9 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
+
+#include <cuda.h>
 
 #include "uk_common.h"
 
@@ -158,6 +161,90 @@ uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t fl
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 && M0 == 1 && N0 == 32 && K0 == 8)
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   return 0;
+}
+
+int iree_uk_b200_mmt4d_ws_peers(const iree_uk_mmt4d_params_t* params,
+                                const void* const* peer_out_buffers, int num_peers,
+                                void* workspace, size_t workspace_bytes, void* cu_stream) {
+  if (num_peers < 0 || num_peers > IREE_UK_B200_MAX_PEERS || (num_peers && !peer_out_buffers))
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  Mmt4dPath path;
+  const int rc = select_mmt4d(params, true, &path);
+  if (rc) return rc;
+  if (path != Mmt4dPath::TcRetile ||
+      (params->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
+    return IREE_UK_B200_UNSUPPORTED;
+  if (!workspace || workspace_bytes < mmt4d_tc_workspace_size(params))
+    return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  return launch_mmt4d_tc(params, workspace, workspace_bytes, kTcVariantDefault,
+                         static_cast<cudaStream_t>(cu_stream), peer_out_buffers, num_peers);
+}
+
+namespace {
+struct PeerMapping {
+  void* base;
+  void* ptr;
+};
+std::mutex g_peer_mu;
+std::vector<PeerMapping> g_peer_mappings;
+}  // namespace
+
+int iree_uk_b200_peer_export(const void* device_ptr, iree_uk_b200_peer_handle_t* handle) {
+  if (!device_ptr || !handle) return IREE_UK_B200_INVALID_ARGUMENT;
+  // base of the allocation that holds device_ptr
+  typedef CUresult (*GetRange)(CUdeviceptr*, size_t*, CUdeviceptr);
+  static GetRange get_range = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<GetRange>(fn);
+  }();
+  if (!get_range) return IREE_UK_B200_CUDA_ERROR;
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (get_range(&base, &size, reinterpret_cast<CUdeviceptr>(device_ptr)) != CUDA_SUCCESS)
+    return IREE_UK_B200_CUDA_ERROR;
+  cudaIpcMemHandle_t h;
+  static_assert(sizeof h == sizeof handle->ipc, "IPC handle size");
+  if (cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)) != cudaSuccess) {
+    cudaGetLastError();
+    return IREE_UK_B200_CUDA_ERROR;
+  }
+  std::memcpy(handle->ipc, &h, sizeof h);
+  handle->offset = uint64_t(reinterpret_cast<CUdeviceptr>(device_ptr) - base);
+  return IREE_UK_B200_OK;
+}
+
+int iree_uk_b200_peer_open(const iree_uk_b200_peer_handle_t* handle, void** device_ptr) {
+  if (!handle || !device_ptr) return IREE_UK_B200_INVALID_ARGUMENT;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle->ipc, sizeof h);
+  void* base = nullptr;
+  if (cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return IREE_UK_B200_CUDA_ERROR;
+  }
+  *device_ptr = static_cast<char*>(base) + handle->offset;
+  std::lock_guard<std::mutex> lock(g_peer_mu);
+  g_peer_mappings.push_back({base, *device_ptr});
+  return IREE_UK_B200_OK;
+}
+
+int iree_uk_b200_peer_close(void* device_ptr) {
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_peer_mu);
+    for (size_t i = 0; i < g_peer_mappings.size(); ++i)
+      if (g_peer_mappings[i].ptr == device_ptr) {
+        base = g_peer_mappings[i].base;
+        g_peer_mappings.erase(g_peer_mappings.begin() + i);
+        break;
+      }
+  }
+  if (!base) return IREE_UK_B200_INVALID_ARGUMENT;
+  return cudaIpcCloseMemHandle(base) == cudaSuccess ? IREE_UK_B200_OK : IREE_UK_B200_CUDA_ERROR;
 }
 
 static int validate_matmul(const iree_uk_b200_matmul_params_t* p, int* es) {

@@ -79,6 +79,8 @@ struct TcParams {
   int32_t accumulate;
   int32_t out_is_int;
   int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
+  int32_t num_peers;     // copies of every output tile also stored to this many peer buffers
+  int64_t peer_delta[IREE_UK_B200_MAX_PEERS];  // byte distance from `out` to each peer's buffer
   int32_t out_row_major; // fused matmul: the output is a row-major rows x cols matrix
   int32_t out_vec16;     // row-major output rows may be accessed with 16-byte vectors
   int64_t rows, cols;    // extent of the row-major output
@@ -396,6 +398,10 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
         }
         st_global_v8(dst, &r[0]);
         st_global_v8(dst + 32, &r[8]);
+        for (int g = 0; g < P.num_peers; ++g) {  // the same tile row into every peer's buffer
+          st_global_v8(dst + P.peer_delta[g], &r[0]);
+          st_global_v8(dst + P.peer_delta[g] + 32, &r[8]);
+        }
       } else {
         uint4* d4 = reinterpret_cast<uint4*>(dst);
         if (P.accumulate) {
@@ -413,6 +419,12 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
 #pragma unroll
         for (int v = 0; v < 4; ++v)
           d4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        for (int g = 0; g < P.num_peers; ++g) {
+          uint4* p4 = reinterpret_cast<uint4*>(dst + P.peer_delta[g]);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            p4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+        }
       }
     }
   }
@@ -1392,7 +1404,12 @@ bool pair_kernel_pays(const iree_uk_mmt4d_params_t* p) {
 }  // namespace
 
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, const void* const* peer_out_buffers, int num_peers) {
+  if (num_peers < 0 || num_peers > IREE_UK_B200_MAX_PEERS || (num_peers && !peer_out_buffers))
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  // Peer copies exist for the plain tiled epilogue only.
+  if (num_peers && (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
+    return IREE_UK_B200_UNSUPPORTED;
   if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
     return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
   TypeInfo ti;
@@ -1555,6 +1572,15 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
   P.out_is_int = ti.is_int ? 1 : 0;
   P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * 4) % 32 == 0) ? 1 : 0;
+  P.num_peers = num_peers;
+  for (int g = 0; g < num_peers; ++g) {
+    const char* peer = static_cast<const char*>(peer_out_buffers[g]);
+    if (!peer) return IREE_UK_B200_INVALID_ARGUMENT;
+    P.peer_delta[g] = int64_t(reinterpret_cast<intptr_t>(peer) -
+                              reinterpret_cast<intptr_t>(p->out_buffer));
+    // a peer buffer must allow the same vector width as the local one
+    if (P.peer_delta[g] % (P.out_vec32 ? 32 : 16)) return IREE_UK_B200_INVALID_ARGUMENT;
+  }
   P.status = status;
   P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
 

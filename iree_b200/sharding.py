@@ -37,3 +37,33 @@ def gather_output(slab, M, N, tile_elems, group=None, stream=None):
     full = torch.empty_like(gathered)
     uk.interleave_slabs(gathered, full, M, N, tile_elems, slab.element_size(), world, stream)
     return full
+
+
+class PeerOutputs:
+    """The other ranks' copies of a replicated output buffer, addressable from this GPU.
+
+    Every rank allocates a full [M][N][M0][N0] buffer and calls ``PeerOutputs(buffer, group)``
+    (a collective: handles travel through ``all_gather_object``). ``ptrs`` then lists the
+    addresses of the other ranks' buffers for ``ukernel.mmt4d_peers``, so that each rank's
+    kernel stores its tile columns into all copies and no all-gather is needed. ``exchange``,
+    ``export`` and ``open_`` are injectable for tests that run without GPUs."""
+
+    def __init__(self, buffer, group=None, export=None, open_=None, close=None, exchange=None):
+        export = export or uk.peer_export
+        self._close = close or uk.peer_close
+        open_ = open_ or uk.peer_open
+        if exchange is None:
+            import torch.distributed as dist
+
+            def exchange(mine):
+                got = [None] * dist.get_world_size(group)
+                dist.all_gather_object(got, mine, group=group)
+                return got, dist.get_rank(group)
+        handles, rank = exchange(export(buffer))
+        self.rank = rank
+        self.ptrs = [open_(h) for r, h in enumerate(handles) if r != rank]
+
+    def close(self):
+        for ptr in self.ptrs:
+            self._close(ptr)
+        self.ptrs = []

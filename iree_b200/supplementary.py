@@ -104,6 +104,63 @@ def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None
     return name, res
 
 
+def _matmul_rowmajor_case(M, N, K, bf16_peak):
+    """bf16 x bf16 -> f32, lhs [M][K], rhs [K][N], out [M][N], all row-major."""
+    lhs = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    rhs = torch.randn(K, N, device="cuda").to(torch.bfloat16)
+    out = torch.empty(M, N, device="cuda")
+    ops = 2.0 * M * N * K
+    # fused
+    mp = abi.MatmulParams()
+    mp.lhs_buffer, mp.rhs_buffer, mp.out_buffer = lhs.data_ptr(), rhs.data_ptr(), out.data_ptr()
+    mp.lhs_stride0, mp.rhs_stride0, mp.out_stride0 = K, N, N
+    mp.M, mp.N, mp.K, mp.flags = M, N, K, abi.MMT4D_BF16BF16F32
+    ws = torch.empty(uk.matmul_workspace_size(mp), dtype=torch.uint8, device="cuda")
+    fused, fused_best = _time(lambda: uk.matmul(mp, ws))
+    del ws
+    # chain, tiles 16x16x2
+    M1, N1, K1 = M // 16, N // 16, K // 2
+    plhs = torch.empty(M * K, dtype=torch.bfloat16, device="cuda")
+    prhs = torch.empty(N * K, dtype=torch.bfloat16, device="cuda")
+    pout = torch.empty(M * N, device="cuda")
+
+    def pack_params(src, dst, flags, s0, s1, o0, o1, t0, t1):
+        p = abi.PackParams()
+        p.in_buffer, p.out_buffer = src.data_ptr(), dst.data_ptr()
+        p.in_size0, p.in_size1, p.in_stride0, p.in_stride1 = s0, s1, s1, 1
+        p.out_size0, p.out_size1, p.out_size2, p.out_size3 = o0, o1, t0, t1
+        p.out_stride1, p.out_stride0, p.flags = t0 * t1, o1 * t0 * t1, flags
+        return p
+
+    pl = pack_params(lhs, plhs, abi.PACK_BF16BF16, M, K, M1, K1, 16, 2)
+    pr = pack_params(rhs, prhs, abi.PACK_BF16BF16 | abi.PACK_TRANSPOSE_INNER |
+                     abi.PACK_TRANSPOSE_OUTER, K, N, N1, K1, 16, 2)
+    q = _mmt4d_params(abi.MMT4D_BF16BF16F32, M1, N1, K1, 16, 16, 2, plhs, prhs, pout)
+    ws = torch.empty(uk.mmt4d_workspace_size(q), dtype=torch.uint8, device="cuda")
+    u = abi.UnpackParams()
+    u.in_buffer, u.out_buffer = pout.data_ptr(), out.data_ptr()
+    u.in_size0, u.in_size1, u.in_size2, u.in_size3 = M1, N1, 16, 16
+    u.in_stride1, u.in_stride0 = 256, N1 * 256
+    u.out_size0, u.out_size1, u.out_stride0, u.out_stride1 = M, N, N, 1
+    u.flags = abi.UNPACK_F32F32
+
+    def chain():
+        uk.pack(pl)
+        uk.pack(pr)
+        uk.mmt4d(q, workspace=ws)
+        uk.unpack(u)
+
+    chain_ms, chain_best = _time(chain)
+    parts = {}
+    for name, fn in [("pack_lhs", lambda: uk.pack(pl)), ("pack_rhs", lambda: uk.pack(pr)),
+                     ("mmt4d", lambda: uk.mmt4d(q, workspace=ws)), ("unpack", lambda: uk.unpack(u))]:
+        parts[name] = _time(fn)[0]
+    return {"fused_ms": fused, "fused_ms_best": fused_best, "fused_tflops": ops / fused / 1e9,
+            "fused_frac_of_bf16_burst": ops / fused / 1e9 / bf16_peak,
+            "chain_ms": chain_ms, "chain_ms_best": chain_best, "chain_tflops": ops / chain_ms / 1e9,
+            "chain_parts_ms": parts, "chain_tiles": "16x16x2"}
+
+
 def run(peaks, only=None, custom=None):
     """All supplementary configurations, or those whose name contains ``only``. ``custom`` =
     (type name, M1, N1, K1) adds one tensor-core mmt4d of that size (used for profiling)."""
@@ -156,6 +213,12 @@ def run(peaks, only=None, custom=None):
         r["gbs"] = gemv_bytes / r["ms"] / 1e6
         r["frac_hbm"] = r["gbs"] / hbm
         res[k] = r
+
+    # row-major matmul at the headline dimensions: the fused entry point beside the chain
+    # pack LHS, pack RHS (TRANSPOSE_INNER | TRANSPOSE_OUTER), mmt4d, unpack run on this library
+    if want("matmul_rowmajor_bf16_8192x28672x8192"):
+        res["matmul_rowmajor_bf16_8192x28672x8192"] = _matmul_rowmajor_case(
+            8192, 28672, 8192, bf16_peak)
 
     # pack f32 8192x8192 -> [512][8192][16][1]; TRANSPOSE_INNER variant; RHS-style 0x301
     n = 8192

@@ -63,6 +63,40 @@ def mmt4d_host(params, arena, stream=None):
                                        _stream_handle(stream)), "mmt4d_host")
 
 
+def mmt4d_peers(params, peer_out_ptrs, workspace, stream=None):
+    """mmt4d whose output tiles are also stored, by the same kernel, to the buffers at
+    ``peer_out_ptrs`` (device addresses valid on this GPU, usually other GPUs' memory opened
+    with ``peer_open``); each stands for ``params.out_buffer`` in one more copy of the output.
+    Tensor-core problems only (raises UNSUPPORTED otherwise)."""
+    n = len(peer_out_ptrs)
+    arr = (C.c_void_p * max(n, 1))(*peer_out_ptrs)
+    _check(lib.iree_uk_b200_mmt4d_ws_peers(C.addressof(params), arr, n, workspace.data_ptr(),
+                                           workspace.numel() * workspace.element_size(),
+                                           _stream_handle(stream)), "mmt4d_peers")
+
+
+def peer_export(device_ptr):
+    """Bytes another process on this machine can pass to ``peer_open`` to address the device
+    buffer at ``device_ptr`` (an int, or a tensor)."""
+    ptr = device_ptr.data_ptr() if hasattr(device_ptr, "data_ptr") else int(device_ptr)
+    h = abi.PeerHandle()
+    _check(lib.iree_uk_b200_peer_export(ptr, C.addressof(h)), "peer_export")
+    return bytes(h)
+
+
+def peer_open(handle_bytes):
+    """Device address, valid in this process on the current device, of a buffer another
+    process exported with ``peer_export``."""
+    h = abi.PeerHandle.from_buffer_copy(handle_bytes)
+    out = C.c_void_p()
+    _check(lib.iree_uk_b200_peer_open(C.addressof(h), C.addressof(out)), "peer_open")
+    return int(out.value)
+
+
+def peer_close(ptr):
+    _check(lib.iree_uk_b200_peer_close(ptr), "peer_close")
+
+
 def matmul_workspace_size(params):
     """Scratch bytes ``matmul`` needs for ``params`` (an ``abi.MatmulParams``)."""
     return int(lib.iree_uk_b200_matmul_workspace_size(C.addressof(params)))

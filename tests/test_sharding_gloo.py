@@ -90,3 +90,53 @@ def test_shard_bounds_cover_every_tile_row():
                 b, c = sharding.shard_bounds(n, r, world)
                 rows += list(range(b, b + c))
             assert rows == list(range(n))
+
+
+def _peer_worker(rank, world, port):
+    """Replicated output without an all-gather, on CPU: shared host memory stands in for peer
+    device memory. Each rank computes its tile columns with the oracle and stores them into
+    every rank's copy, as the device kernel does through the addresses PeerOutputs hands out."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M0 = N0 = 16
+        case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, M0, N0, 2, 3, 8, 5, 0, seed=7, mode="normal",
+                               loose=False)
+        want = case.out_init.copy()
+        oracle.mmt4d(case.params(case.lhs, case.rhs, want))
+        nbytes = case.out_init.nbytes
+        from multiprocessing import shared_memory
+        mine = shared_memory.SharedMemory(create=True, size=nbytes)
+        opened = []
+
+        def open_(name):
+            shm = shared_memory.SharedMemory(name=name)
+            opened.append(shm)
+            return shm
+
+        peers = sharding.PeerOutputs(mine, export=lambda buf: buf.name, open_=open_,
+                                     close=lambda shm: shm.close())
+        assert peers.rank == rank and len(peers.ptrs) == world - 1
+        local = case.out_init.copy()
+        p, begin = sharding.local_params(case.params(case.lhs, case.rhs, local), rank, world,
+                                         rhs_is_local=False, out_is_local=False)
+        oracle.mmt4d(p)
+        tiles = local.view(np.int32).reshape(case.M, case.N, M0 * N0)[:, begin:begin + p.N]
+        for shm in [mine] + peers.ptrs:
+            dst = np.ndarray((case.M, case.N, M0 * N0), dtype=np.int32, buffer=shm.buf)
+            dst[:, begin:begin + p.N] = tiles
+            del dst
+        dist.barrier()  # every rank's stores have landed in every copy
+        got = np.ndarray(want.view(np.int32).shape, dtype=np.int32, buffer=mine.buf).copy()
+        assert np.array_equal(got, want.view(np.int32))
+        dist.barrier()
+        peers.close()
+        mine.close()
+        mine.unlink()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_outputs_replicate_without_a_gather_two_ranks():
+    mp.spawn(_peer_worker, args=(2, _free_port()), nprocs=2, join=True)
