@@ -340,6 +340,56 @@ def main():
     assert torch.equal(h_out, out.cpu()), "host-buffer path and device-buffer path disagree"
     e2e_value = total_flops / (e2e_ms * 1e-3) / 1e12
 
+    # ---- replicated output (N > 1): all-gather + interleave beside the fused route, where
+    # the kernel's epilogue stores every tile into all ranks' buffers over NVLink ----
+    replicated = None
+    if world > 1:
+        from iree_b200 import sharding
+        rep_steps = max(3, min(10, args.steps))
+        tile = M0 * N0
+
+        def timed(fn):
+            fn()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(rep_steps):
+                fn()
+            b.record(stream)
+            barrier()
+            tt = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item()) / rep_steps
+
+        gathered_full = [None]
+
+        def gather_route():
+            uk.mmt4d(p, stream, ws)
+            gathered_full[0] = sharding.gather_output(out, M1, N1, tile, stream=stream)
+
+        gather_ms = timed(gather_route)
+        full_out = torch.zeros(M1 * N1 * tile, dtype=torch.float32, device="cuda")
+        full.out_buffer = full_out.data_ptr()
+        pr, _ = uk.shard_params(full, rank, world, rhs_is_local=True, out_is_local=False)
+        peers = sharding.PeerOutputs(full_out)
+        fused_ms = timed(lambda: uk.mmt4d_peers(pr, peers.ptrs, ws, stream))
+        same = bool(torch.equal(full_out, gathered_full[0]))
+        flag = torch.tensor([1 if same else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        assert int(flag.item()) == 1, "fused replication and all-gather route disagree"
+        barrier()
+        peers.close()
+        nvlink_bytes = (world - 1) * out.numel() * 4  # leaves each GPU per step
+        replicated = {
+            "gather_route_ms": gather_ms, "fused_peer_store_ms": fused_ms,
+            "fused_tflops": total_flops / (fused_ms * 1e-3) / 1e12,
+            "gather_route_tflops": total_flops / (gather_ms * 1e-3) / 1e12,
+            "nvlink_bytes_out_per_gpu": nvlink_bytes,
+            "fused_nvlink_gbs_per_gpu": nvlink_bytes / fused_ms / 1e6,
+            "results_identical_on_all_ranks": True, "steps": rep_steps,
+        }
+        del gathered_full, full_out
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -386,6 +436,8 @@ def main():
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
     }
+    if replicated is not None:
+        line["replicated_output"] = replicated
     if world == 1 and not args.no_supplementary:
         try:
             from iree_b200 import supplementary

@@ -363,12 +363,90 @@ __device__ __forceinline__ void epilogue_rows_rowmajor(const TcParams& P, uint32
   }
 }
 
+// Bulk copy of `bytes` (a multiple of 16) from this CTA's shared memory to global memory,
+// which may be a peer GPU's; completion is tracked by the issuing thread's bulk groups.
+__device__ __forceinline__ void bulk_store(void* gdst, uint32_t ssrc, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               :: "l"(gdst), "r"(ssrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory");
+}
+
+constexpr int kEpiStageBytes = 4096;  // per epilogue warp: two buffers of 32 rows x 64 bytes
+
+// Epilogue with peer copies: the warp's 32 rows x 16 columns (two whole 16x16 output tiles of
+// 1 KB each) are staged in shared memory and leave as 1 KB bulk copies, one per tile and
+// destination: the local output and every peer buffer. Whole-tile writes are what NVLink
+// carries efficiently; 32-byte stores from registers reach a fraction of the link rate.
+// `stage` is this warp's kEpiStageBytes of shared memory. All 32 lanes must call this.
+__device__ __forceinline__ void epilogue_rows_peers(const TcParams& P, uint32_t taddr0,
+                                                    int64_t row, int64_t n1_0, int chunks,
+                                                    uint32_t stage, int lane) {
+  const int64_t m1 = row >> 4;
+  const int m0 = int(row & 15);
+  const int64_t m1_first = (row - lane) >> 4;  // lanes 0-15: this tile row, 16-31: the next
+  const int copies = 2 * (1 + P.num_peers);    // (tile of the pair) x (destination)
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[16];
+    tmem_ld16(taddr0 + uint32_t(c * 16), r);
+    tmem_ld_wait();
+    const int64_t n1 = n1_0 + c;
+    if (P.accumulate && m1 < P.M1 && n1 < P.N1) {
+      const uint4* d4 = reinterpret_cast<const uint4*>(
+          P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const uint4 old = d4[v];
+        const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          r[4 * v + j] = P.out_is_int
+                             ? r[4 * v + j] + o[j]
+                             : __float_as_uint(__uint_as_float(r[4 * v + j]) + __uint_as_float(o[j]));
+      }
+    }
+    const uint32_t buf = stage + uint32_t(c & 1) * 2048u;
+    bulk_wait_read<1>();  // the copies that read this buffer two chunks ago are done with it
+    __syncwarp();
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                   :: "r"(buf + uint32_t(lane) * 64u + uint32_t(v) * 16u), "r"(r[4 * v + 0]),
+                      "r"(r[4 * v + 1]), "r"(r[4 * v + 2]), "r"(r[4 * v + 3]) : "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (n1 < P.N1 && !(P.debug_flags & 1u)) {
+      for (int j = lane; j < copies; j += 32) {
+        const int t = j & 1, g = (j >> 1) - 1;  // g = -1: the local output
+        if (m1_first + t < P.M1) {
+          char* dst = P.out + ((m1_first + t) * P.out_stride0 + n1 * 256) * 4;
+          if (g >= 0) dst += P.peer_delta[g];
+          bulk_store(dst, buf + uint32_t(t) * 1024u, 1024u);
+        }
+      }
+    }
+    bulk_commit();
+  }
+  bulk_wait_read<0>();  // shared memory is reused by the next tile, or released at exit
+  __syncwarp();
+}
+
 // Epilogue of one accumulator tile for one warp: lanes own rows row0 .. row0+31 of the output
 // (row = m1*16 + m0), `chunks` groups of 16 columns starting at tile column n1_0. Each thread
 // moves one 64-byte row of a 16x16 output tile per chunk. All 32 lanes must call this.
 __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0, int64_t row,
-                                              int64_t n1_0, int chunks) {
+                                              int64_t n1_0, int chunks, uint32_t epi_stage,
+                                              int lane) {
   if (P.debug_flags & 2u) return;
+  if (P.num_peers) {
+    epilogue_rows_peers(P, taddr0, row, n1_0, chunks, epi_stage, lane);
+    return;
+  }
   if (P.out_row_major) {
     epilogue_rows_rowmajor(P, taddr0, row, n1_0 * 16, chunks);
     return;
@@ -398,10 +476,6 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
         }
         st_global_v8(dst, &r[0]);
         st_global_v8(dst + 32, &r[8]);
-        for (int g = 0; g < P.num_peers; ++g) {  // the same tile row into every peer's buffer
-          st_global_v8(dst + P.peer_delta[g], &r[0]);
-          st_global_v8(dst + P.peer_delta[g] + 32, &r[8]);
-        }
       } else {
         uint4* d4 = reinterpret_cast<uint4*>(dst);
         if (P.accumulate) {
@@ -419,12 +493,6 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
 #pragma unroll
         for (int v = 0; v < 4; ++v)
           d4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-        for (int g = 0; g < P.num_peers; ++g) {
-          uint4* p4 = reinterpret_cast<uint4*>(dst + P.peer_delta[g]);
-#pragma unroll
-          for (int v = 0; v < 4; ++v)
-            p4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-        }
       }
     }
   }
@@ -671,6 +739,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
     // ------------------------------- epilogue -------------------------------
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
     const int m_local = q * 32 + lane;
+    const uint32_t epi_stage = stage_base + uint32_t(S) * stage_bytes + uint32_t(q) * kEpiStageBytes;
     int buf = 0;
     uint32_t buf_phase = 0;
     const int chunks = P.bn >> 4;
@@ -690,7 +759,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
         epilogue_rows_dual(P, t_hi, t_hi + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
       } else {
         const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
-        epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks);
+        epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks, epi_stage, lane);
       }
       tc_fence_before();
       __syncwarp();
@@ -869,6 +938,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
   } else {
     // ------------------------------- epilogue (both CTAs) -------------------------------
     const int q = warp & 3;
+    const uint32_t epi_stage = stage_base + uint32_t(S) * stage_bytes + uint32_t(q) * kEpiStageBytes;
     int buf = 0;
     uint32_t buf_phase = 0;
     const int chunks = P.bn >> 4;
@@ -883,7 +953,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
       tc_fence_after();
       const int64_t row = int64_t(mt) * 256 + int64_t(rank) * 128 + q * 32 + lane;
       const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
-      epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks);
+      epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks, epi_stage, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[buf]), 0));
@@ -1587,7 +1657,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   const int smem_budget = 200 * 1024;
   P.num_stages = std::max(2, std::min(kMaxStages, smem_budget / stage_bytes));
-  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 + (num_peers ? 4 * kEpiStageBytes : 0);
 
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
