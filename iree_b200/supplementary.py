@@ -73,7 +73,8 @@ def _rand_bytes(n):
     return torch.randint(0, 256, (n,), dtype=torch.uint8, device="cuda")
 
 
-def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None, copies=1):
+def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None, copies=1,
+                graph_calls=0):
     """``copies`` > 1: the call is timed as a sweep over that many independent buffer sets
     (see _time_rotating); otherwise one call per event pair, with ``flush`` read in between."""
     lb, rb, _ = abi.MMT4D_BITS[flags & 0xFF]
@@ -101,7 +102,38 @@ def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None
     res = {"ms": med, "ms_best": best, "path": path, "tops": ops / med / 1e9}
     if copies > 1:
         res["timing"] = "sweep over %d buffer sets (footprint > L2), one event pair" % copies
+    if graph_calls:
+        res["graph_replay"] = _graph_replay(fns, graph_calls, ops)
     return name, res
+
+
+def _graph_replay(fns, calls, ops_per_call):
+    """``calls`` launches (cycling over the buffer sets) captured once in a CUDA graph and
+    replayed: per-call time without the host's launch path."""
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fns[0]()  # anything lazily created on first use happens outside the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(calls):
+                fns[i % len(fns)]()
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        g.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(5):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) / calls)
+    times.sort()
+    med = times[len(times) // 2]
+    return {"calls_per_graph": calls, "ms_per_call": med, "tops": ops_per_call / med / 1e9}
 
 
 def _matmul_rowmajor_case(M, N, K, bf16_peak):
@@ -180,7 +212,9 @@ def run(peaks, only=None, custom=None):
     ]:
         if not want(name):
             continue
-        k, r = _mmt4d_case(name, *args, peaks, None, copies=24 if args[1] < 512 else 1)
+        small = args[1] < 512
+        k, r = _mmt4d_case(name, *args, peaks, None, copies=24 if small else 1,
+                           graph_calls=100 if small else 0)
         r["frac_of_2x_bf16_burst"] = r["tops"] / (2 * bf16_peak)
         r["frac_of_spec_4500"] = r["tops"] / 4500.0
         res[k] = r
@@ -208,10 +242,11 @@ def run(peaks, only=None, custom=None):
     # decode GEMV s16u4s32: bytes are the algorithmic figure (weights + vector + output)
     if want("mmt4d_s16u4s32_gemv_1x14336x4096"):
         k, r = _mmt4d_case("mmt4d_s16u4s32_gemv_1x14336x4096", abi.MMT4D_S16U4S32, 1, 448, 512,
-                           1, 32, 8, peaks, None, copies=10)
+                           1, 32, 8, peaks, None, copies=10, graph_calls=100)
         gemv_bytes = 448 * 512 * 128 + 512 * 16 + 448 * 32 * 4
         r["gbs"] = gemv_bytes / r["ms"] / 1e6
         r["frac_hbm"] = r["gbs"] / hbm
+        r["graph_replay"]["gbs"] = gemv_bytes / r["graph_replay"]["ms_per_call"] / 1e6
         res[k] = r
 
     # row-major matmul at the headline dimensions: the fused entry point beside the chain
