@@ -157,6 +157,100 @@ class CpuReference:
         return max(self.threads, rows // self.threads * self.threads)
 
 
+def cpu_supplementary():
+    """The CPU reference on the other configurations of the path (or bounded samples of them),
+    all host threads, best of a few runs: the small s8 GEMM, the f16 GEMM with ACCUMULATE
+    (M reduced), the s16u4 GEMV, and the f32 pack / i32 unpack of an 8192 x 8192 matrix."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    import numpy as np
+
+    import oracle
+    from iree_b200 import abi
+    impl = "ref" if oracle.ref_available() else "oracle"
+    kind = "reference" if impl == "ref" else "port"
+    threads = os.cpu_count() or 1
+    rng = np.random.default_rng(7)
+    res = {}
+
+    def best(fn, runs=3):
+        times = []
+        for _ in range(runs):
+            t0 = time.perf_counter()
+            fn()
+            times.append(time.perf_counter() - t0)
+        return min(times)
+
+    def mmt4d_case(name, flags, M, N, K, m0, n0, k0, lhs, rhs, out, sample):
+        p = abi.Mmt4dParams()
+        p.lhs_buffer, p.rhs_buffer, p.out_buffer = lhs.ctypes.data, rhs.ctypes.data, out.ctypes.data
+        p.M, p.N, p.K, p.M0, p.N0, p.K0, p.flags = M, N, K, m0, n0, k0, flags
+        lb, rb, _ = abi.MMT4D_BITS[flags & 0xFF]
+        p.lhs_stride0, p.rhs_stride0, p.out_stride0 = K * m0 * k0, K * n0 * k0, N * m0 * n0
+        used = [0]
+
+        def run():
+            used[0] = oracle.mmt4d_threaded(p, threads, impl)
+        sec = best(run)
+        ops = 2.0 * M * m0 * N * n0 * K * k0
+        res[name] = {"ms": sec * 1e3, "tops": ops / sec / 1e12, "threads": used[0], "kind": kind,
+                     "sample": sample}
+
+    i8 = lambda n: rng.integers(-128, 128, n, dtype=np.int8)
+    mmt4d_case("mmt4d_s8s8s32_1024x1024x1024", abi.MMT4D_S8S8S32, 64, 64, 512, 16, 16, 2,
+               i8(1 << 20), i8(1 << 20), np.zeros(1 << 20, dtype=np.int32), "whole problem")
+    f16 = lambda n: rng.standard_normal(n, dtype=np.float32).astype(np.float16)
+    rows = 64
+    mmt4d_case("mmt4d_f16f16f32_acc_4096x4096x4096", abi.MMT4D_F16F16F32 | abi.MMT4D_ACCUMULATE,
+               rows, 256, 4096, 16, 16, 1, f16(rows * 4096 * 16), f16(256 * 4096 * 16),
+               rng.standard_normal(rows * 256 * 256, dtype=np.float32),
+               "M reduced to %d of 256 LHS tile rows" % rows)
+    mmt4d_case("mmt4d_s16u4s32_gemv_1x14336x4096", abi.MMT4D_S16U4S32, 1, 448, 512, 1, 32, 8,
+               rng.integers(-32768, 32768, 4096, dtype=np.int16),
+               rng.integers(0, 256, 448 * 512 * 128, dtype=np.uint8),
+               np.zeros(448 * 32, dtype=np.int32), "whole problem, N split over threads")
+    res["mmt4d_s16u4s32_gemv_1x14336x4096"]["gbs"] = \
+        29425664 / res["mmt4d_s16u4s32_gemv_1x14336x4096"]["ms"] / 1e6
+
+    # pack f32 8192 x 8192 -> [512][8192][16][1] and unpack i32 [512][512][16][16] -> 8192 x 8192,
+    # outer tile rows split over threads (callers slice the work, ukernel/README.md:26)
+    n = 8192
+    src = rng.standard_normal(n * n, dtype=np.float32)
+    dst = np.empty(n * n, dtype=np.float32)
+
+    def slices(total):
+        per = -(-total // threads)
+        return [(b, min(per, total - b)) for b in range(0, total, per)]
+
+    def pack_job(b, c):
+        q = abi.PackParams()
+        q.in_buffer, q.out_buffer = src.ctypes.data, dst.ctypes.data
+        q.in_offset, q.out_offset = b * 16 * n, b * n * 16
+        q.in_size0, q.in_size1, q.in_stride0, q.in_stride1 = c * 16, n, n, 1
+        q.out_size0, q.out_size1, q.out_size2, q.out_size3 = c, n, 16, 1
+        q.out_stride1, q.out_stride0, q.flags = 16, n * 16, abi.PACK_F32F32
+        return q
+
+    def unpack_job(b, c):
+        q = abi.UnpackParams()
+        q.in_buffer, q.out_buffer = src.ctypes.data, dst.ctypes.data
+        q.in_offset, q.out_offset = b * 512 * 256, b * 16 * n
+        q.in_size0, q.in_size1, q.in_size2, q.in_size3 = c, 512, 16, 16
+        q.in_stride1, q.in_stride0 = 256, 512 * 256
+        q.out_size0, q.out_size1, q.out_stride0, q.out_stride1 = c * 16, n, n, 1
+        q.flags = abi.UNPACK_I32I32
+        return q
+
+    for name, make, call in [("pack_f32_8192x8192_to_512x8192x16x1", pack_job, oracle.pack),
+                             ("unpack_i32_512x512x16x16_to_8192x8192", unpack_job, oracle.unpack)]:
+        jobs = [make(b, c) for b, c in slices(512)]
+        with ThreadPoolExecutor(len(jobs)) as ex:
+            sec = best(lambda: list(ex.map(lambda q: call(q, impl), jobs)))
+        res[name] = {"ms": sec * 1e3, "gbs": 2.0 * n * n * 4 / sec / 1e9, "threads": len(jobs),
+                     "kind": kind, "sample": "whole problem, bytes = read + written"}
+    return res
+
+
 def sample_flops(rows):
     return 2.0 * (rows * M0) * (N1 * N0) * (K1 * K0)
 
@@ -442,6 +536,7 @@ def main():
         try:
             from iree_b200 import supplementary
             line["supplementary"] = supplementary.run(peaks)
+            line["supplementary_cpu_reference"] = cpu_supplementary()
         except Exception as e:  # supplementary figures never block the headline line
             line["supplementary"] = {"error": repr(e)}
     print(json.dumps(line), flush=True)
