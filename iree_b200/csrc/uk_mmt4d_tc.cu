@@ -171,6 +171,18 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
                : "memory");
 }
+// Programmatic dependent launch. A pre-pass kernel calls pdl_launch_dependents() at its start:
+// the main kernel that follows it in the stream may then be scheduled while the pre-pass's last
+// blocks still run, and overlaps its own set-up (barriers, TMEM allocation) with them. Every
+// thread of a main kernel calls pdl_wait() after that set-up and before it touches global
+// memory: it returns once the preceding kernel has completed and its writes are visible.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() {
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
 }
@@ -636,6 +648,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
@@ -832,6 +845,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------- TMA producer (both CTAs) -------------------------------
@@ -990,6 +1004,7 @@ struct RetileOperand {
 template <int G>
 __global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOperand opb,
                                                      int64_t dst_pitch_b, int64_t K1, int kchunks) {
+  pdl_launch_dependents();
   const bool is_a = int64_t(blockIdx.x) < opa.blocks;
   const char* __restrict__ src = is_a ? opa.src : opb.src;
   const int64_t src_stride_b = is_a ? opa.src_stride_b : opb.src_stride_b;
@@ -1146,6 +1161,7 @@ __global__ void __launch_bounds__(256) split_s16_kernel(const char* __restrict__
 __global__ void __launch_bounds__(256) unpack_u4_kernel(const char* __restrict__ rhs,
                                                         int64_t rhs_stride_b, char* __restrict__ dst,
                                                         int64_t pitch_b, int64_t K1, int kchunks) {
+  pdl_launch_dependents();
   constexpr int KC = 64, PITCH = KC * 8 + 16;
   __shared__ __align__(16) unsigned char sm[32 * PITCH];
   const int64_t n1 = blockIdx.x / kchunks;
@@ -1254,6 +1270,53 @@ int max_pair_clusters(size_t smem) {
   return n;
 }
 
+// What the launchers need to know about the current device, found once per device: the
+// kernels' dynamic shared memory limit is raised to the device maximum at that point, so the
+// per-call path makes no attribute or occupancy calls.
+struct DeviceInfo {
+  bool ok = false;
+  int sms = 0;
+  int max_smem = 0;           // dynamic shared memory per block the kernels may be launched with
+  int pair_clusters[2] = {};  // co-resident CTA pairs of mmt4d_tc2_kernel<false / true>
+};
+
+const DeviceInfo* device_info() {
+  constexpr int kMaxDevices = 64;
+  static DeviceInfo info[kMaxDevices];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceInfo& d = info[dev];
+  if (!d.ok) {
+    if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&d.max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+      return nullptr;
+    // dynamic limit of each kernel = the device's opt-in maximum minus its static shared memory
+    int dyn_limit = d.max_smem;
+    auto raise_limit = [&](const void* fn) {
+      cudaFuncAttributes fa;
+      if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return false;
+      const int dyn = d.max_smem - int(fa.sharedSizeBytes);
+      dyn_limit = std::min(dyn_limit, dyn);
+      return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess;
+    };
+    if (!raise_limit(reinterpret_cast<const void*>(mmt4d_tc_kernel<false>)) ||
+        !raise_limit(reinterpret_cast<const void*>(mmt4d_tc_kernel<true>)) ||
+        !raise_limit(reinterpret_cast<const void*>(mmt4d_tc2_kernel<false>)) ||
+        !raise_limit(reinterpret_cast<const void*>(mmt4d_tc2_kernel<true>))) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    d.max_smem = dyn_limit;
+    const size_t smem_probe = size_t(6) * (BM * 128 + 128 * 128) + 1024;
+    d.pair_clusters[0] = max_pair_clusters<false>(smem_probe);
+    d.pair_clusters[1] = max_pair_clusters<true>(smem_probe);
+    d.ok = true;
+  }
+  return &d;
+}
+
 // Accumulator width for the pair kernel: among the multiples of 32 columns up to 256, the one
 // that minimises (waves of 256 x bn tiles over `clusters` pairs) x bn, i.e. the estimated time.
 int pick_bn_pair(int64_t M1, int64_t N1, int clusters) {
@@ -1339,6 +1402,34 @@ S16U4Layout s16u4_layout(const iree_uk_mmt4d_params_t* p) {
   return l;
 }
 
+// Launches a main kernel (one-CTA form when cluster == 1, CTA pairs when cluster == 2) with
+// programmatic stream serialisation, so that it may overlap the tail of the pre-pass kernel
+// enqueued just before it (see pdl_wait).
+template <typename Kernel>
+cudaError_t launch_main(Kernel kernel, int grid, int cluster, size_t smem, cudaStream_t stream,
+                        const TcParams& P) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(unsigned(grid), 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int n = 0;
+  attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = unsigned(cluster);
+    attrs[n].val.clusterDim.y = 1;
+    attrs[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = unsigned(n);
+  return cudaLaunchKernelEx(&cfg, kernel, P);
+}
+
 int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes,
                           cudaStream_t stream) {
   if (!mmt4d_tc_s16u4_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
@@ -1412,15 +1503,12 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
   const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const DeviceInfo* di = device_info();
+  if (!di || smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
   if (tev) cudaEventRecord(tev[1], stream);
-  if (cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           int(smem)) != cudaSuccess)
+  const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
+  if (launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P) != cudaSuccess)
     return IREE_UK_B200_CUDA_ERROR;
-  const int grid = std::min(P.m_tiles * P.n_tiles, sms);
-  mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
   if (tev) {
     cudaEventRecord(tev[2], stream);
     ++timing.calls;
@@ -1485,7 +1573,8 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || !mmt4d_tc_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
   uint32_t* status = device_status_word();
-  if (!status) return IREE_UK_B200_CUDA_ERROR;
+  const DeviceInfo* di = device_info();
+  if (!status || !di) return IREE_UK_B200_CUDA_ERROR;
 
   TcParams P;
   std::memset(&P, 0, sizeof P);
@@ -1545,10 +1634,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     const size_t need = mmt4d_tc_workspace_size(p);
     if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
     if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
-    const size_t smem_probe = size_t(6) * (BM * 128 + 128 * 128) + 1024;
-    if (ti.is_int) cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
-    else cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
-    pair_clusters = ti.is_int ? max_pair_clusters<true>(smem_probe) : max_pair_clusters<false>(smem_probe);
+    pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0];
     if (pair_clusters < 1) return IREE_UK_B200_CUDA_ERROR;
     bn = pick_bn_pair(p->M, p->N, pair_clusters);
     const int64_t pitch = round_up(kelems * ti.es, 128);
@@ -1659,47 +1745,19 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   P.num_stages = std::max(2, std::min(kMaxStages, smem_budget / stage_bytes));
   const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 + (num_peers ? 4 * kEpiStageBytes : 0);
 
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
   cudaError_t e;
   if (tev) cudaEventRecord(tev[1], stream);
   if (pair) {
-    const int clusters = std::min(P.m_tiles * P.n_tiles, pair_clusters);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(2 * clusters), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    if (ti.is_int) {
-      e = cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<true>, P);
-    } else {
-      e = cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<false>, P);
-    }
-    if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+    const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
+    e = ti.is_int ? launch_main(mmt4d_tc2_kernel<true>, grid, 2, smem, stream, P)
+                  : launch_main(mmt4d_tc2_kernel<false>, grid, 2, smem, stream, P);
   } else {
-    const int grid = std::min(P.m_tiles * P.n_tiles, sms);
-    if (ti.is_int) {
-      e = cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
-    } else {
-      e = cudaFuncSetAttribute(mmt4d_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-      if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
-    }
+    const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
+    e = ti.is_int ? launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P)
+                  : launch_main(mmt4d_tc_kernel<false>, grid, 1, smem, stream, P);
   }
+  if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   if (tev) {
     cudaEventRecord(tev[2], stream);
     ++timing.calls;
@@ -1770,6 +1828,7 @@ __global__ void __launch_bounds__(256) transpose_kn_kernel(const char* __restric
   using E = typename std::conditional<ES == 1, uint8_t, uint16_t>::type;
   constexpr int T = 64;
   __shared__ E tile[T][T + 2 * (4 / ES) + 0];  // [n][k], padded
+  pdl_launch_dependents();
   const int64_t k_base = int64_t(blockIdx.y) * T, n_base = int64_t(blockIdx.x) * T;
   for (int e = threadIdx.x; e < T * T; e += blockDim.x) {
     const int k = e / T, n = e - k * T;
@@ -1832,7 +1891,8 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   if (!ws || ws_bytes < size_t(l.rhs_t_bytes + l.lhs_copy_bytes)) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
   uint32_t* status = device_status_word();
-  if (!status) return IREE_UK_B200_CUDA_ERROR;
+  const DeviceInfo* di = device_info();
+  if (!status || !di) return IREE_UK_B200_CUDA_ERROR;
   KernelTiming& timing = kernel_timing();
   cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
   if (tev) cudaEventRecord(tev[0], stream);
@@ -1867,10 +1927,7 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   bool pair = false;
   int pair_clusters = 0, bn = pick_bn(M1, N1), kboxes = 1;
   if (want_pair) {
-    const size_t smem_probe = size_t(6) * (BM * 128 + 128 * 128) + 1024;
-    if (ti.is_int) cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
-    else cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_probe));
-    pair_clusters = ti.is_int ? max_pair_clusters<true>(smem_probe) : max_pair_clusters<false>(smem_probe);
+    pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0];
     if (pair_clusters >= 1) {
       pair = true;
       kboxes = 2;
@@ -1923,40 +1980,15 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   if (tev) cudaEventRecord(tev[1], stream);
   cudaError_t e;
   if (pair) {
-    const int clusters = std::min(P.m_tiles * P.n_tiles, pair_clusters);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(unsigned(2 * clusters), 1, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    if (ti.is_int) {
-      if (cudaFuncSetAttribute(mmt4d_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<true>, P);
-    } else {
-      if (cudaFuncSetAttribute(mmt4d_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      e = cudaLaunchKernelEx(&cfg, mmt4d_tc2_kernel<false>, P);
-    }
-    if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+    const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
+    e = ti.is_int ? launch_main(mmt4d_tc2_kernel<true>, grid, 2, smem, stream, P)
+                  : launch_main(mmt4d_tc2_kernel<false>, grid, 2, smem, stream, P);
   } else {
-    int dev = 0, sms = 148;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int grid = std::min(P.m_tiles * P.n_tiles, sms);
-    if (ti.is_int) {
-      if (cudaFuncSetAttribute(mmt4d_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      mmt4d_tc_kernel<true><<<grid, kThreads, smem, stream>>>(P);
-    } else {
-      if (cudaFuncSetAttribute(mmt4d_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-      mmt4d_tc_kernel<false><<<grid, kThreads, smem, stream>>>(P);
-    }
+    const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
+    e = ti.is_int ? launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P)
+                  : launch_main(mmt4d_tc_kernel<false>, grid, 1, smem, stream, P);
   }
+  if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   if (tev) {
     cudaEventRecord(tev[2], stream);
     ++timing.calls;
