@@ -256,6 +256,22 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws_peers(const iree_uk_mmt4d_params_t
                                                     int num_peers, void* workspace,
                                                     size_t workspace_bytes, void* cu_stream);
 
+/* The N-sharded mmt4d driven from ONE process that owns several GPUs. For g in [0, n_gpus):
+ * makes device_ids[g] current and enqueues per_gpu[g] (as produced by
+ * iree_uk_b200_mmt4d_shard_params, with buffers on that device) on streams[g] with
+ * workspaces[g] / workspace_bytes[g]; the caller's current device is restored afterwards.
+ * replicate_output = 0: every GPU writes only its own buffer (no data-path collective).
+ * replicate_output = 1: per_gpu[g].out_buffer must be a full [M][N][M0][N0] buffer on GPU g
+ * addressed with out_is_local = 0; peer access between the devices is enabled as needed and
+ * every GPU stores its tile columns into all n_gpus buffers (iree_uk_b200_mmt4d_ws_peers), so
+ * that after all streams have completed each buffer holds the whole result. Returns the first
+ * non-zero status; work enqueued before it stays enqueued. n_gpus <= IREE_UK_B200_MAX_PEERS + 1. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_sharded(int n_gpus, const int* device_ids,
+                                                   const iree_uk_mmt4d_params_t* per_gpu,
+                                                   void* const* workspaces,
+                                                   const size_t* workspace_bytes,
+                                                   void* const* cu_streams, int replicate_output);
+
 /* What one process hands to another (same machine) so that the other can address this
  * process's device buffer: a CUDA IPC handle of the allocation plus the buffer's offset in it. */
 typedef struct iree_uk_b200_peer_handle_t {

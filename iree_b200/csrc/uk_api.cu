@@ -180,6 +180,41 @@ int iree_uk_b200_mmt4d_ws_peers(const iree_uk_mmt4d_params_t* params,
                          static_cast<cudaStream_t>(cu_stream), peer_out_buffers, num_peers);
 }
 
+int iree_uk_b200_mmt4d_sharded(int n_gpus, const int* device_ids,
+                               const iree_uk_mmt4d_params_t* per_gpu, void* const* workspaces,
+                               const size_t* workspace_bytes, void* const* cu_streams,
+                               int replicate_output) {
+  if (n_gpus < 1 || n_gpus > IREE_UK_B200_MAX_PEERS + 1 || !device_ids || !per_gpu || !workspaces ||
+      !workspace_bytes || !cu_streams)
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  int previous = 0;
+  if (cudaGetDevice(&previous) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  int rc = IREE_UK_B200_OK;
+  for (int g = 0; g < n_gpus && rc == IREE_UK_B200_OK; ++g) {
+    if (cudaSetDevice(device_ids[g]) != cudaSuccess) { rc = IREE_UK_B200_CUDA_ERROR; break; }
+    if (!replicate_output || n_gpus == 1) {
+      rc = iree_uk_b200_mmt4d_ws(&per_gpu[g], workspaces[g], workspace_bytes[g], cu_streams[g]);
+      continue;
+    }
+    const void* peers[IREE_UK_B200_MAX_PEERS];
+    int n = 0;
+    for (int h = 0; h < n_gpus && rc == IREE_UK_B200_OK; ++h) {
+      if (h == g) continue;
+      if (device_ids[h] != device_ids[g]) {
+        const cudaError_t e = cudaDeviceEnablePeerAccess(device_ids[h], 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+        else if (e != cudaSuccess) { cudaGetLastError(); rc = IREE_UK_B200_CUDA_ERROR; }
+      }
+      peers[n++] = per_gpu[h].out_buffer;
+    }
+    if (rc == IREE_UK_B200_OK)
+      rc = iree_uk_b200_mmt4d_ws_peers(&per_gpu[g], peers, n, workspaces[g], workspace_bytes[g],
+                                       cu_streams[g]);
+  }
+  cudaSetDevice(previous);
+  return rc;
+}
+
 namespace {
 struct PeerMapping {
   void* base;

@@ -75,6 +75,21 @@ def mmt4d_peers(params, peer_out_ptrs, workspace, stream=None):
                                            _stream_handle(stream)), "mmt4d_peers")
 
 
+def mmt4d_sharded(device_ids, per_gpu_params, workspaces, streams, replicate_output=False):
+    """The N-sharded mmt4d from one process that owns several GPUs: enqueues
+    ``per_gpu_params[g]`` on ``device_ids[g]`` / ``streams[g]`` with ``workspaces[g]`` (torch
+    uint8 tensors on that device). With ``replicate_output`` every GPU's full-size output
+    buffer receives all tile columns through peer stores."""
+    n = len(device_ids)
+    ids = (C.c_int * n)(*device_ids)
+    params = (abi.Mmt4dParams * n)(*per_gpu_params)
+    ws = (C.c_void_p * n)(*[w.data_ptr() for w in workspaces])
+    nb = (C.c_size_t * n)(*[w.numel() * w.element_size() for w in workspaces])
+    st = (C.c_void_p * n)(*[getattr(s, "cuda_stream", s) for s in streams])
+    _check(lib.iree_uk_b200_mmt4d_sharded(n, ids, params, ws, nb, st,
+                                          1 if replicate_output else 0), "mmt4d_sharded")
+
+
 def peer_export(device_ptr):
     """Bytes another process on this machine can pass to ``peer_open`` to address the device
     buffer at ``device_ptr`` (an int, or a tensor)."""
