@@ -1901,7 +1901,12 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   // else copied with a TMA-friendly pitch.
   char* rhs_t = static_cast<char*>(ws);
   char* lhs_copy = rhs_t + l.rhs_t_bytes;
-  {
+  // A 16-bit row-major RHS is itself a legal tensor-core operand: N-contiguous ("MN-major")
+  // rows that TMA stages as 64-column x K swizzled boxes. It needs TMA's alignment; 8-bit
+  // operands must be K-major, so they are always transposed.
+  const bool b_direct = ti.es == 2 && (reinterpret_cast<uintptr_t>(rhs) & 15) == 0 &&
+                        (rhs_pitch_b & 15) == 0 && !debug_int("IREE_UK_B200_DEBUG_MATMUL_TRANSPOSE", 0);
+  if (!b_direct) {
     dim3 grid(unsigned((N + 63) / 64), unsigned((K + 63) / 64));
     if (grid.y > 65535) return IREE_UK_B200_UNSUPPORTED;
     if (ti.es == 1) transpose_kn_kernel<1><<<grid, 256, 0, stream>>>(rhs, rhs_pitch_b, rhs_t, l.pitch, K, N);
@@ -1934,25 +1939,57 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
       bn = pick_bn_pair(M1, N1, pair_clusters);
     }
   }
-  const int b_rows = pair ? bn / 2 : bn;  // RHS rows one CTA stages
-  const uint64_t da[3] = {uint64_t(K), uint64_t(M), 1};
-  const uint64_t db[3] = {uint64_t(K), uint64_t(N), 1};
-  const uint64_t sa[2] = {uint64_t(a_pitch), uint64_t(a_pitch) * uint64_t(M)};
-  const uint64_t sb[2] = {uint64_t(l.pitch), uint64_t(l.pitch) * uint64_t(N)};
-  const uint32_t ba[3] = {uint32_t(kblk_elems), BM, 1};
-  const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(b_rows), 1};
-  if (!encode_map(&P.map_a, ti.tm_type, const_cast<char*>(a_ptr), da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
-      !encode_map(&P.map_b, ti.tm_type, rhs_t, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
-    return IREE_UK_B200_CUDA_ERROR;
+  if (b_direct) {
+    // whole 64-column swizzle atoms per CTA: 128 or 256 columns per CTA pair, 64..256 per CTA
+    if (pair) {
+      const int64_t mt = (M + 255) / 256;
+      auto cost = [&](int w) {
+        const int64_t tiles = mt * ((N + w - 1) / w);
+        return ((tiles + pair_clusters - 1) / pair_clusters) * (w + 32);
+      };
+      bn = cost(128) < cost(256) ? 128 : 256;
+    } else {
+      bn = N > 128 ? 256 : (N > 64 ? 128 : 64);
+    }
+  }
+  const int b_rows = pair ? bn / 2 : bn;  // RHS rows (output columns) one CTA stages
   const int tile_m = pair ? 2 * BM : BM;
+  const uint64_t da[3] = {uint64_t(K), uint64_t(M), 1};
+  const uint64_t sa[2] = {uint64_t(a_pitch), uint64_t(a_pitch) * uint64_t(M)};
+  const uint32_t ba[3] = {uint32_t(kblk_elems), BM, 1};
+  if (!encode_map(&P.map_a, ti.tm_type, const_cast<char*>(a_ptr), da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B))
+    return IREE_UK_B200_CUDA_ERROR;
   P.sa = {kboxes, BM * 128, {kboxes * kblk_elems, 0, 0}, {0, tile_m, 0}, {kblk_elems, 0, 0}, {0, BM, 0}};
-  P.sb = {kboxes, b_rows * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}, {0, b_rows, 0}};
   P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
   P.desc_lbo_a = P.desc_lbo_b = 1;
   P.kadv_a = P.kadv_b = 2;
   P.kbox_units_a = uint32_t(BM * 128) >> 4;
-  P.kbox_units_b = uint32_t(b_rows * 128) >> 4;
   P.idesc = make_idesc(ti, bn, false, tile_m);
+  if (b_direct) {
+    // [K][N] as it lies: boxes of 64 columns (one 128-byte swizzle row) x all K rows of a stage.
+    // In shared memory a box is [k][64 columns]; 8 K rows form one 1 KB swizzle atom (stride
+    // byte offset), the next 64 columns are the next box (leading byte offset).
+    const int stage_rows = kboxes * kblk_elems;
+    const uint64_t db[3] = {uint64_t(N), uint64_t(K), 1};
+    const uint64_t sb[2] = {uint64_t(rhs_pitch_b), uint64_t(rhs_pitch_b) * uint64_t(K)};
+    const uint32_t bb[3] = {64, uint32_t(stage_rows), 1};
+    if (!encode_map(&P.map_b, ti.tm_type, const_cast<char*>(rhs), db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+      return IREE_UK_B200_CUDA_ERROR;
+    const int box_bytes = stage_rows * 128;
+    P.sb = {b_rows / 64, box_bytes, {0, stage_rows, 0}, {bn, 0, 0}, {64, 0, 0}, {b_rows, 0, 0}};
+    P.desc_lbo_b = uint32_t(box_bytes) >> 4;
+    P.kadv_b = (16 * 128) >> 4;                 // 16 K rows per MMA
+    P.kbox_units_b = (kblk_elems * 128) >> 4;   // K rows covered by one K box of the LHS
+    P.idesc |= 1u << 16;                        // B is MN-major
+  } else {
+    const uint64_t db[3] = {uint64_t(K), uint64_t(N), 1};
+    const uint64_t sb[2] = {uint64_t(l.pitch), uint64_t(l.pitch) * uint64_t(N)};
+    const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(b_rows), 1};
+    if (!encode_map(&P.map_b, ti.tm_type, rhs_t, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+      return IREE_UK_B200_CUDA_ERROR;
+    P.sb = {kboxes, b_rows * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}, {0, b_rows, 0}};
+    P.kbox_units_b = uint32_t(b_rows * 128) >> 4;
+  }
   P.kboxes = kboxes;
   P.mma_per_box = 4;
   P.stage_bytes_a = kboxes * BM * 128;
