@@ -151,9 +151,12 @@ int iree_uk_b200_mmt4d_flat(const void* lhs_buffer, iree_uk_index_t lhs_offset,
 
 uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t flags) {
   const uint32_t type = flags & IREE_UK_FLAG_MMT4D_TYPE_MASK;
+  const bool skip = (flags & IREE_UK_FLAG_MMT4D_SKIP_INTERMEDIATE_ROUNDINGS) != 0;
   const bool tc_type = type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 ||
                        type == IREE_UK_FLAG_MMT4D_TYPE_F16F16F32 ||
-                       type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32;
+                       type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32 ||
+                       (skip && (type == IREE_UK_FLAG_MMT4D_TYPE_F16F16F16 ||
+                                 type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16BF16));
   const int es = type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 ? 1 : 2;
   const int g = K0 * es;
   if (tc_type && M0 == 16 && N0 == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16))

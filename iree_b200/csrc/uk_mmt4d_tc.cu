@@ -29,6 +29,8 @@
 // their loops; the producer then waits (bounded) for its own copies in flight, TMEM is
 // freed and the kernel returns.
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <algorithm>
 #include <cstdlib>
@@ -79,6 +81,7 @@ struct TcParams {
   int32_t accumulate;
   int32_t out_is_int;
   int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
+  int32_t out16;         // 0: 32-bit output; 1: f16 output, 2: bf16 output (rounded once, RNE)
   int32_t num_peers;     // copies of every output tile also stored to this many peer buffers
   int64_t peer_delta[IREE_UK_B200_MAX_PEERS];  // byte distance from `out` to each peer's buffer
   int32_t out_row_major; // fused matmul: the output is a row-major rows x cols matrix
@@ -448,6 +451,52 @@ __device__ __forceinline__ void epilogue_rows_peers(const TcParams& P, uint32_t 
   __syncwarp();
 }
 
+// 16-bit output (f16f16f16 / bf16bf16bf16 with one final rounding): lane owns row (m1, m0) of
+// 16x16 tiles of 512 bytes; its 16 values of a tile are one 32-byte row.
+__device__ __forceinline__ uint32_t pack_out16(float lo, float hi, int kind) {
+  if (kind == 1) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&b);
+}
+__device__ __forceinline__ float2 unpack_out16(uint32_t v, int kind) {
+  if (kind == 1) return __half22float2(*reinterpret_cast<const __half2*>(&v));
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
+__device__ __forceinline__ void epilogue_rows_out16(const TcParams& P, uint32_t taddr0, int64_t row,
+                                                    int64_t n1_0, int chunks) {
+  const int64_t m1 = row >> 4;
+  const int m0 = int(row & 15);
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[16];
+    tmem_ld16(taddr0 + uint32_t(c * 16), r);
+    tmem_ld_wait();
+    const int64_t n1 = n1_0 + c;
+    if (m1 < P.M1 && n1 < P.N1 && !(P.debug_flags & 1u)) {
+      uint4* d4 = reinterpret_cast<uint4*>(P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 2);
+      uint32_t w[8];
+      if (P.accumulate) {
+        const uint4 o0 = d4[0], o1 = d4[1];
+        const uint32_t o[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float2 old = unpack_out16(o[j], P.out16);
+          w[j] = pack_out16(__uint_as_float(r[2 * j]) + old.x, __uint_as_float(r[2 * j + 1]) + old.y,
+                            P.out16);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          w[j] = pack_out16(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]), P.out16);
+      }
+      d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  }
+}
+
 // Epilogue of one accumulator tile for one warp: lanes own rows row0 .. row0+31 of the output
 // (row = m1*16 + m0), `chunks` groups of 16 columns starting at tile column n1_0. Each thread
 // moves one 64-byte row of a 16x16 output tile per chunk. All 32 lanes must call this.
@@ -457,6 +506,10 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
   if (P.debug_flags & 2u) return;
   if (P.num_peers) {
     epilogue_rows_peers(P, taddr0, row, n1_0, chunks, epi_stage, lane);
+    return;
+  }
+  if (P.out16) {
+    epilogue_rows_out16(P, taddr0, row, n1_0, chunks);
     return;
   }
   if (P.out_row_major) {
@@ -1235,13 +1288,20 @@ struct TypeInfo {
   uint32_t fmt;   // a/b format field of the instruction descriptor
   uint32_t cfmt;  // accumulator format
   CUtensorMapDataType tm_type;
+  int out_es;     // output element bytes: 4, or 2 for the f16 / bf16 output triples
 };
 
 bool tc_type_info(uint32_t flags, TypeInfo* ti) {
+  // The 16-bit-output triples accumulate in f32 on the tensor cores and round once at the end,
+  // which is what the reference computes only under SKIP_INTERMEDIATE_ROUNDINGS
+  // (mmt4d_tile_generic.c:395-404); without that flag they stay on the generic kernel.
+  const bool skip = (flags & IREE_UK_FLAG_MMT4D_SKIP_INTERMEDIATE_ROUNDINGS) != 0;
   switch (flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) {
-    case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: *ti = {1, true, 1u, 2u, CU_TENSOR_MAP_DATA_TYPE_UINT8}; return true;
-    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32: *ti = {2, false, 0u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16}; return true;
-    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32: *ti = {2, false, 1u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16}; return true;
+    case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: *ti = {1, true, 1u, 2u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4}; return true;
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32: *ti = {2, false, 0u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4}; return true;
+    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32: *ti = {2, false, 1u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4}; return true;
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F16: *ti = {2, false, 0u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2}; return skip;
+    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16BF16: *ti = {2, false, 1u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2}; return skip;
     default: return false;
   }
 }
@@ -1526,9 +1586,10 @@ bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
   if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return false;
   const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * ti.es);
   const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset * ti.es);
-  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * 4);
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * ti.out_es);
   if ((lhs | rhs | out) & 15) return false;
-  if ((p->lhs_stride0 * ti.es) % 16 || (p->rhs_stride0 * ti.es) % 16 || (p->out_stride0 * 4) % 16)
+  if ((p->lhs_stride0 * ti.es) % 16 || (p->rhs_stride0 * ti.es) % 16 ||
+      (p->out_stride0 * ti.out_es) % 16)
     return false;
   if ((p->M + 7) / 8 * ((p->N + 3) / 4) > 0x3FFFFFFF) return false;
   return true;
@@ -1572,6 +1633,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || !mmt4d_tc_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
+  if (num_peers && ti.out_es != 4) return IREE_UK_B200_UNSUPPORTED;  // peer copies: 32-bit tiles only
   uint32_t* status = device_status_word();
   const DeviceInfo* di = device_info();
   if (!status || !di) return IREE_UK_B200_CUDA_ERROR;
@@ -1721,13 +1783,14 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   P.m_tiles = int((p->M * 16 + tile_m - 1) / tile_m);
   P.n_tiles = int((p->N * 16 + bn - 1) / bn);
   P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
-  P.out = static_cast<char*>(p->out_buffer) + p->out_offset * 4;
+  P.out = static_cast<char*>(p->out_buffer) + p->out_offset * ti.out_es;
   P.out_stride0 = p->out_stride0;
   P.M1 = p->M;
   P.N1 = p->N;
   P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
   P.out_is_int = ti.is_int ? 1 : 0;
-  P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * 4) % 32 == 0) ? 1 : 0;
+  P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * ti.out_es) % 32 == 0) ? 1 : 0;
+  P.out16 = ti.out_es == 2 ? (ti.fmt == 0u ? 1 : 2) : 0;
   P.num_peers = num_peers;
   for (int g = 0; g < num_peers; ++g) {
     const char* peer = static_cast<const char*>(peer_out_buffers[g]);

@@ -83,6 +83,37 @@ def test_mmt4d_tensor_core_loose_out_stride():
     assert np.array_equal(got, G.oracle_mmt4d(case))
 
 
+def _half_bits_to_f32(a, is_bf16):
+    u = a.view(np.uint16)
+    if is_bf16:
+        return (u.astype(np.uint32) << 16).view(np.float32)
+    return u.view(np.float16).astype(np.float32)
+
+
+@pytest.mark.parametrize("t,K0,is_bf16", [(abi.MMT4D_F16F16F16, 1, False),
+                                          (abi.MMT4D_BF16BF16BF16, 2, True)], ids=["f16", "bf16"])
+@pytest.mark.parametrize("shape", [(1, 1, 8), (9, 17, 65), (40, 24, 300), (160, 64, 64)],
+                         ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_16bit_output_on_tensor_cores(t, K0, is_bf16, shape, accumulate):
+    """f16f16f16 / bf16bf16bf16 with SKIP_INTERMEDIATE_ROUNDINGS (f32 accumulation, one final
+    rounding — what the reference's own benchmark runs, tools/mmt4d_benchmark.c:100) take the
+    tensor-core kernel; N(0,1) operands, relative Frobenius error <= 1e-3 against the oracle.
+    Without the flag the same problem stays on the generic kernel (rounding at every step)."""
+    M, N, K = shape
+    flags = t | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS
+    case = cases.Mmt4dCase(flags, 16, 16, K0, M, N, K, accumulate, seed=17, mode="normal",
+                           loose=False)
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    want = G.oracle_mmt4d(case)
+    err = cases.rel_frobenius(_half_bits_to_f32(got, is_bf16), _half_bits_to_f32(want, is_bf16))
+    assert err <= 1e-3, err
+    plain = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, accumulate, seed=17, mode="normal", loose=False)
+    _, path = G.run_mmt4d_case(plain)
+    assert path == abi.PATH_GENERIC
+
+
 @pytest.mark.parametrize("t,M0,N0,K0,M,N,K,acc,tol", [
     (abi.MMT4D_F16F16F32, 16, 16, 1, 16, 16, 512, 1, 1e-3),
     (abi.MMT4D_BF16BF16F32, 16, 16, 2, 24, 32, 256, 0, 1e-3),
