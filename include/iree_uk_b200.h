@@ -235,6 +235,18 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* para
                                               void* workspace, size_t workspace_bytes,
                                               void* cu_stream);
 
+/* How f32f32f32 with 16x16xK0 tiles is computed when scratch is supplied. The reference adds
+ * f32 products in k order; the default here does the same on the CUDA cores. TF32X3 moves the
+ * work to the tensor cores: each operand is split into a tf32 part and a remainder and every
+ * product becomes three tf32 products accumulated in f32 (measured 266 TFLOP/s at 8192^3, f32
+ * operations counted once). The result then differs
+ * from the reference's by a relative Frobenius error of about 7e-9 x K (1e-6 at K = 129, 5e-6
+ * at K = 700): tensor-core accumulation truncates. Process-wide, like a math mode; returns the
+ * previous mode. */
+#define IREE_UK_B200_F32_MODE_CUDA_CORES 0
+#define IREE_UK_B200_F32_MODE_TF32X3 1
+IREE_UK_B200_EXPORT int iree_uk_b200_set_f32_mode(int mode);
+
 /* Most peer output buffers one call of iree_uk_b200_mmt4d_ws_peers can store to. */
 #define IREE_UK_B200_MAX_PEERS 16
 

@@ -1,6 +1,7 @@
 // extern "C" entry points of libiree_uk_b200.so: validation, kernel selection, launch.
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -28,6 +29,9 @@ uint32_t* device_status_word() {
   }
   return addr[dev];
 }
+
+static std::atomic<int> g_f32_mode{0};
+int f32_mode() { return g_f32_mode.load(std::memory_order_relaxed); }
 
 KernelTiming& kernel_timing() {
   static KernelTiming t;
@@ -156,14 +160,21 @@ uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t fl
                        type == IREE_UK_FLAG_MMT4D_TYPE_F16F16F32 ||
                        type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32 ||
                        (skip && (type == IREE_UK_FLAG_MMT4D_TYPE_F16F16F16 ||
-                                 type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16BF16));
-  const int es = type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 ? 1 : 2;
+                                 type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16BF16)) ||
+                       (type == IREE_UK_FLAG_MMT4D_TYPE_F32F32F32 && f32_mode() == IREE_UK_B200_F32_MODE_TF32X3);
+  const int es = type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 ? 1 : (type == IREE_UK_FLAG_MMT4D_TYPE_F32F32F32 ? 4 : 2);
   const int g = K0 * es;
   if (tc_type && M0 == 16 && N0 == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16))
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 && M0 == 1 && N0 == 32 && K0 == 8)
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   return 0;
+}
+
+int iree_uk_b200_set_f32_mode(int mode) {
+  if (mode != IREE_UK_B200_F32_MODE_CUDA_CORES && mode != IREE_UK_B200_F32_MODE_TF32X3)
+    return g_f32_mode.load();
+  return g_f32_mode.exchange(mode);
 }
 
 int iree_uk_b200_mmt4d_ws_peers(const iree_uk_mmt4d_params_t* params,

@@ -63,6 +63,9 @@ size_t matmul_workspace_size(uint32_t flags, int64_t M, int64_t N, int64_t K);
 int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b, const char* rhs,
                            int64_t rhs_pitch_b, char* out, int64_t out_stride0, int64_t M, int64_t N,
                            int64_t K, void* ws, size_t ws_bytes, cudaStream_t stream);
+// Process-wide choice for f32f32f32 with 16x16 tiles: 0 = CUDA cores in the reference's
+// accumulation order (default), 1 = tensor cores, three tf32 products per term.
+int f32_mode();
 constexpr int kTcVariantDefault = 0;
 constexpr int kTcVariantDirect = 3;  // MN-major, 32-byte swizzle, straight from the operand
 // f16f16f32 / bf16bf16f32 with M0 = N0 = 16 and K0 = 1: served by the tensor cores without scratch.

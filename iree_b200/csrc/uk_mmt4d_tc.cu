@@ -81,6 +81,7 @@ struct TcParams {
   int32_t accumulate;
   int32_t out_is_int;
   int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
+  int32_t triple;        // f32 operands as hi/lo tf32 planes, three MMAs per K slice
   int32_t out16;         // 0: 32-bit output; 1: f16 output, 2: bf16 output (rounded once, RNE)
   int32_t num_peers;     // copies of every output tile also stored to this many peer buffers
   int64_t peer_delta[IREE_UK_B200_MAX_PEERS];  // byte distance from `out` to each peer's buffer
@@ -260,6 +261,29 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
                : "memory");
 }
+// kind::tf32: 32-bit operands of which the tensor core uses sign, exponent and 10 mantissa bits.
+template <bool PAIR>
+__device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  if (PAIR) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
 template <bool IS_INT>
 __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                             uint32_t idesc, uint32_t accumulate) {
@@ -610,7 +634,7 @@ __device__ __forceinline__ void issue_operand_loads(const CUtensorMap* map, cons
 // lives in registers of the single issuing thread.
 struct MmaIssue {
   uint32_t lo_a, lo_b, hi_a, hi_b, kadv_a, kadv_b, kbox_a, kbox_b, idesc, idesc2;
-  int kboxes, mma_per_box, dual;
+  int kboxes, mma_per_box, dual, triple;
 };
 __device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
   MmaIssue m;
@@ -619,7 +643,7 @@ __device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
   m.kadv_a = P.kadv_a; m.kadv_b = P.kadv_b;
   m.kbox_a = P.kbox_units_a; m.kbox_b = P.kbox_units_b;
   m.idesc = P.idesc; m.kboxes = P.kboxes; m.mma_per_box = P.mma_per_box;
-  m.idesc2 = P.idesc2; m.dual = P.dual;
+  m.idesc2 = P.idesc2; m.dual = P.dual; m.triple = P.triple;
   return m;
 }
 // Dual-LHS stage (s16u4s32): shared memory holds [high-byte plane | low-byte plane | RHS]; each K
@@ -646,6 +670,25 @@ template <bool IS_INT, bool PAIR>
 __device__ __forceinline__ void issue_stage_mmas(const MmaIssue& m, uint32_t d_tmem, uint32_t a_units,
                                                  uint32_t b_units, bool first_kblock) {
   uint32_t acc = first_kblock ? 0u : 1u;
+  if (!IS_INT && m.triple) {
+    // f32 as three tf32 products: shared memory holds [hi plane | lo plane] of each operand
+    // (x = hi + lo, hi = the tf32 part); hi*hi + lo*hi + hi*lo, the lo*lo term is below f32's
+    // own rounding error. Small terms first.
+    uint32_t au = a_units, bu = b_units;
+    for (int j = 0; j < m.mma_per_box; ++j) {
+      const uint64_t a_hi = (uint64_t(m.hi_a) << 32) | uint64_t((au & 0x3FFFu) | m.lo_a);
+      const uint64_t a_lo = (uint64_t(m.hi_a) << 32) | uint64_t(((au + m.kbox_a) & 0x3FFFu) | m.lo_a);
+      const uint64_t b_hi = (uint64_t(m.hi_b) << 32) | uint64_t((bu & 0x3FFFu) | m.lo_b);
+      const uint64_t b_lo = (uint64_t(m.hi_b) << 32) | uint64_t(((bu + m.kbox_b) & 0x3FFFu) | m.lo_b);
+      tc_mma_tf32<PAIR>(d_tmem, a_lo, b_hi, m.idesc, acc);
+      tc_mma_tf32<PAIR>(d_tmem, a_hi, b_lo, m.idesc, 1u);
+      tc_mma_tf32<PAIR>(d_tmem, a_hi, b_hi, m.idesc, 1u);
+      acc = 1u;
+      au += m.kadv_a;
+      bu += m.kadv_b;
+    }
+    return;
+  }
   for (int kb = 0; kb < m.kboxes; ++kb) {
     uint32_t au = a_units + uint32_t(kb) * m.kbox_a, bu = b_units + uint32_t(kb) * m.kbox_b;
     for (int j = 0; j < m.mma_per_box; ++j) {
@@ -1289,6 +1332,7 @@ struct TypeInfo {
   uint32_t cfmt;  // accumulator format
   CUtensorMapDataType tm_type;
   int out_es;     // output element bytes: 4, or 2 for the f16 / bf16 output triples
+  bool triple = false;  // f32 x f32: split into tf32 hi/lo planes, three products per K slice
 };
 
 bool tc_type_info(uint32_t flags, TypeInfo* ti) {
@@ -1300,6 +1344,7 @@ bool tc_type_info(uint32_t flags, TypeInfo* ti) {
     case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: *ti = {1, true, 1u, 2u, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4}; return true;
     case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32: *ti = {2, false, 0u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4}; return true;
     case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32: *ti = {2, false, 1u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4}; return true;
+    case IREE_UK_FLAG_MMT4D_TYPE_F32F32F32: *ti = {4, false, 2u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, true}; return f32_mode() == IREE_UK_B200_F32_MODE_TF32X3;
     case IREE_UK_FLAG_MMT4D_TYPE_F16F16F16: *ti = {2, false, 0u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2}; return skip;
     case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16BF16: *ti = {2, false, 1u, 1u, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2}; return skip;
     default: return false;
@@ -1462,6 +1507,30 @@ S16U4Layout s16u4_layout(const iree_uk_mmt4d_params_t* p) {
   return l;
 }
 
+// f32 -> tf32 planes, in place: hi is x rounded to sign, exponent and 10 mantissa bits (what
+// kind::tf32 reads), lo = x - hi (exact in f32) goes to the second plane.
+__global__ void __launch_bounds__(256) split_tf32_kernel(uint4* __restrict__ hi, uint4* __restrict__ lo,
+                                                         int64_t vecs) {
+  pdl_launch_dependents();
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs;
+       i += int64_t(gridDim.x) * blockDim.x) {
+    const uint4 x = hi[i];
+    const uint32_t v[4] = {x.x, x.y, x.z, x.w};
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // round to nearest tf32 (truncate instead where rounding up would overflow to infinity)
+      const bool top = (v[j] & 0x7F800000u) == 0x7F000000u;
+      h[j] = (top ? v[j] : v[j] + 0x1000u) & 0xFFFFE000u;
+      const float d = __uint_as_float(v[j]) - __uint_as_float(h[j]);
+      // inf - inf and nan - nan must not poison the sum twice: the hi plane carries them
+      l[j] = ((v[j] & 0x7F800000u) == 0x7F800000u) ? 0u : __float_as_uint(d);
+    }
+    hi[i] = make_uint4(h[0], h[1], h[2], h[3]);
+    lo[i] = make_uint4(l[0], l[1], l[2], l[3]);
+  }
+}
+
 // Launches a main kernel (one-CTA form when cluster == 1, CTA pairs when cluster == 2) with
 // programmatic stream serialisation, so that it may overlap the tail of the pre-pass kernel
 // enqueued just before it (see pdl_wait).
@@ -1610,7 +1679,8 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
   if (!tc_type_info(p->flags, &ti)) return 0;
   if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
   const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
-  return size_t(round_up(p->M * 16 * pitch, 1024) + round_up(p->N * 16 * pitch, 1024));
+  const size_t one = size_t(round_up(p->M * 16 * pitch, 1024) + round_up(p->N * 16 * pitch, 1024));
+  return ti.triple ? 2 * one : one;  // f32: a hi and a lo plane of both operands
 }
 
 namespace {
@@ -1658,77 +1728,67 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   int kboxes = debug_int("IREE_UK_B200_DEBUG_KBOXES", variant == 5 ? 2 : 1) == 2 ? 2 : 1;
   const int mma_k = 32 / ti.es;        // K per tcgen05.mma: 16 (16-bit) or 32 (8-bit)
 
-  if (variant == 6) {
+  if (variant == 5 || variant == 6) {
+    // K-major operands from the re-tiled scratch: the one-CTA kernel (6) on 128 x bn tiles, or
+    // the two-CTA kernel (5) on 256 x bn tiles per CTA pair.
     const size_t need = mmt4d_tc_workspace_size(p);
     if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
     if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+    pair = variant == 5;
+    if (pair) {
+      pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0];
+      if (pair_clusters < 1) return IREE_UK_B200_CUDA_ERROR;
+      bn = pick_bn_pair(p->M, p->N, pair_clusters);
+    }
+    if (ti.triple) kboxes = 1;  // the two boxes of a stage are the hi and lo planes
     const int64_t pitch = round_up(kelems * ti.es, 128);
+    const int64_t a_bytes = round_up(p->M * 16 * pitch, 1024), b_bytes = round_up(p->N * 16 * pitch, 1024);
     char* ws_a = static_cast<char*>(ws);
-    char* ws_b = ws_a + round_up(p->M * 16 * pitch, 1024);
+    char* ws_b = ws_a + a_bytes;
     const int G = p->K0 * ti.es;
     const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, p->M, rhs,
                                  p->rhs_stride0 * ti.es, ws_b, p->N, pitch, p->K, G, stream);
     if (rc) return rc;
-    const uint64_t da[3] = {uint64_t(kelems), uint64_t(p->M * 16), 1};
-    const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), 1};
-    const uint64_t sa[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->M * 16)};
-    const uint64_t sb[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->N * 16)};
+    const int64_t plane_bytes = a_bytes + b_bytes;  // [A hi | B hi][A lo | B lo]
+    if (ti.triple) {
+      const int64_t vecs = plane_bytes / 16;
+      const int blocks = int(std::min<int64_t>((vecs + 255) / 256, int64_t(di->sms) * 16));
+      split_tf32_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<uint4*>(ws_a),
+                                                    reinterpret_cast<uint4*>(ws_a + plane_bytes), vecs);
+      if (cudaGetLastError() != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+    }
+    const int b_rows = pair ? bn / 2 : bn;  // RHS rows one CTA stages
+    const int tile_m = pair ? 2 * BM : BM;
+    const uint64_t planes = ti.triple ? 2 : 1;
+    const uint64_t da[3] = {uint64_t(kelems), uint64_t(p->M * 16), planes};
+    const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), planes};
+    const uint64_t sa[2] = {uint64_t(pitch), ti.triple ? uint64_t(plane_bytes) : uint64_t(pitch) * uint64_t(p->M * 16)};
+    const uint64_t sb[2] = {uint64_t(pitch), ti.triple ? uint64_t(plane_bytes) : uint64_t(pitch) * uint64_t(p->N * 16)};
     const uint32_t ba[3] = {uint32_t(kblk_elems), BM, 1};
-    const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(bn), 1};
+    const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(b_rows), 1};
     if (!encode_map(&P.map_a, ti.tm_type, ws_a, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !encode_map(&P.map_b, ti.tm_type, ws_b, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
       return IREE_UK_B200_CUDA_ERROR;
-    P.sa = {kboxes, BM * 128, {kboxes * kblk_elems, 0, 0}, {0, BM, 0}, {kblk_elems, 0, 0}};
-    P.sb = {kboxes, bn * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}};
+    if (ti.triple) {
+      P.sa = {2, BM * 128, {kblk_elems, 0, 0}, {0, tile_m, 0}, {0, 0, 1}, {0, pair ? BM : 0, 0}};
+      P.sb = {2, b_rows * 128, {kblk_elems, 0, 0}, {0, bn, 0}, {0, 0, 1}, {0, pair ? b_rows : 0, 0}};
+      P.triple = 1;
+    } else {
+      P.sa = {kboxes, BM * 128, {kboxes * kblk_elems, 0, 0}, {0, tile_m, 0}, {kblk_elems, 0, 0}, {0, pair ? BM : 0, 0}};
+      P.sb = {kboxes, b_rows * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}, {0, pair ? b_rows : 0, 0}};
+    }
+    const int boxes = ti.triple ? 2 : kboxes;
     P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
     P.desc_lbo_a = P.desc_lbo_b = 1;
     P.kadv_a = P.kadv_b = 2;  // 32 bytes of K per MMA inside the 128-byte swizzle row
     P.kbox_units_a = uint32_t(BM * 128) >> 4;
-    P.kbox_units_b = uint32_t(bn * 128) >> 4;
-    P.idesc = make_idesc(ti, bn, false);
+    P.kbox_units_b = uint32_t(b_rows * 128) >> 4;
+    P.idesc = make_idesc(ti, bn, false, tile_m);
     P.kboxes = kboxes;
     P.mma_per_box = 4;
-    P.stage_bytes_a = kboxes * BM * 128;
-    P.stage_bytes_b = kboxes * bn * 128;
+    P.stage_bytes_a = boxes * BM * 128;
+    P.stage_bytes_b = boxes * b_rows * 128;
     P.num_kb = int((kelems + kboxes * kblk_elems - 1) / (kboxes * kblk_elems));
-  } else if (variant == 5) {
-    // Two-CTA kernel on the re-tiled K-major scratch: 256 x bn tile per CTA pair.
-    const size_t need = mmt4d_tc_workspace_size(p);
-    if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
-    if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
-    pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0];
-    if (pair_clusters < 1) return IREE_UK_B200_CUDA_ERROR;
-    bn = pick_bn_pair(p->M, p->N, pair_clusters);
-    const int64_t pitch = round_up(kelems * ti.es, 128);
-    char* ws_a = static_cast<char*>(ws);
-    char* ws_b = ws_a + round_up(p->M * 16 * pitch, 1024);
-    const int G = p->K0 * ti.es;
-    const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, p->M, rhs,
-                                 p->rhs_stride0 * ti.es, ws_b, p->N, pitch, p->K, G, stream);
-    if (rc) return rc;
-    const uint64_t da[3] = {uint64_t(kelems), uint64_t(p->M * 16), 1};
-    const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), 1};
-    const uint64_t sa[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->M * 16)};
-    const uint64_t sb[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->N * 16)};
-    const uint32_t ba[3] = {uint32_t(kblk_elems), BM, 1};
-    const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(bn / 2), 1};
-    if (!encode_map(&P.map_a, ti.tm_type, ws_a, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !encode_map(&P.map_b, ti.tm_type, ws_b, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
-      return IREE_UK_B200_CUDA_ERROR;
-    P.sa = {kboxes, BM * 128, {kboxes * kblk_elems, 0, 0}, {0, 2 * BM, 0}, {kblk_elems, 0, 0}, {0, BM, 0}};
-    P.sb = {kboxes, (bn / 2) * 128, {kboxes * kblk_elems, 0, 0}, {0, bn, 0}, {kblk_elems, 0, 0}, {0, bn / 2, 0}};
-    P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
-    P.desc_lbo_a = P.desc_lbo_b = 1;
-    P.kadv_a = P.kadv_b = 2;
-    P.kbox_units_a = uint32_t(BM * 128) >> 4;
-    P.kbox_units_b = uint32_t((bn / 2) * 128) >> 4;
-    P.idesc = make_idesc(ti, bn, false, 2 * BM);
-    P.kboxes = kboxes;
-    P.mma_per_box = 4;
-    P.stage_bytes_a = kboxes * BM * 128;
-    P.stage_bytes_b = kboxes * (bn / 2) * 128;
-    P.num_kb = int((kelems + kboxes * kblk_elems - 1) / (kboxes * kblk_elems));
-    pair = true;
   } else {
     // MN-major, straight from a K0 = 1 16-bit operand (experimental variants 1..4).
     if (ti.es != 2 || p->K0 != 1 || variant < 1 || variant > 4) return IREE_UK_B200_UNSUPPORTED;

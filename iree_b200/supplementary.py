@@ -222,9 +222,13 @@ def run(peaks, only=None, custom=None):
         tname, cm, cn, ck = custom
         flags, k0, dt = {"bf16": (abi.MMT4D_BF16BF16F32, 2, torch.bfloat16),
                          "f16": (abi.MMT4D_F16F16F32, 1, torch.float16),
+                         "f32": (abi.MMT4D_F32F32F32, 1, torch.float32),
                          "s8": (abi.MMT4D_S8S8S32, 2, None)}[tname]
+        prev = uk.set_f32_mode(uk.F32_MODE_TF32X3) if tname == "f32" else None
         k, r = _mmt4d_case("mmt4d_%s_custom_%dx%dx%d" % (tname, cm, cn, ck), flags, cm, cn, ck,
                            16, 16, k0, peaks, None, dt)
+        if prev is not None:
+            uk.set_f32_mode(prev)
         res[k] = r
     if want("mmt4d_f16f16f32_acc_4096x4096x4096"):
         k, r = _mmt4d_case("mmt4d_f16f16f32_acc_4096x4096x4096",

@@ -75,6 +75,16 @@ def mmt4d_peers(params, peer_out_ptrs, workspace, stream=None):
                                            _stream_handle(stream)), "mmt4d_peers")
 
 
+F32_MODE_CUDA_CORES, F32_MODE_TF32X3 = 0, 1
+
+
+def set_f32_mode(mode):
+    """Process-wide: how f32f32f32 with 16x16 tiles is computed when scratch is supplied —
+    ``F32_MODE_CUDA_CORES`` (default, the reference's accumulation order) or ``F32_MODE_TF32X3``
+    (tensor cores, three tf32 products per term). Returns the previous mode."""
+    return int(lib.iree_uk_b200_set_f32_mode(mode))
+
+
 def mmt4d_sharded(device_ids, per_gpu_params, workspaces, streams, replicate_output=False):
     """The N-sharded mmt4d from one process that owns several GPUs: enqueues
     ``per_gpu_params[g]`` on ``device_ids[g]`` / ``streams[g]`` with ``workspaces[g]`` (torch

@@ -65,3 +65,21 @@ def oracle_unpack(case):
 def check_device_status():
     st, detail = uk.device_status()
     assert st == 0, "device-side bounded wait ran out: status %d detail 0x%x" % (st, detail)
+
+
+import contextlib
+
+
+@contextlib.contextmanager
+def f32_tensor_cores(type_flag):
+    """Switches f32f32f32 to the tensor-core (three tf32 products) mode for the duration, when
+    ``type_flag`` is that triple; other triples are unaffected."""
+    from iree_b200 import abi
+    if (type_flag & 0xFF) != abi.MMT4D_F32F32F32:
+        yield
+        return
+    prev = uk.set_f32_mode(uk.F32_MODE_TF32X3)
+    try:
+        yield
+    finally:
+        uk.set_f32_mode(prev)

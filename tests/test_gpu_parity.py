@@ -54,7 +54,8 @@ def test_mmt4d_16bit_output_triples(tile):
 
 @pytest.mark.parametrize("tile", [(abi.MMT4D_S8S8S32, 16, 16, 2), (abi.MMT4D_F16F16F32, 16, 16, 1),
                                   (abi.MMT4D_BF16BF16F32, 16, 16, 2),
-                                  (abi.MMT4D_S8S8S32, 16, 16, 8), (abi.MMT4D_BF16BF16F32, 16, 16, 1)],
+                                  (abi.MMT4D_S8S8S32, 16, 16, 8), (abi.MMT4D_BF16BF16F32, 16, 16, 1),
+                                  (abi.MMT4D_F32F32F32, 16, 16, 1), (abi.MMT4D_F32F32F32, 16, 16, 4)],
                          ids=lambda t: "t%x_%dx%dx%d" % t)
 @pytest.mark.parametrize("shape", [(1, 1, 1), (8, 16, 64), (9, 17, 65), (3, 5, 7), (16, 32, 130),
                                    (24, 40, 31), (1, 1, 1000)], ids=lambda s: "%dx%dx%d" % s)
@@ -65,10 +66,15 @@ def test_mmt4d_tensor_core_path_exact(tile, shape, accumulate):
     t, M0, N0, K0 = tile
     M, N, K = shape
     case = cases.Mmt4dCase(t, M0, N0, K0, M, N, K, accumulate, seed=7, mode="exact", loose=False)
-    got, path = G.run_mmt4d_case(case)
+    with G.f32_tensor_cores(t):
+        got, path = G.run_mmt4d_case(case)
     assert path == abi.PATH_TCGEN05_RETILE
     want = G.oracle_mmt4d(case)
     assert np.array_equal(got, want), case.label()
+    if t == abi.MMT4D_F32F32F32:  # default mode: the CUDA-core kernel, same exact result
+        got, path = G.run_mmt4d_case(case)
+        assert path == abi.PATH_GENERIC
+        assert np.array_equal(got, want), case.label()
 
 
 def test_mmt4d_tensor_core_loose_out_stride():
@@ -118,12 +124,18 @@ def test_mmt4d_16bit_output_on_tensor_cores(t, K0, is_bf16, shape, accumulate):
     (abi.MMT4D_F16F16F32, 16, 16, 1, 16, 16, 512, 1, 1e-3),
     (abi.MMT4D_BF16BF16F32, 16, 16, 2, 24, 32, 256, 0, 1e-3),
     (abi.MMT4D_F16F16F32, 4, 6, 5, 5, 7, 13, 1, 1e-3),
+    # f32 on the tensor cores (opt-in mode) as three tf32 products: error about 7e-9 x K
+    (abi.MMT4D_F32F32F32, 16, 16, 1, 24, 40, 700, 0, 1e-5),
+    (abi.MMT4D_F32F32F32, 16, 16, 2, 160, 64, 129, 1, 1e-5),
 ])
 def test_mmt4d_float_normal_values(t, M0, N0, K0, M, N, K, acc, tol):
     """N(0,1) operands: relative Frobenius error <= 1e-3 against the oracle's f32
     accumulation (the tolerance the headline configurations state)."""
     case = cases.Mmt4dCase(t, M0, N0, K0, M, N, K, acc, seed=11, mode="normal", loose=False)
-    got, _ = G.run_mmt4d_case(case)
+    with G.f32_tensor_cores(t):
+        got, path = G.run_mmt4d_case(case)
+    if M0 == 16:
+        assert path == abi.PATH_TCGEN05_RETILE
     want = G.oracle_mmt4d(case)
     err = cases.rel_frobenius(got.view(np.float32), want.view(np.float32))
     assert err <= tol, err
