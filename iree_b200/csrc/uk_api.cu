@@ -529,7 +529,8 @@ int iree_uk_b200_device_status(void* cu_stream, uint32_t* detail) {
 }
 
 // Internal, not declared in the public header: runs the tensor-core kernel with an explicit
-// operand-staging variant. Used to validate experimental staging layouts on hardware.
+// kernel form (0 = automatic, 5 = two-CTA, 6 = one-CTA, 3 = scratch-free MN-major staging). Used
+// by tests and probes to pin the form that runs.
 IREE_UK_B200_EXPORT int iree_uk_b200_debug_mmt4d_variant(const iree_uk_mmt4d_params_t* params,
                                                          void* workspace, size_t workspace_bytes,
                                                          int variant, void* cu_stream) {

@@ -25,39 +25,39 @@ struct GenericArgs {
 
 template <uint32_t TYPE> struct Traits;
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_F32F32F32> {
-  using Acc = float; static constexpr int LB = 32, RB = 32;
+  using Acc = float;
   static __device__ float lhs(const char* p, int64_t e) { return reinterpret_cast<const float*>(p)[e]; }
   static __device__ float rhs(const char* p, int64_t e) { return reinterpret_cast<const float*>(p)[e]; }
 };
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_F16F16F32> {
-  using Acc = float; static constexpr int LB = 16, RB = 16;
+  using Acc = float;
   static __device__ float lhs(const char* p, int64_t e) { return __half2float(reinterpret_cast<const __half*>(p)[e]); }
   static __device__ float rhs(const char* p, int64_t e) { return __half2float(reinterpret_cast<const __half*>(p)[e]); }
 };
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32> {
-  using Acc = float; static constexpr int LB = 16, RB = 16;
+  using Acc = float;
   static __device__ float lhs(const char* p, int64_t e) { return __uint_as_float(uint32_t(reinterpret_cast<const uint16_t*>(p)[e]) << 16); }
   static __device__ float rhs(const char* p, int64_t e) { return lhs(p, e); }
 };
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S8S8S32> {
-  using Acc = uint32_t; static constexpr int LB = 8, RB = 8;
+  using Acc = uint32_t;
   static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
   static __device__ int32_t rhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
 };
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S16S16S32> {
-  using Acc = uint32_t; static constexpr int LB = 16, RB = 16;
+  using Acc = uint32_t;
   static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
   static __device__ int32_t rhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
 };
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S16S8S32> {
-  using Acc = uint32_t; static constexpr int LB = 16, RB = 8;
+  using Acc = uint32_t;
   static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
   static __device__ int32_t rhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
 };
 // 4-bit right-hand sides: element e is in byte e/2, low nibble when e is even
 // (ukernel/mmt4d_tile_generic.c:35-44 signed, :130-136 unsigned).
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S16U4S32> {
-  using Acc = uint32_t; static constexpr int LB = 16, RB = 4;
+  using Acc = uint32_t;
   static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int16_t*>(p)[e]; }
   static __device__ int32_t rhs(const char* p, int64_t e) {
     const uint32_t b = reinterpret_cast<const uint8_t*>(p)[e >> 1];
@@ -65,7 +65,7 @@ template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S16U4S32> {
   }
 };
 template <> struct Traits<IREE_UK_FLAG_MMT4D_TYPE_S8S4S32> {
-  using Acc = uint32_t; static constexpr int LB = 8, RB = 4;
+  using Acc = uint32_t;
   static __device__ int32_t lhs(const char* p, int64_t e) { return reinterpret_cast<const int8_t*>(p)[e]; }
   static __device__ int32_t rhs(const char* p, int64_t e) {
     const uint32_t b = reinterpret_cast<const uint8_t*>(p)[e >> 1];

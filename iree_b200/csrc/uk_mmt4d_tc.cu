@@ -328,10 +328,6 @@ __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr_units, uint32_t lbo, uint32_t hi) {
-  return (uint64_t(hi) << 32) | uint64_t((addr_units & 0x3FFFu) | (lbo << 16));
-}
-
 __device__ __forceinline__ void tile_coords(const TcParams& P, int tile, int* mt, int* nt) {
   const int per_group = P.group_m * P.n_tiles;
   const int g = tile / per_group, r = tile - g * per_group;
@@ -1721,7 +1717,8 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   char* rhs = const_cast<char*>(static_cast<const char*>(p->rhs_buffer)) + p->rhs_offset * ti.es;
   const int kblk_elems = 128 / ti.es;  // one 128-byte swizzle row of K per TMA box
   // Variant 0 = automatic: the two-CTA kernel when the problem gives every CTA pair work,
-  // the one-CTA kernel otherwise. 5 / 6 force the two-CTA / one-CTA kernel.
+  // the one-CTA kernel otherwise. 5 / 6 force the two-CTA / one-CTA kernel; 3 is the
+  // scratch-free MN-major staging of 16-bit K0 = 1 operands.
   if (variant == 0) variant = pair_kernel_pays(p) ? 5 : 6;
   // K boxes per stage: two for the two-CTA kernel (64 KB stages, half the barrier round trips
   // per MMA), one for the one-CTA kernel (its stage is already 48 KB).
@@ -1790,48 +1787,29 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     P.stage_bytes_b = boxes * b_rows * 128;
     P.num_kb = int((kelems + kboxes * kblk_elems - 1) / (kboxes * kblk_elems));
   } else {
-    // MN-major, straight from a K0 = 1 16-bit operand (experimental variants 1..4).
-    if (ti.es != 2 || p->K0 != 1 || variant < 1 || variant > 4) return IREE_UK_B200_UNSUPPORTED;
-    const bool sw128 = variant <= 2, swapped = (variant % 2) == 0;
+    // MN-major, straight from a K0 = 1 16-bit operand [tile][K1][16]: for a fixed k the 16 rows
+    // of a tile are 32 contiguous bytes, so TMA stages boxes of 16 elements x kblk k-steps x
+    // (rows / 16) tiles with the 32-byte swizzle. In shared memory 8 k-steps of one tile are a
+    // 256-byte atom (stride byte offset); the next tile is kblk * 32 bytes on (leading byte
+    // offset). No scratch is needed; the main loop runs at about half the K-major rate.
+    if (ti.es != 2 || p->K0 != 1 || variant != kTcVariantDirect) return IREE_UK_B200_UNSUPPORTED;
     const int kblk = 64;
-    if (sw128) {
-      const uint64_t da[3] = {16, uint64_t(p->M), uint64_t(p->K)};
-      const uint64_t db[3] = {16, uint64_t(p->N), uint64_t(p->K)};
-      const uint64_t sa[2] = {uint64_t(p->lhs_stride0 * 2), 32};
-      const uint64_t sb[2] = {uint64_t(p->rhs_stride0 * 2), 32};
-      const uint32_t box[3] = {16, 4, uint32_t(kblk)};
-      if (!encode_map(&P.map_a, ti.tm_type, lhs, da, sa, box, CU_TENSOR_MAP_SWIZZLE_128B) ||
-          !encode_map(&P.map_b, ti.tm_type, rhs, db, sb, box, CU_TENSOR_MAP_SWIZZLE_128B))
-        return IREE_UK_B200_CUDA_ERROR;
-      const int box_bytes = kblk * 128;
-      P.sa = {BM / 64, box_bytes, {0, 0, kblk}, {0, BM / 16, 0}, {0, 4, 0}};
-      P.sb = {bn / 64, box_bytes, {0, 0, kblk}, {0, bn / 16, 0}, {0, 4, 0}};
-      const uint32_t mn_off = uint32_t(box_bytes), k_off = 1024;
-      P.desc_hi_a = P.desc_hi_b = desc_hi(swapped ? mn_off : k_off, 2);
-      P.desc_lbo_a = P.desc_lbo_b = (swapped ? k_off : mn_off) >> 4;
-      P.kadv_a = P.kadv_b = (16 * 128) >> 4;
-      P.stage_bytes_a = BM * kblk * 2;
-      P.stage_bytes_b = bn * kblk * 2;
-      if (bn % 64) return IREE_UK_B200_UNSUPPORTED;
-    } else {
-      const uint64_t da[3] = {16, uint64_t(p->K), uint64_t(p->M)};
-      const uint64_t db[3] = {16, uint64_t(p->K), uint64_t(p->N)};
-      const uint64_t sa[2] = {32, uint64_t(p->lhs_stride0 * 2)};
-      const uint64_t sb[2] = {32, uint64_t(p->rhs_stride0 * 2)};
-      const uint32_t ba[3] = {16, uint32_t(kblk), BM / 16};
-      const uint32_t bb[3] = {16, uint32_t(kblk), uint32_t(bn / 16)};
-      if (!encode_map(&P.map_a, ti.tm_type, lhs, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_32B) ||
-          !encode_map(&P.map_b, ti.tm_type, rhs, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_32B))
-        return IREE_UK_B200_CUDA_ERROR;
-      P.sa = {1, BM * kblk * 2, {0, kblk, 0}, {0, 0, BM / 16}, {0, 0, 0}};
-      P.sb = {1, bn * kblk * 2, {0, kblk, 0}, {0, 0, bn / 16}, {0, 0, 0}};
-      const uint32_t mn_off = uint32_t(kblk * 32), k_off = 256;
-      P.desc_hi_a = P.desc_hi_b = desc_hi(swapped ? mn_off : k_off, 6);
-      P.desc_lbo_a = P.desc_lbo_b = (swapped ? k_off : mn_off) >> 4;
-      P.kadv_a = P.kadv_b = (16 * 32) >> 4;
-      P.stage_bytes_a = BM * kblk * 2;
-      P.stage_bytes_b = bn * kblk * 2;
-    }
+    const uint64_t da[3] = {16, uint64_t(p->K), uint64_t(p->M)};
+    const uint64_t db[3] = {16, uint64_t(p->K), uint64_t(p->N)};
+    const uint64_t sa[2] = {32, uint64_t(p->lhs_stride0 * 2)};
+    const uint64_t sb[2] = {32, uint64_t(p->rhs_stride0 * 2)};
+    const uint32_t ba[3] = {16, uint32_t(kblk), BM / 16};
+    const uint32_t bb[3] = {16, uint32_t(kblk), uint32_t(bn / 16)};
+    if (!encode_map(&P.map_a, ti.tm_type, lhs, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_32B) ||
+        !encode_map(&P.map_b, ti.tm_type, rhs, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_32B))
+      return IREE_UK_B200_CUDA_ERROR;
+    P.sa = {1, BM * kblk * 2, {0, kblk, 0}, {0, 0, BM / 16}, {0, 0, 0}};
+    P.sb = {1, bn * kblk * 2, {0, kblk, 0}, {0, 0, bn / 16}, {0, 0, 0}};
+    P.desc_hi_a = P.desc_hi_b = desc_hi(256, 6);
+    P.desc_lbo_a = P.desc_lbo_b = uint32_t(kblk * 32) >> 4;
+    P.kadv_a = P.kadv_b = (16 * 32) >> 4;
+    P.stage_bytes_a = BM * kblk * 2;
+    P.stage_bytes_b = bn * kblk * 2;
     P.idesc = make_idesc(ti, bn, true);
     P.kboxes = 1;
     P.mma_per_box = kblk / mma_k;
