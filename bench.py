@@ -473,6 +473,24 @@ def main():
         assert int(flag.item()) == 1, "fused replication and all-gather route disagree"
         barrier()
         peers.close()
+        # third route: one multimem.st per tile through an NVLink multicast mapping
+        mc_ms, mc_note = None, None
+        try:
+            mc = sharding.MulticastOutput(M1 * N1 * tile, torch.float32)
+            if mc.multicast_ptr:
+                full.out_buffer = mc.tensor.data_ptr()
+                pm, _ = uk.shard_params(full, rank, world, rhs_is_local=True, out_is_local=False)
+                mc_ms = timed(lambda: uk.mmt4d_multicast(pm, mc.multicast_ptr, ws, stream))
+                ok = torch.tensor([1 if torch.equal(mc.tensor, gathered_full[0]) else 0], device="cuda")
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                assert int(ok.item()) == 1, "multicast route and all-gather route disagree"
+            else:
+                mc_note = "no multicast support reported"
+        except AssertionError:
+            raise
+        except Exception as e:  # symmetric memory unavailable: the other two routes stand
+            mc_note = repr(e)[:200]
+        barrier()
         nvlink_bytes = (world - 1) * out.numel() * 4  # leaves each GPU per step
         replicated = {
             "gather_route_ms": gather_ms, "fused_peer_store_ms": fused_ms,
@@ -480,6 +498,8 @@ def main():
             "gather_route_tflops": total_flops / (gather_ms * 1e-3) / 1e12,
             "nvlink_bytes_out_per_gpu": nvlink_bytes,
             "fused_nvlink_gbs_per_gpu": nvlink_bytes / fused_ms / 1e6,
+            "fused_multicast_ms": mc_ms, "fused_multicast_note": mc_note,
+            "fused_multicast_tflops": (total_flops / (mc_ms * 1e-3) / 1e12) if mc_ms else None,
             "results_identical_on_all_ranks": True, "steps": rep_steps,
         }
         del gathered_full, full_out

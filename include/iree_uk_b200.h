@@ -268,6 +268,20 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws_peers(const iree_uk_mmt4d_params_t
                                                     int num_peers, void* workspace,
                                                     size_t workspace_bytes, void* cu_stream);
 
+/* As iree_uk_b200_mmt4d_ws_peers, but through an NVLink multicast mapping (NVSwitch systems):
+ * `multicast_out_buffer` is the address, in the multicast mapping bound to the same-shaped
+ * output buffers of all GPUs of a group (this GPU's included), that stands for
+ * params->out_buffer. Every output tile is stored once with multimem.st and replicated to all
+ * bound buffers by the switch, so the result leaves this GPU once instead of once per peer.
+ * The mapping is created by the caller (cuMulticastCreate / cuMulticastBindMem, or a library
+ * that wraps them); params->out_buffer stays this GPU's ordinary address of its own buffer
+ * (ACCUMULATE reads the old values through it). Same completion and synchronisation rules as
+ * iree_uk_b200_mmt4d_ws_peers. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws_multicast(const iree_uk_mmt4d_params_t* params,
+                                                        const void* multicast_out_buffer,
+                                                        void* workspace, size_t workspace_bytes,
+                                                        void* cu_stream);
+
 /* The N-sharded mmt4d driven from ONE process that owns several GPUs. For g in [0, n_gpus):
  * makes device_ids[g] current and enqueues per_gpu[g] (as produced by
  * iree_uk_b200_mmt4d_shard_params, with buffers on that device) on streams[g] with

@@ -194,6 +194,22 @@ int iree_uk_b200_mmt4d_ws_peers(const iree_uk_mmt4d_params_t* params,
                          static_cast<cudaStream_t>(cu_stream), peer_out_buffers, num_peers);
 }
 
+int iree_uk_b200_mmt4d_ws_multicast(const iree_uk_mmt4d_params_t* params,
+                                    const void* multicast_out_buffer, void* workspace,
+                                    size_t workspace_bytes, void* cu_stream) {
+  if (!multicast_out_buffer) return IREE_UK_B200_INVALID_ARGUMENT;
+  Mmt4dPath path;
+  const int rc = select_mmt4d(params, true, &path);
+  if (rc) return rc;
+  if (path != Mmt4dPath::TcRetile ||
+      (params->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
+    return IREE_UK_B200_UNSUPPORTED;
+  if (!workspace || workspace_bytes < mmt4d_tc_workspace_size(params))
+    return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  return launch_mmt4d_tc(params, workspace, workspace_bytes, kTcVariantDefault,
+                         static_cast<cudaStream_t>(cu_stream), nullptr, 0, multicast_out_buffer);
+}
+
 int iree_uk_b200_mmt4d_sharded(int n_gpus, const int* device_ids,
                                const iree_uk_mmt4d_params_t* per_gpu, void* const* workspaces,
                                const size_t* workspace_bytes, void* const* cu_streams,

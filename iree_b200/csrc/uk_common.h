@@ -54,9 +54,11 @@ bool mmt4d_tc_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 // `peer_out_buffers`: optional device pointers (usually on other GPUs) that stand for
 // p->out_buffer in further copies of the output; every tile is stored to all of them too.
+// `multicast_out`: alternatively, the NVLink multicast mapping that stands for p->out_buffer
+// on every GPU of a group; tiles are then stored once, through multimem.st.
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream, const void* const* peer_out_buffers = nullptr,
-                    int num_peers = 0);
+                    int num_peers = 0, const void* multicast_out = nullptr);
 // Row-major matmul on the tensor-core kernels (lhs [M][K], rhs [K][N], out [M][N] 32-bit);
 // pitches in bytes, out_stride0 in elements.
 size_t matmul_workspace_size(uint32_t flags, int64_t M, int64_t N, int64_t K);

@@ -83,6 +83,8 @@ struct TcParams {
   int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
   int32_t triple;        // f32 operands as hi/lo tf32 planes, three MMAs per K slice
   int32_t out16;         // 0: 32-bit output; 1: f16 output, 2: bf16 output (rounded once, RNE)
+  int32_t use_multicast; // output tiles are stored through an NVLink multicast mapping
+  int64_t mc_delta;      // byte distance from `out` to that mapping
   int32_t num_peers;     // copies of every output tile also stored to this many peer buffers
   int64_t peer_delta[IREE_UK_B200_MAX_PEERS];  // byte distance from `out` to each peer's buffer
   int32_t out_row_major; // fused matmul: the output is a row-major rows x cols matrix
@@ -471,6 +473,63 @@ __device__ __forceinline__ void epilogue_rows_peers(const TcParams& P, uint32_t 
   __syncwarp();
 }
 
+// Epilogue through an NVLink multicast mapping: one multimem.st reaches the output buffer of
+// every GPU bound to the mapping (this one included), replicated by the switch, so the result
+// leaves this GPU once instead of once per peer. The warp's 32 rows x 16 columns are staged in
+// shared memory and read back so that each store instruction covers 512 contiguous bytes of
+// an output tile. All 32 lanes must call this.
+__device__ __forceinline__ void epilogue_rows_multicast(const TcParams& P, uint32_t taddr0,
+                                                        int64_t row, int64_t n1_0, int chunks,
+                                                        uint32_t stage, int lane) {
+  const int64_t m1 = row >> 4;
+  const int m0 = int(row & 15);
+  const int64_t m1_first = (row - lane) >> 4;
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[16];
+    tmem_ld16(taddr0 + uint32_t(c * 16), r);
+    tmem_ld_wait();
+    const int64_t n1 = n1_0 + c;
+    if (P.accumulate && m1 < P.M1 && n1 < P.N1) {
+      const uint4* d4 = reinterpret_cast<const uint4*>(
+          P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        const uint4 old = d4[v];
+        const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          r[4 * v + j] = P.out_is_int
+                             ? r[4 * v + j] + o[j]
+                             : __float_as_uint(__uint_as_float(r[4 * v + j]) + __uint_as_float(o[j]));
+      }
+    }
+    __syncwarp();  // the previous chunk has been read out of the staging buffer
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                   :: "r"(stage + uint32_t(lane) * 64u + uint32_t(v) * 16u), "r"(r[4 * v + 0]),
+                      "r"(r[4 * v + 1]), "r"(r[4 * v + 2]), "r"(r[4 * v + 3]) : "memory");
+    __syncwarp();
+    if (n1 < P.N1 && !(P.debug_flags & 1u)) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {  // 4 x 512 bytes = the two 1 KB tiles
+        const int t = i >> 1;
+        if (m1_first + t < P.M1) {
+          float x, y, z, w;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(x), "=f"(y), "=f"(z), "=f"(w)
+                       : "r"(stage + uint32_t(i) * 512u + uint32_t(lane) * 16u) : "memory");
+          char* dst = P.out + P.mc_delta + ((m1_first + t) * P.out_stride0 + n1 * 256) * 4 +
+                      (i & 1) * 512 + lane * 16;
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                       :: "l"(dst), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+        }
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // 16-bit output (f16f16f16 / bf16bf16bf16 with one final rounding): lane owns row (m1, m0) of
 // 16x16 tiles of 512 bytes; its 16 values of a tile are one 32-byte row.
 __device__ __forceinline__ uint32_t pack_out16(float lo, float hi, int kind) {
@@ -524,6 +583,10 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
                                               int64_t n1_0, int chunks, uint32_t epi_stage,
                                               int lane) {
   if (P.debug_flags & 2u) return;
+  if (P.use_multicast) {
+    epilogue_rows_multicast(P, taddr0, row, n1_0, chunks, epi_stage, lane);
+    return;
+  }
   if (P.num_peers) {
     epilogue_rows_peers(P, taddr0, row, n1_0, chunks, epi_stage, lane);
     return;
@@ -1689,17 +1752,19 @@ bool pair_kernel_pays(const iree_uk_mmt4d_params_t* p) {
 }  // namespace
 
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
-                    cudaStream_t stream, const void* const* peer_out_buffers, int num_peers) {
+                    cudaStream_t stream, const void* const* peer_out_buffers, int num_peers,
+                    const void* multicast_out) {
+  if (multicast_out && num_peers) return IREE_UK_B200_INVALID_ARGUMENT;
   if (num_peers < 0 || num_peers > IREE_UK_B200_MAX_PEERS || (num_peers && !peer_out_buffers))
     return IREE_UK_B200_INVALID_ARGUMENT;
   // Peer copies exist for the plain tiled epilogue only.
-  if (num_peers && (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
+  if ((num_peers || multicast_out) && (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
     return IREE_UK_B200_UNSUPPORTED;
   if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
     return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || !mmt4d_tc_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
-  if (num_peers && ti.out_es != 4) return IREE_UK_B200_UNSUPPORTED;  // peer copies: 32-bit tiles only
+  if ((num_peers || multicast_out) && ti.out_es != 4) return IREE_UK_B200_UNSUPPORTED;  // 32-bit tiles only
   uint32_t* status = device_status_word();
   const DeviceInfo* di = device_info();
   if (!status || !di) return IREE_UK_B200_CUDA_ERROR;
@@ -1829,6 +1894,12 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   P.out_is_int = ti.is_int ? 1 : 0;
   P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * ti.out_es) % 32 == 0) ? 1 : 0;
   P.out16 = ti.out_es == 2 ? (ti.fmt == 0u ? 1 : 2) : 0;
+  if (multicast_out) {
+    P.use_multicast = 1;
+    P.mc_delta = int64_t(reinterpret_cast<intptr_t>(multicast_out) -
+                         reinterpret_cast<intptr_t>(p->out_buffer));
+    if (P.mc_delta % 16) return IREE_UK_B200_INVALID_ARGUMENT;
+  }
   P.num_peers = num_peers;
   for (int g = 0; g < num_peers; ++g) {
     const char* peer = static_cast<const char*>(peer_out_buffers[g]);
@@ -1844,7 +1915,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   const int smem_budget = 200 * 1024;
   P.num_stages = std::max(2, std::min(kMaxStages, smem_budget / stage_bytes));
-  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 + (num_peers ? 4 * kEpiStageBytes : 0);
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 + ((num_peers || multicast_out) ? 4 * kEpiStageBytes : 0);
 
   if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
   cudaError_t e;

@@ -67,3 +67,26 @@ class PeerOutputs:
         for ptr in self.ptrs:
             self._close(ptr)
         self.ptrs = []
+
+
+class MulticastOutput:
+    """A replicated output buffer reachable through an NVLink multicast mapping.
+
+    A collective over ``group``: every rank gets ``tensor`` (its own full-size buffer, 1-D, of
+    ``numel`` elements of ``dtype``) and ``multicast_ptr``, the address of the mapping that
+    writes into all ranks' buffers at once (for ``ukernel.mmt4d_multicast``). The buffers and
+    the mapping come from ``torch.distributed._symmetric_memory``; ``multicast_ptr`` is 0 where
+    the system has no multicast support (no NVSwitch), and callers then use ``PeerOutputs``."""
+
+    def __init__(self, numel, dtype, group=None):
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        base = int(self.handle.multicast_ptr)
+        offset = int(getattr(self.handle, "offset", 0) or 0)
+        self.multicast_ptr = base + offset if base else 0  # stands for tensor.data_ptr()
+        self.peer_ptrs = [int(p) for r, p in enumerate(self.handle.buffer_ptrs)
+                          if r != dist.get_rank(group)]

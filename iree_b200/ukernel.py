@@ -100,6 +100,16 @@ def mmt4d_sharded(device_ids, per_gpu_params, workspaces, streams, replicate_out
                                           1 if replicate_output else 0), "mmt4d_sharded")
 
 
+def mmt4d_multicast(params, multicast_out_ptr, workspace, stream=None):
+    """mmt4d whose output tiles are stored once through an NVLink multicast mapping and
+    replicated by the switch into every GPU's buffer; ``multicast_out_ptr`` is the address in
+    that mapping that stands for ``params.out_buffer``."""
+    _check(lib.iree_uk_b200_mmt4d_ws_multicast(C.addressof(params), multicast_out_ptr,
+                                               workspace.data_ptr(),
+                                               workspace.numel() * workspace.element_size(),
+                                               _stream_handle(stream)), "mmt4d_multicast")
+
+
 def peer_export(device_ptr):
     """Bytes another process on this machine can pass to ``peer_open`` to address the device
     buffer at ``device_ptr`` (an int, or a tensor)."""
