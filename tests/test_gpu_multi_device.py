@@ -72,3 +72,51 @@ def test_sharded_with_replication_every_buffer_holds_everything(world, t, K0):
             assert np.array_equal(o, want)
         else:
             assert cases.rel_frobenius(o.view(np.float32), want.view(np.float32)) <= 1e-3
+
+
+def _multicast_worker(rank, world, port):
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        from iree_b200 import sharding, ukernel as uk
+        case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 20, 24, 40, 0, seed=21, mode="normal",
+                               loose=False)
+        want = G.oracle_mmt4d(case)
+        mc = sharding.MulticastOutput(case.out_init.nbytes, torch.uint8)
+        assert mc.multicast_ptr, "no multicast mapping on this system"
+        mc.tensor.copy_(torch.from_numpy(case.out_init.view(np.uint8)))
+        lhs, rhs = G.to_device(case.lhs), G.to_device(case.rhs)
+        torch.cuda.synchronize()
+        dist.barrier()
+        full = case.params(lhs.data_ptr(), rhs.data_ptr(), mc.tensor.data_ptr())
+        p, _ = uk.shard_params(full, rank, world, rhs_is_local=False, out_is_local=False)
+        ws = torch.empty(max(uk.mmt4d_workspace_size(p), 256), dtype=torch.uint8, device="cuda")
+        uk.mmt4d_multicast(p, mc.multicast_ptr, ws)
+        torch.cuda.synchronize()
+        dist.barrier()   # every rank's tiles have landed in every buffer
+        assert uk.device_status() == (0, 0)
+        assert np.array_equal(mc.tensor.cpu().numpy(), want.view(np.uint8))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_multicast_replication_two_processes():
+    """Two ranks on two GPUs: each computes its tile columns and stores them once through the
+    NVLink multicast mapping; both buffers then hold the oracle's whole result."""
+    import socket
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_multicast_worker, args=(2, port), nprocs=2, join=True)
