@@ -40,7 +40,7 @@ KernelTiming& kernel_timing() {
 
 namespace {
 
-enum class Mmt4dPath { None, Generic, Tc, TcRetile, Gemv, ZeroFill };
+enum class Mmt4dPath { None, Generic, Tc, TcRetile, TcSw, Gemv, ZeroFill };
 
 // Kernel selection, the analogue of ukernel/mmt4d.c:105-138 (early-out, then an
 // architecture-specific tile function, else the generic one).
@@ -63,6 +63,9 @@ int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path)
     // Without scratch, a 16-bit K0 = 1 operand ([tile][K1][16]) can still be read by TMA as an
     // MN-major tensor-core operand; K0 = 2 operands cannot and fall to the generic kernel.
     if (!have_ws && mmt4d_tc_direct_eligible(p)) { *path = Mmt4dPath::Tc; return 0; }
+    // Any other tensor-core triple without scratch: the kernel whose producer warps re-tile the
+    // operands on their way into shared memory.
+    if (!have_ws && mmt4d_tc_sw_eligible(p)) { *path = Mmt4dPath::TcSw; return 0; }
   }
   *path = Mmt4dPath::Generic;
   return 0;
@@ -73,6 +76,7 @@ int path_code(Mmt4dPath p) {
     case Mmt4dPath::None: return IREE_UK_B200_PATH_NONE;
     case Mmt4dPath::Generic: return IREE_UK_B200_PATH_GENERIC;
     case Mmt4dPath::Tc: return IREE_UK_B200_PATH_TCGEN05;
+    case Mmt4dPath::TcSw: return IREE_UK_B200_PATH_TCGEN05;
     case Mmt4dPath::TcRetile: return IREE_UK_B200_PATH_TCGEN05_RETILE;
     case Mmt4dPath::Gemv: return IREE_UK_B200_PATH_GEMV;
     default: return IREE_UK_B200_PATH_ZERO_FILL;
@@ -91,6 +95,7 @@ int run_mmt4d(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, bool h
     case Mmt4dPath::Gemv: return launch_mmt4d_gemv_s16u4(p, stream);
     case Mmt4dPath::TcRetile: return launch_mmt4d_tc(p, ws, ws_bytes, kTcVariantDefault, stream);
     case Mmt4dPath::Tc: return launch_mmt4d_tc(p, nullptr, 0, kTcVariantDirect, stream);
+    case Mmt4dPath::TcSw: return launch_mmt4d_tc_sw(p, stream);
     default: return launch_mmt4d_generic(p, stream);
   }
 }

@@ -65,6 +65,9 @@ size_t matmul_workspace_size(uint32_t flags, int64_t M, int64_t N, int64_t K);
 int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b, const char* rhs,
                            int64_t rhs_pitch_b, char* out, int64_t out_stride0, int64_t M, int64_t N,
                            int64_t K, void* ws, size_t ws_bytes, cudaStream_t stream);
+// Tensor-core mmt4d without scratch (operands re-tiled on the way into shared memory).
+bool mmt4d_tc_sw_eligible(const iree_uk_mmt4d_params_t* p);
+int launch_mmt4d_tc_sw(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
 // Process-wide choice for f32f32f32 with 16x16 tiles: 0 = CUDA cores in the reference's
 // accumulation order (default), 1 = tensor cores, three tf32 products per term.
 int f32_mode();

@@ -81,6 +81,11 @@ struct TcParams {
   int32_t accumulate;
   int32_t out_is_int;
   int32_t out_vec32;     // output rows may be accessed with 32-byte vectors
+  // scratch-free kernel: the operands as they lie, [tile][K1][16][K0]
+  const char* src_a;
+  const char* src_b;
+  int64_t src_stride_a, src_stride_b;  // bytes between tile rows
+  int64_t K1;
   int32_t triple;        // f32 operands as hi/lo tf32 planes, three MMAs per K slice
   int32_t out16;         // 0: 32-bit output; 1: f16 output, 2: bf16 output (rounded once, RNE)
   int32_t use_multicast; // output tiles are stored through an NVLink multicast mapping
@@ -939,6 +944,250 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// the scratch-free kernel: operands re-tiled on the way into shared memory
+// ---------------------------------------------------------------------------------------
+// Same MMA and epilogue roles as mmt4d_tc_kernel, but the stages are filled by four producer
+// warps instead of TMA: a mmt4d operand [tile][K1][16][K0] holds, for one tile and the K range
+// of one stage (128 bytes per row), exactly 2 KB of contiguous memory; the producers read it
+// with 16-byte loads and scatter the G = K0 * element-size byte granules to their places in the
+// K-major 128-byte-swizzled stage (row = m0, 16-byte chunk index XOR (row & 7)). No pre-pass and
+// no scratch: this is what a call without a workspace gets. The shared-memory stores cost issue
+// slots and bandwidth the TMA form does not spend, so with a workspace the TMA kernels are used.
+constexpr int kSwGroups = 3;                       // producer groups of 4 warps; group g fills stages g, g+3, ...
+constexpr int kSwProducerWarps = 4 * kSwGroups;    // warps 0..11
+constexpr int kSwMmaWarp = kSwProducerWarps + 4;   // warps 12..15 epilogue, 16 MMA issuer
+constexpr int kSwThreads = (kSwMmaWarp + 1) * 32;
+
+template <int G>
+__device__ __forceinline__ void st_granule(uint32_t addr, const uint32_t (&v)[4], int i) {
+  // granule i of the 16-byte vector v (G bytes each)
+  if (G == 16) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+  } else if (G == 8) {
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};" :: "r"(addr), "r"(v[2 * i]), "r"(v[2 * i + 1]) : "memory");
+  } else if (G == 4) {
+    asm volatile("st.shared.b32 [%0], %1;" :: "r"(addr), "r"(v[i]) : "memory");
+  } else if (G == 2) {
+    const uint32_t w = v[i >> 1] >> ((i & 1) * 16);
+    asm volatile("st.shared.b16 [%0], %1;" :: "r"(addr), "h"(uint16_t(w)) : "memory");
+  } else {
+    const uint32_t w = v[i >> 2] >> ((i & 3) * 8);
+    asm volatile("st.shared.b8 [%0], %1;" :: "r"(addr), "r"(w & 0xFFu) : "memory");
+  }
+}
+
+// One stage: BM/16 LHS tiles then bn/16 RHS tiles, each 16 rows x 128 bytes of K (k1 steps
+// [k1_0, k1_0 + 128/G)). Thread t of a group's 128 owns vector t of every tile's 2 KB; the loads
+// of the next batch of tiles are issued before the current batch is stored, so one global-memory
+// latency is exposed per stage, not one per batch.
+struct SwStageSrc {
+  const char* a;      // LHS tile row of the first tile, at k1_0
+  const char* b;      // RHS likewise
+  int64_t stride_a, stride_b;
+  int a_valid, b_valid;  // tiles that exist (the rest of the stage keeps stale rows nobody reads)
+};
+
+template <int G>
+__device__ __forceinline__ void sw_fill_stage(const SwStageSrc& src, int a_tiles, int b_tiles,
+                                              bool k_ok, uint32_t smem, int t) {
+  constexpr int RPV = 16 / G;            // rows covered by one 16-byte vector
+  const int k1_local = t / G;
+  const int sub = t - k1_local * G;
+  const uint32_t col = uint32_t(k1_local * G);
+  const uint32_t chunk = col >> 4, within = col & 15u;
+  const int total = a_tiles + b_tiles;
+  constexpr int kBatch = 8;
+  auto load = [&](int slot) -> uint4 {
+    const bool is_a = slot < a_tiles;
+    const int i = is_a ? slot : slot - a_tiles;
+    const bool ok = k_ok && slot < total && i < (is_a ? src.a_valid : src.b_valid);
+    const char* p = is_a ? src.a + int64_t(i) * src.stride_a : src.b + int64_t(i) * src.stride_b;
+    return ok ? __ldg(reinterpret_cast<const uint4*>(p) + t) : make_uint4(0u, 0u, 0u, 0u);
+  };
+  uint4 cur[kBatch], nxt[kBatch];
+#pragma unroll
+  for (int b = 0; b < kBatch; ++b) cur[b] = load(b);
+  for (int b0 = 0; b0 < total; b0 += kBatch) {
+    if (b0 + kBatch < total) {
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) nxt[b] = load(b0 + kBatch + b);
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      if (b0 + b < total) {
+        // (Some lanes of a warp hit the same banks in the same step — a two-way conflict for
+        // 2- and 4-byte granules. Rotating the per-lane store order removes it but measured
+        // slower: the extra selects cost more issue slots than the conflicts.)
+        const uint32_t v[4] = {cur[b].x, cur[b].y, cur[b].z, cur[b].w};
+#pragma unroll
+        for (int i = 0; i < RPV; ++i) {
+          // rows of the LHS tiles come first in the stage, the RHS tiles follow directly
+          const uint32_t row = uint32_t((b0 + b) * 16 + sub * RPV + i);
+          st_granule<G>(smem + row * 128u + ((chunk ^ (row & 7u)) << 4) + within, v, i);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) cur[b] = nxt[b];
+  }
+}
+
+template <bool IS_INT, int G>
+__global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid_constant__ TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t tmem_full_bar[2];
+  __shared__ __align__(8) uint64_t tmem_empty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t stage_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t stage_bytes = uint32_t(P.stage_bytes_a + P.stage_bytes_b);
+  const int S = P.num_stages;
+  const int num_tiles = P.m_tiles * P.n_tiles;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 128);  // every thread of the filling group arrives
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&tmem_full_bar[b]), 1);
+      mbar_init(smem_u32(&tmem_empty_bar[b]), 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == kSwMmaWarp) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  pdl_wait();
+
+  if (warp < kSwProducerWarps) {
+    // ------------------------------- producers -------------------------------
+    // Group g (four warps) fills every kSwGroups-th stage of the running sequence of k-blocks, so
+    // up to kSwGroups stages are being fetched at the same time.
+    const int group = warp >> 2;
+    const int t = threadIdx.x & 127;
+    bool ok = true;
+    const int num_kb = P.num_kb;
+    constexpr int kps = 128 / G;  // k1 steps per stage
+    const int b_tiles = P.bn >> 4;
+    long long seq = 0;            // k-blocks since the start of the kernel, over all tiles
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int mt, nt;
+      tile_coords(P, tile, &mt, &nt);
+      const int64_t a0 = int64_t(mt) * (BM / 16), b0 = int64_t(nt) * b_tiles;
+      for (int kb = 0; kb < num_kb; ++kb, ++seq) {
+        if (int(seq % kSwGroups) != group) continue;
+        const int stage = int(seq % S);
+        const uint32_t phase = uint32_t((seq / S) & 1);
+        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
+          atomicOr(P.status, kStatusProducerTimeout);
+          abort_flag = 1;
+          ok = false;
+          break;
+        }
+        const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
+        if (!(P.debug_flags & 4u)) {
+          const int64_t k1_0 = int64_t(kb) * kps;
+          SwStageSrc src;
+          src.a = P.src_a + a0 * P.src_stride_a + k1_0 * (16 * G);
+          src.b = P.src_b + b0 * P.src_stride_b + k1_0 * (16 * G);
+          src.stride_a = P.src_stride_a;
+          src.stride_b = P.src_stride_b;
+          src.a_valid = int(min(int64_t(BM / 16), P.M1 - a0));
+          src.b_valid = int(min(int64_t(b_tiles), P.N1 - b0));
+          sw_fill_stage<G>(src, BM / 16, b_tiles, k1_0 + t / G < P.K1, sa, t);
+        }
+        // make the generic-proxy stores visible to the tensor core (async proxy), then signal
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (!(P.debug_flags & 8u)) mbar_arrive(smem_u32(&full_bar[stage]));
+      }
+    }
+  } else if (warp == kSwMmaWarp) {
+    // ------------------------------- MMA issuer -------------------------------
+    int stage = 0;
+    uint32_t phase = 0;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    bool ok = true;
+    const MmaIssue mi = make_mma_issue(P);
+    const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
+    const int num_kb = P.num_kb;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
+        if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
+        abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn);
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
+          if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
+          abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
+        if (elect_one()) {
+          issue_stage_mmas<IS_INT, false>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+          tc_commit(smem_u32(&empty_bar[stage]));
+          if (kb == num_kb - 1) tc_commit(smem_u32(&tmem_full_bar[buf]));
+        }
+        __syncwarp();
+        if (++stage == S) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------
+    const int q = warp & 3;
+    const int m_local = q * 32 + lane;
+    const uint32_t epi_stage = stage_base + uint32_t(S) * stage_bytes + uint32_t(q) * kEpiStageBytes;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    const int chunks = P.bn >> 4;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int mt, nt;
+      tile_coords(P, tile, &mt, &nt);
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp))) {
+        if (lane == 0) atomicOr(P.status, kStatusEpilogueTimeout);
+        abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = int64_t(mt) * BM + m_local;
+      const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
+      epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks, epi_stage, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
+      if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kSwMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -1930,6 +2179,122 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
                   : launch_main(mmt4d_tc_kernel<false>, grid, 1, smem, stream, P);
   }
   if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  if (tev) {
+    cudaEventRecord(tev[2], stream);
+    ++timing.calls;
+  }
+  return cuda_status(cudaGetLastError());
+}
+
+}  // namespace uk
+
+namespace uk {
+namespace {
+
+using SwKernel = void (*)(const TcParams);
+// [is_int][log2 G]
+SwKernel sw_kernel(bool is_int, int G) {
+  int lg = 0;
+  while ((1 << lg) < G) ++lg;
+  static const SwKernel table[2][5] = {
+      {mmt4d_tc_sw_kernel<false, 1>, mmt4d_tc_sw_kernel<false, 2>, mmt4d_tc_sw_kernel<false, 4>,
+       mmt4d_tc_sw_kernel<false, 8>, mmt4d_tc_sw_kernel<false, 16>},
+      {mmt4d_tc_sw_kernel<true, 1>, mmt4d_tc_sw_kernel<true, 2>, mmt4d_tc_sw_kernel<true, 4>,
+       mmt4d_tc_sw_kernel<true, 8>, mmt4d_tc_sw_kernel<true, 16>}};
+  return table[is_int ? 1 : 0][lg];
+}
+
+// Raises the dynamic shared-memory limit of every scratch-free kernel once per device.
+bool sw_kernels_ready(const DeviceInfo* di, int* max_dyn) {
+  constexpr int kMaxDevices = 64;
+  static int limit[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return false;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!limit[dev]) {
+    int optin = 0;
+    if (cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess)
+      return false;
+    int lim = optin;
+    for (int is_int = 0; is_int < 2; ++is_int)
+      for (int G = 1; G <= 16; G *= 2) {
+        const void* fn = reinterpret_cast<const void*>(sw_kernel(is_int != 0, G));
+        cudaFuncAttributes fa;
+        if (cudaFuncGetAttributes(&fa, fn) != cudaSuccess) return false;
+        const int dyn = optin - int(fa.sharedSizeBytes);
+        if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) != cudaSuccess) {
+          cudaGetLastError();
+          return false;
+        }
+        lim = std::min(lim, dyn);
+      }
+    limit[dev] = lim;
+  }
+  (void)di;
+  *max_dyn = limit[dev];
+  return true;
+}
+
+}  // namespace
+
+bool mmt4d_tc_sw_eligible(const iree_uk_mmt4d_params_t* p) {
+  TypeInfo ti;
+  return tc_type_info(p->flags, &ti) && !ti.triple && mmt4d_tc_eligible(p);
+}
+
+// Tensor-core mmt4d without scratch: one launch of mmt4d_tc_sw_kernel.
+int launch_mmt4d_tc_sw(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
+  TypeInfo ti;
+  if (!tc_type_info(p->flags, &ti) || ti.triple || !mmt4d_tc_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
+  uint32_t* status = device_status_word();
+  const DeviceInfo* di = device_info();
+  int max_dyn = 0;
+  if (!status || !di || !sw_kernels_ready(di, &max_dyn)) return IREE_UK_B200_CUDA_ERROR;
+  TcParams P;
+  std::memset(&P, 0, sizeof P);
+  KernelTiming& timing = kernel_timing();
+  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  if (tev) { cudaEventRecord(tev[0], stream); cudaEventRecord(tev[1], stream); }
+  const int G = p->K0 * ti.es;
+  const int bn = pick_bn(p->M, p->N);
+  P.src_a = static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * ti.es;
+  P.src_b = static_cast<const char*>(p->rhs_buffer) + p->rhs_offset * ti.es;
+  P.src_stride_a = p->lhs_stride0 * ti.es;
+  P.src_stride_b = p->rhs_stride0 * ti.es;
+  P.K1 = p->K;
+  const int kps = 128 / G;  // k1 steps per 128-byte swizzle row
+  P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
+  P.desc_lbo_a = P.desc_lbo_b = 1;
+  P.kadv_a = P.kadv_b = 2;
+  P.kbox_units_a = uint32_t(BM * 128) >> 4;
+  P.kbox_units_b = uint32_t(bn * 128) >> 4;
+  P.idesc = make_idesc(ti, bn, false);
+  P.kboxes = 1;
+  P.mma_per_box = 4;
+  P.stage_bytes_a = BM * 128;
+  P.stage_bytes_b = bn * 128;
+  P.num_kb = int((p->K + kps - 1) / kps);
+  P.bn = bn;
+  P.m_tiles = int((p->M * 16 + BM - 1) / BM);
+  P.n_tiles = int((p->N * 16 + bn - 1) / bn);
+  P.group_m = std::min(P.m_tiles, 16);
+  P.out = static_cast<char*>(p->out_buffer) + p->out_offset * ti.out_es;
+  P.out_stride0 = p->out_stride0;
+  P.M1 = p->M;
+  P.N1 = p->N;
+  P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
+  P.out_is_int = ti.is_int ? 1 : 0;
+  P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * ti.out_es) % 32 == 0) ? 1 : 0;
+  P.out16 = ti.out_es == 2 ? (ti.fmt == 0u ? 1 : 2) : 0;
+  P.status = status;
+  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
+  const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
+  P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
+  if (smem > size_t(max_dyn)) return IREE_UK_B200_CUDA_ERROR;
+  const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
+  sw_kernel(ti.is_int, G)<<<grid, kSwThreads, smem, stream>>>(P);
   if (tev) {
     cudaEventRecord(tev[2], stream);
     ++timing.calls;

@@ -74,7 +74,7 @@ def _rand_bytes(n):
 
 
 def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None, copies=1,
-                graph_calls=0):
+                graph_calls=0, use_ws=True):
     """``copies`` > 1: the call is timed as a sweep over that many independent buffer sets
     (see _time_rotating); otherwise one call per event pair, with ``flush`` read in between."""
     lb, rb, _ = abi.MMT4D_BITS[flags & 0xFF]
@@ -89,7 +89,7 @@ def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None
         out = torch.randn(M * N * M0 * N0, device="cuda") if float_dtype is not None else \
             torch.zeros(M * N * M0 * N0, dtype=torch.int32, device="cuda")
         p = _mmt4d_params(flags, M, N, K, M0, N0, K0, lhs, rhs, out)
-        nws = uk.mmt4d_workspace_size(p)
+        nws = uk.mmt4d_workspace_size(p) if use_ws else 0
         ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
         path = uk.mmt4d_path(p, ws is not None)
         keep.append((lhs, rhs, out, ws, p))
@@ -193,7 +193,7 @@ def _matmul_rowmajor_case(M, N, K, bf16_peak):
             "chain_parts_ms": parts, "chain_tiles": "16x16x2"}
 
 
-def run(peaks, only=None, custom=None):
+def run(peaks, only=None, custom=None, custom_ws=True):
     """All supplementary configurations, or those whose name contains ``only``. ``custom`` =
     (type name, M1, N1, K1) adds one tensor-core mmt4d of that size (used for profiling)."""
     res = {}
@@ -225,8 +225,10 @@ def run(peaks, only=None, custom=None):
                          "f32": (abi.MMT4D_F32F32F32, 1, torch.float32),
                          "s8": (abi.MMT4D_S8S8S32, 2, None)}[tname]
         prev = uk.set_f32_mode(uk.F32_MODE_TF32X3) if tname == "f32" else None
-        k, r = _mmt4d_case("mmt4d_%s_custom_%dx%dx%d" % (tname, cm, cn, ck), flags, cm, cn, ck,
-                           16, 16, k0, peaks, None, dt)
+        small = cm * cn * ck < (1 << 24)
+        k, r = _mmt4d_case("mmt4d_%s_custom_%dx%dx%d%s" % (tname, cm, cn, ck, "" if custom_ws else "_no_ws"),
+                           flags, cm, cn, ck, 16, 16, k0, peaks, None, dt, use_ws=custom_ws,
+                           copies=24 if small else 1, graph_calls=100 if small else 0)
         if prev is not None:
             uk.set_f32_mode(prev)
         res[k] = r
@@ -315,6 +317,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default=None)
     ap.add_argument("--mmt4d", default=None)
+    ap.add_argument("--no-ws", action="store_true")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
@@ -330,7 +333,7 @@ def main():
     except OSError:
         peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
     only = a.only if a.only is not None else ("\0" if custom else None)
-    print(json.dumps(run(peaks, only=only, custom=custom)))
+    print(json.dumps(run(peaks, only=only, custom=custom, custom_ws=not a.no_ws)))
 
 
 if __name__ == "__main__":

@@ -330,6 +330,35 @@ def test_mmt4d_tensor_core_without_workspace(t, shape, accumulate):
     assert np.array_equal(got, G.oracle_mmt4d(case)), case.label()
 
 
+@pytest.mark.parametrize("tile", [
+    (abi.MMT4D_S8S8S32, 1), (abi.MMT4D_S8S8S32, 2), (abi.MMT4D_S8S8S32, 4), (abi.MMT4D_S8S8S32, 8),
+    (abi.MMT4D_S8S8S32, 16), (abi.MMT4D_BF16BF16F32, 2), (abi.MMT4D_F16F16F32, 4),
+    (abi.MMT4D_BF16BF16F32, 8),
+    (abi.MMT4D_BF16BF16BF16 | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS, 2),
+], ids=lambda t: "t%x_k0_%d" % t)
+@pytest.mark.parametrize("shape", [(1, 1, 1), (8, 16, 64), (9, 17, 65), (24, 40, 31), (3, 50, 300)],
+                         ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_scratch_free_kernel(tile, shape, accumulate):
+    """Every other tensor-core triple without a workspace: the kernel whose producer warps
+    re-tile the operands into shared memory themselves. Small-integer values: exact."""
+    t, K0 = tile
+    M, N, K = shape
+    case = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, accumulate, seed=19, mode="exact", loose=False)
+    got, path = G.run_mmt4d_case(case, use_workspace=False)
+    assert path == abi.PATH_TCGEN05
+    assert np.array_equal(got, G.oracle_mmt4d(case)), case.label()
+
+
+def test_mmt4d_scratch_free_kernel_normal_values():
+    case = cases.Mmt4dCase(abi.MMT4D_BF16BF16F32, 16, 16, 2, 40, 24, 300, 1, seed=23, mode="normal",
+                           loose=False)
+    got, path = G.run_mmt4d_case(case, use_workspace=False)
+    assert path == abi.PATH_TCGEN05
+    want = G.oracle_mmt4d(case)
+    assert cases.rel_frobenius(got.view(np.float32), want.view(np.float32)) <= 1e-3
+
+
 def test_bounded_waits_report_a_timeout_instead_of_hanging():
     """Failure detection without faulting the GPU: a test hook makes the TMA producer never fill
     a stage, so the MMA warp's wait on the full barrier runs out (about a second); the kernel
