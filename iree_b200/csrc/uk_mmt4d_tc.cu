@@ -986,6 +986,27 @@ __device__ __forceinline__ void st_granule(uint32_t addr, const uint32_t (&v)[4]
 // [k1_0, k1_0 + 128/G)). Thread t of a group's 128 owns vector t of every tile's 2 KB; the loads
 // of the next batch of tiles are issued before the current batch is stored, so one global-memory
 // latency is exposed per stage, not one per batch.
+// Which of a tile's 128 vectors (k1 step, group of 16/G rows) thread t of a producer group
+// owns. The natural order (t = k1 * G + group) makes lanes of a warp whose rows agree in
+// (row & 7) store to the same banks in the same step for 2- and 4-byte granules; these orders
+// give every lane of a warp its own bank (lanes that share a 32-bit word merge):
+//   G = 4: a warp takes 16 k1 steps x 2 neighbouring row groups (rows r and r + 4),
+//   G = 2: a warp takes 32 k1 steps x 1 row group.
+template <int G>
+__device__ __forceinline__ void sw_vector_of_thread(int t, int* k1_local, int* sub) {
+  const int w = t >> 5, l = t & 31;
+  if (G == 4) {
+    *sub = (l & 1) + 2 * (w & 1);
+    *k1_local = (l >> 1) + 16 * (w >> 1);
+  } else if (G == 2) {
+    *sub = w & 1;
+    *k1_local = l + 32 * (w >> 1);
+  } else {
+    *k1_local = t / G;
+    *sub = t - *k1_local * G;
+  }
+}
+
 struct SwStageSrc {
   const char* a;      // LHS tile row of the first tile, at k1_0
   const char* b;      // RHS likewise
@@ -993,49 +1014,67 @@ struct SwStageSrc {
   int a_valid, b_valid;  // tiles that exist (the rest of the stage keeps stale rows nobody reads)
 };
 
+// 16-byte read-only load that does not allocate in L1: every operand byte is used once per CTA.
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// `n` tiles of one operand (n <= 8) from `p` (first tile, this thread's vector), `stride` bytes
+// apart, the first `valid` of which exist; `off[i]` is the shared-memory offset of granule i
+// inside a tile's 2 KB of rows.
+template <int G>
+__device__ __forceinline__ void sw_load_batch(uint4 (&v)[8], const char* p, int64_t stride, int n,
+                                              int valid, bool k_ok) {
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    const bool ok = k_ok && b < n && b < valid;
+    v[b] = ok ? ld_stream_v4(p + int64_t(b) * stride) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+template <int G>
+__device__ __forceinline__ void sw_store_batch(const uint4 (&v)[8], int n, uint32_t smem,
+                                               const uint32_t (&off)[16 / G]) {
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    if (b < n) {
+      const uint32_t w[4] = {v[b].x, v[b].y, v[b].z, v[b].w};
+#pragma unroll
+      for (int i = 0; i < 16 / G; ++i) st_granule<G>(smem + uint32_t(b) * 2048u + off[i], w, i);
+    }
+  }
+}
+
 template <int G>
 __device__ __forceinline__ void sw_fill_stage(const SwStageSrc& src, int a_tiles, int b_tiles,
                                               bool k_ok, uint32_t smem, int t) {
   constexpr int RPV = 16 / G;            // rows covered by one 16-byte vector
-  const int k1_local = t / G;
-  const int sub = t - k1_local * G;
+  int k1_local, sub;
+  sw_vector_of_thread<G>(t, &k1_local, &sub);
+  const int vec = k1_local * G + sub;    // index of this thread's vector in a tile's 2 KB
   const uint32_t col = uint32_t(k1_local * G);
   const uint32_t chunk = col >> 4, within = col & 15u;
-  const int total = a_tiles + b_tiles;
-  constexpr int kBatch = 8;
-  auto load = [&](int slot) -> uint4 {
-    const bool is_a = slot < a_tiles;
-    const int i = is_a ? slot : slot - a_tiles;
-    const bool ok = k_ok && slot < total && i < (is_a ? src.a_valid : src.b_valid);
-    const char* p = is_a ? src.a + int64_t(i) * src.stride_a : src.b + int64_t(i) * src.stride_b;
-    return ok ? __ldg(reinterpret_cast<const uint4*>(p) + t) : make_uint4(0u, 0u, 0u, 0u);
-  };
-  uint4 cur[kBatch], nxt[kBatch];
+  uint32_t off[RPV];
 #pragma unroll
-  for (int b = 0; b < kBatch; ++b) cur[b] = load(b);
-  for (int b0 = 0; b0 < total; b0 += kBatch) {
-    if (b0 + kBatch < total) {
-#pragma unroll
-      for (int b = 0; b < kBatch; ++b) nxt[b] = load(b0 + kBatch + b);
-    }
-#pragma unroll
-    for (int b = 0; b < kBatch; ++b) {
-      if (b0 + b < total) {
-        // (Some lanes of a warp hit the same banks in the same step — a two-way conflict for
-        // 2- and 4-byte granules. Rotating the per-lane store order removes it but measured
-        // slower: the extra selects cost more issue slots than the conflicts.)
-        const uint32_t v[4] = {cur[b].x, cur[b].y, cur[b].z, cur[b].w};
-#pragma unroll
-        for (int i = 0; i < RPV; ++i) {
-          // rows of the LHS tiles come first in the stage, the RHS tiles follow directly
-          const uint32_t row = uint32_t((b0 + b) * 16 + sub * RPV + i);
-          st_granule<G>(smem + row * 128u + ((chunk ^ (row & 7u)) << 4) + within, v, i);
-        }
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < kBatch; ++b) cur[b] = nxt[b];
+  for (int i = 0; i < RPV; ++i) {
+    const uint32_t row = uint32_t(sub * RPV + i);
+    off[i] = row * 128u + ((chunk ^ (row & 7u)) << 4) + within;
   }
+  // LHS tiles (a_tiles = 8) are one batch, RHS tiles (b_tiles <= 16) up to two; the next batch
+  // is loaded before the current one is stored.
+  const char* pa = src.a + vec * 16;
+  const char* pb = src.b + vec * 16;
+  uint4 v0[8], v1[8];
+  sw_load_batch<G>(v0, pa, src.stride_a, a_tiles, src.a_valid, k_ok);
+  sw_load_batch<G>(v1, pb, src.stride_b, b_tiles, src.b_valid, k_ok);
+  sw_store_batch<G>(v0, a_tiles, smem, off);
+  const uint32_t smem_b = smem + uint32_t(a_tiles) * 2048u;
+  if (b_tiles > 8)
+    sw_load_batch<G>(v0, pb + 8 * src.stride_b, src.stride_b, b_tiles - 8, src.b_valid - 8, k_ok);
+  sw_store_batch<G>(v1, b_tiles, smem_b, off);
+  if (b_tiles > 8) sw_store_batch<G>(v0, b_tiles - 8, smem_b + 8u * 2048u, off);
 }
 
 template <bool IS_INT, int G>
@@ -1113,7 +1152,9 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
           src.stride_b = P.src_stride_b;
           src.a_valid = int(min(int64_t(BM / 16), P.M1 - a0));
           src.b_valid = int(min(int64_t(b_tiles), P.N1 - b0));
-          sw_fill_stage<G>(src, BM / 16, b_tiles, k1_0 + t / G < P.K1, sa, t);
+          int k1_local, sub;
+          sw_vector_of_thread<G>(t, &k1_local, &sub);
+          sw_fill_stage<G>(src, BM / 16, b_tiles, k1_0 + k1_local < P.K1, sa, t);
         }
         // make the generic-proxy stores visible to the tensor core (async proxy), then signal
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -193,7 +193,7 @@ def _matmul_rowmajor_case(M, N, K, bf16_peak):
             "chain_parts_ms": parts, "chain_tiles": "16x16x2"}
 
 
-def run(peaks, only=None, custom=None, custom_ws=True):
+def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
     """All supplementary configurations, or those whose name contains ``only``. ``custom`` =
     (type name, M1, N1, K1) adds one tensor-core mmt4d of that size (used for profiling)."""
     res = {}
@@ -255,6 +255,10 @@ def run(peaks, only=None, custom=None, custom_ws=True):
         r["graph_replay"]["gbs"] = gemv_bytes / r["graph_replay"]["ms_per_call"] / 1e6
         res[k] = r
 
+    if custom_matmul is not None:
+        mm, mn, mk = custom_matmul
+        res["matmul_rowmajor_bf16_custom_%dx%dx%d" % (mm, mn, mk)] = _matmul_rowmajor_case(
+            mm, mn, mk, bf16_peak)
     # row-major matmul at the headline dimensions: the fused entry point beside the chain
     # pack LHS, pack RHS (TRANSPOSE_INNER | TRANSPOSE_OUTER), mmt4d, unpack run on this library
     if want("matmul_rowmajor_bf16_8192x28672x8192"):
@@ -307,8 +311,8 @@ def run(peaks, only=None, custom=None, custom_ws=True):
 
 
 def main():
-    """``python -m iree_b200.supplementary [--only SUBSTR] [--mmt4d bf16,M1,N1,K1]
-    [--iters N] [--warmup N]``: prints one JSON object. Small, single-kernel runs of this
+    """``python -m iree_b200.supplementary [--only SUBSTR] [--mmt4d bf16,M1,N1,K1 [--no-ws]]
+    [--matmul M,N,K] [--iters N] [--warmup N]``: prints one JSON object. Small, single-kernel runs of this
     command are what the profiles under ``profiles/`` were captured from."""
     import argparse
     import json
@@ -318,6 +322,7 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--mmt4d", default=None)
     ap.add_argument("--no-ws", action="store_true")
+    ap.add_argument("--matmul", default=None, help="M,N,K of a bf16 row-major matmul (elements)")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
@@ -332,8 +337,9 @@ def main():
         peaks = json.load(open(peaks_path))
     except OSError:
         peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-    only = a.only if a.only is not None else ("\0" if custom else None)
-    print(json.dumps(run(peaks, only=only, custom=custom, custom_ws=not a.no_ws)))
+    mm = tuple(int(x) for x in a.matmul.split(",")) if a.matmul else None
+    only = a.only if a.only is not None else ("\0" if (custom or mm) else None)
+    print(json.dumps(run(peaks, only=only, custom=custom, custom_ws=not a.no_ws, custom_matmul=mm)))
 
 
 if __name__ == "__main__":

@@ -161,3 +161,27 @@ def test_matmul_empty_reduction_and_rejections():
         uk.matmul(p, ws[:256])             # scratch too small
     assert e.value.status == abi.WORKSPACE_TOO_SMALL
     assert int(out.sum()) == 9 * 32
+
+
+def test_matmul_column_shards_equal_the_whole():
+    """N-sharding of the row-major matmul needs no extra entry point: shard g passes
+    rhs_offset = out_offset = its first column and its column count, with the full pitches."""
+    import torch
+    from iree_b200 import ukernel as uk
+    M, N, K = 300, 520, 200
+    lhs, rhs, _ = _operands(abi.MMT4D_BF16BF16F32, M, N, K, seed=4)
+    whole, _, _ = _run_gpu(abi.MMT4D_BF16BF16F32, lhs, rhs, None)
+    dl, dr = torch.from_numpy(lhs).cuda(), torch.from_numpy(rhs).cuda()
+    out = torch.zeros(M, N, device="cuda")
+    bounds = [0, 128, 136, 400, 520]   # uneven shards, one of them 8 columns wide
+    for b, e in zip(bounds[:-1], bounds[1:]):
+        p = abi.MatmulParams()
+        p.lhs_buffer, p.rhs_buffer, p.out_buffer = dl.data_ptr(), dr.data_ptr(), out.data_ptr()
+        p.rhs_offset = p.out_offset = b
+        p.lhs_stride0, p.rhs_stride0, p.out_stride0 = K, N, N
+        p.M, p.N, p.K, p.flags = M, e - b, K, abi.MMT4D_BF16BF16F32
+        ws = torch.empty(uk.matmul_workspace_size(p), dtype=torch.uint8, device="cuda")
+        uk.matmul(p, ws)
+    torch.cuda.synchronize()
+    assert uk.device_status() == (0, 0)
+    assert np.array_equal(out.cpu().numpy(), whole)

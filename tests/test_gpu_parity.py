@@ -359,6 +359,48 @@ def test_mmt4d_scratch_free_kernel_normal_values():
     assert cases.rel_frobenius(got.view(np.float32), want.view(np.float32)) <= 1e-3
 
 
+def test_concurrent_host_threads_on_their_own_streams():
+    """The library keeps per-device caches behind mutexes and no per-call state: two host
+    threads enqueue different problems on their own streams with their own scratch at the
+    same time, many times over, and every result is the oracle's."""
+    import threading
+    import torch
+    from iree_b200 import ukernel as uk
+    specs = [(abi.MMT4D_S8S8S32, 2, (9, 17, 65)), (abi.MMT4D_BF16BF16F32, 2, (24, 40, 31))]
+    errors = []
+
+    def worker(t, K0, shape, use_ws):
+        try:
+            M, N, K = shape
+            case = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, 0, seed=29, mode="exact", loose=False)
+            want = G.oracle_mmt4d(case)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                lhs, rhs = G.to_device(case.lhs), G.to_device(case.rhs)
+                p0 = case.params(lhs.data_ptr(), rhs.data_ptr(), 0)
+                ws = torch.empty(max(uk.mmt4d_workspace_size(p0), 256), dtype=torch.uint8,
+                                 device="cuda") if use_ws else None
+                for _ in range(50):
+                    out = G.to_device(case.out_init)
+                    p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+                    uk.mmt4d(p, stream, ws)
+                    stream.synchronize()
+                    if not np.array_equal(out.cpu().numpy(), want):
+                        errors.append(case.label())
+                        return
+        except Exception as e:  # surfaced by the assertion below
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(t, k0, shape, i % 2 == 0))
+               for i, (t, k0, shape) in enumerate(specs * 2)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    G.check_device_status()
+
+
 def test_bounded_waits_report_a_timeout_instead_of_hanging():
     """Failure detection without faulting the GPU: a test hook makes the TMA producer never fill
     a stage, so the MMA warp's wait on the full barrier runs out (about a second); the kernel
