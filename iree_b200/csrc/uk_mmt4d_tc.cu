@@ -713,6 +713,7 @@ __device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
 // Dual-LHS stage (s16u4s32): shared memory holds [high-byte plane | low-byte plane | RHS]; each K
 // slice feeds two MMAs that share the RHS descriptor and accumulate into two TMEM regions
 // (d_tmem and d_tmem + bn), recombined as hi*256 + lo by the epilogue.
+template <bool PAIR>
 __device__ __forceinline__ void issue_stage_mmas_dual(const MmaIssue& m, uint32_t d_hi, uint32_t d_lo,
                                                       uint32_t a_units, uint32_t b_units,
                                                       bool first_kblock) {
@@ -722,8 +723,13 @@ __device__ __forceinline__ void issue_stage_mmas_dual(const MmaIssue& m, uint32_
     const uint64_t da_hi = (uint64_t(m.hi_a) << 32) | uint64_t((au & 0x3FFFu) | m.lo_a);
     const uint64_t da_lo = (uint64_t(m.hi_a) << 32) | uint64_t(((au + m.kbox_a) & 0x3FFFu) | m.lo_a);
     const uint64_t db = (uint64_t(m.hi_b) << 32) | uint64_t((bu & 0x3FFFu) | m.lo_b);
-    tc_mma<true>(d_hi, da_hi, db, m.idesc, acc);
-    tc_mma<true>(d_lo, da_lo, db, m.idesc2, acc);
+    if (PAIR) {
+      tc_mma_pair<true>(d_hi, da_hi, db, m.idesc, acc);
+      tc_mma_pair<true>(d_lo, da_lo, db, m.idesc2, acc);
+    } else {
+      tc_mma<true>(d_hi, da_hi, db, m.idesc, acc);
+      tc_mma<true>(d_lo, da_lo, db, m.idesc2, acc);
+    }
     acc = 1u;
     au += m.kadv_a;
     bu += m.kadv_b;
@@ -895,7 +901,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
           if (elect_one()) {
             if (IS_INT && mi.dual)
-              issue_stage_mmas_dual(mi, d_tmem, d_tmem + uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+              issue_stage_mmas_dual<false>(mi, d_tmem, d_tmem + uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             else
               issue_stage_mmas<IS_INT, false>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             tc_commit(smem_u32(&empty_bar[stage]));  // stage reusable once these MMAs finish
@@ -1014,14 +1020,6 @@ struct SwStageSrc {
   int a_valid, b_valid;  // tiles that exist (the rest of the stage keeps stale rows nobody reads)
 };
 
-// 16-byte read-only load that does not allocate in L1: every operand byte is used once per CTA.
-__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-
 // `n` tiles of one operand (n <= 8) from `p` (first tile, this thread's vector), `stride` bytes
 // apart, the first `valid` of which exist; `off[i]` is the shared-memory offset of granule i
 // inside a tile's 2 KB of rows.
@@ -1031,7 +1029,7 @@ __device__ __forceinline__ void sw_load_batch(uint4 (&v)[8], const char* p, int6
 #pragma unroll
   for (int b = 0; b < 8; ++b) {
     const bool ok = k_ok && b < n && b < valid;
-    v[b] = ok ? ld_stream_v4(p + int64_t(b) * stride) : make_uint4(0u, 0u, 0u, 0u);
+    v[b] = ok ? __ldg(reinterpret_cast<const uint4*>(p + int64_t(b) * stride)) : make_uint4(0u, 0u, 0u, 0u);
   }
 }
 template <int G>
@@ -1372,7 +1370,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn);
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn * (mi.dual ? 2 : 1));
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
             if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
@@ -1383,7 +1381,10 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
           tc_fence_after();
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
           if (elect_one()) {
-            issue_stage_mmas<IS_INT, true>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            if (IS_INT && mi.dual)
+              issue_stage_mmas_dual<true>(mi, d_tmem, d_tmem + uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            else
+              issue_stage_mmas<IS_INT, true>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             tc_commit_pair(smem_u32(&empty_bar[stage]), 3);  // both CTAs may refill the stage
             if (kb == num_kb - 1) tc_commit_pair(smem_u32(&tmem_full_bar[buf]), 3);  // accumulators done
           }
@@ -1411,8 +1412,13 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
       }
       tc_fence_after();
       const int64_t row = int64_t(mt) * 256 + int64_t(rank) * 128 + q * 32 + lane;
-      const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
-      epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks, epi_stage, lane);
+      if (P.dual) {
+        const uint32_t t_hi = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * 2 * P.bn);
+        epilogue_rows_dual(P, t_hi, t_hi + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
+      } else {
+        const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
+        epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks, epi_stage, lane);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[buf]), 0));
@@ -1944,32 +1950,43 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   const uint64_t db[3] = {uint64_t(kbytes), uint64_t(ncols), 1};
   const uint64_t sa[2] = {uint64_t(l.pitch), uint64_t(l.plane_bytes)};
   const uint64_t sb[2] = {uint64_t(l.pitch), uint64_t(l.pitch) * uint64_t(ncols)};
+  // The two-CTA form (256 rows x 128 columns per CTA pair, two accumulators of 128 columns, double
+  // buffered = all 512 TMEM columns) once every pair has a tile; the one-CTA form otherwise.
+  const DeviceInfo* di = device_info();
+  if (!di) return IREE_UK_B200_CUDA_ERROR;
+  const int pair_clusters = di->pair_clusters[1];
+  const bool pair = bn == 128 && p->M >= 256 && pair_clusters >= 1 &&
+                    ((p->M + 255) / 256) * ((ncols + 127) / 128) >= 74 &&
+                    !debug_int("IREE_UK_B200_DEBUG_S16U4_ONE_CTA", 0);
+  const int tile_m = pair ? 2 * BM : BM;
+  const int b_rows = pair ? bn / 2 : bn;
   const uint32_t ba[3] = {128, BM, 1};
-  const uint32_t bb[3] = {128, uint32_t(bn), 1};
+  const uint32_t bb[3] = {128, uint32_t(b_rows), 1};
   if (!encode_map(&P.map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, hi, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !encode_map(&P.map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, w8, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
     return IREE_UK_B200_CUDA_ERROR;
-  P.sa = {2, BM * 128, {128, 0, 0}, {0, BM, 0}, {0, 0, 1}};  // box 0: high plane, box 1: low plane
-  P.sb = {1, bn * 128, {128, 0, 0}, {0, bn, 0}, {0, 0, 0}};
+  // box 0: high plane, box 1: low plane
+  P.sa = {2, BM * 128, {128, 0, 0}, {0, tile_m, 0}, {0, 0, 1}, {0, pair ? BM : 0, 0}};
+  P.sb = {1, b_rows * 128, {128, 0, 0}, {0, bn, 0}, {0, 0, 0}, {0, pair ? b_rows : 0, 0}};
   P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
   P.desc_lbo_a = P.desc_lbo_b = 1;
   P.kadv_a = P.kadv_b = 2;
   P.kbox_units_a = uint32_t(BM * 128) >> 4;  // distance from the high to the low plane tile
   P.kbox_units_b = 0;
   // accumulate s32; LHS high bytes signed, low bytes unsigned; weights unsigned
-  const uint32_t common = (2u << 4) | (uint32_t(bn >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+  const uint32_t common = (2u << 4) | (uint32_t(bn >> 3) << 17) | (uint32_t(tile_m >> 4) << 24);
   P.idesc = common | (1u << 7);
   P.idesc2 = common;
   P.dual = 1;
   P.kboxes = 1;
   P.mma_per_box = 4;
   P.stage_bytes_a = 2 * BM * 128;
-  P.stage_bytes_b = bn * 128;
+  P.stage_bytes_b = b_rows * 128;
   P.num_kb = int((kbytes + 127) / 128);
   P.bn = bn;
-  P.m_tiles = int((p->M + BM - 1) / BM);
+  P.m_tiles = int((p->M + tile_m - 1) / tile_m);
   P.n_tiles = int((ncols + bn - 1) / bn);
-  P.group_m = std::min(P.m_tiles, 16);
+  P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
   P.out = static_cast<char*>(p->out_buffer) + p->out_offset * 4;
   P.out_stride0 = p->out_stride0;
   P.M1 = p->M;
@@ -1981,12 +1998,17 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
   const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
-  const DeviceInfo* di = device_info();
-  if (!di || smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
+  if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
   if (tev) cudaEventRecord(tev[1], stream);
-  const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
-  if (launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P) != cudaSuccess)
-    return IREE_UK_B200_CUDA_ERROR;
+  cudaError_t e;
+  if (pair) {
+    const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
+    e = launch_main(mmt4d_tc2_kernel<true>, grid, 2, smem, stream, P);
+  } else {
+    const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
+    e = launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P);
+  }
+  if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   if (tev) {
     cudaEventRecord(tev[2], stream);
     ++timing.calls;

@@ -151,7 +151,9 @@ def test_mmt4d_s16u4_gemv_path():
 
 
 @pytest.mark.parametrize("shape", [(32, 4, 16), (128, 8, 64), (200, 7, 33), (129, 5, 1),
-                                   (256, 448, 40)], ids=lambda s: "%dx%dx%d" % s)
+                                   (256, 448, 40),
+                                   # enough 256 x 128 tiles for the two-CTA form, ragged edges
+                                   (2560, 32, 5), (2700, 35, 3)], ids=lambda s: "%dx%dx%d" % s)
 @pytest.mark.parametrize("accumulate", [0, 1])
 def test_mmt4d_s16u4_tensor_core_path(shape, accumulate):
     """s16u4s32 1x32x8 with many rows: signed-high / unsigned-low byte planes against u8 weights
