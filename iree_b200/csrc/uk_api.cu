@@ -563,7 +563,8 @@ IREE_UK_B200_EXPORT int iree_uk_b200_debug_mmt4d_variant(const iree_uk_mmt4d_par
 }
 
 // Internal, not declared in the public header: benchmark timing of the tensor-core path.
-// enable != 0 creates the CUDA events (once) and makes every later tensor-core mmt4d call
+// enable != 0 creates the CUDA events (once) and makes every later (enable = 1) or every n-th
+// later (enable = n) tensor-core mmt4d call
 // record three of them: before the re-tile pre-pass, before the main kernel and after it.
 // The last 64 calls are remembered.
 IREE_UK_B200_EXPORT int iree_uk_b200_debug_kernel_timing(int enable) {
@@ -574,7 +575,9 @@ IREE_UK_B200_EXPORT int iree_uk_b200_debug_kernel_timing(int enable) {
         if (cudaEventCreate(&t.ev[c][i]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   }
   t.enabled = enable != 0;
+  t.every = enable > 1 ? enable : 1;  // enable = n > 1: record every n-th call only
   t.calls = 0;
+  t.seen = 0;
   return IREE_UK_B200_OK;
 }
 

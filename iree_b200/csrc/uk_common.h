@@ -101,9 +101,15 @@ inline int cuda_status(cudaError_t e) {
 struct KernelTiming {
   static constexpr int kRing = 64;  // calls remembered
   bool enabled = false;
-  cudaEvent_t ev[kRing][3] = {};  // per call: before pre-pass, before main, after main
+  int every = 1;                  // record one call in `every` (the others run unobserved)
+  long long seen = 0;             // tensor-core calls since timing was enabled
+  cudaEvent_t ev[kRing][3] = {};  // per recorded call: before pre-pass, before main, after main
   long long calls = 0;            // calls recorded since timing was enabled
-  cudaEvent_t* slot() { return ev[calls % kRing]; }
+  // The event triple for this call, or nullptr when the call is not to be recorded.
+  cudaEvent_t* next_slot() {
+    if (!enabled) return nullptr;
+    return (seen++ % every == 0) ? ev[calls % kRing] : nullptr;
+  }
 };
 KernelTiming& kernel_timing();
 

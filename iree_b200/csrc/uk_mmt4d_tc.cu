@@ -1923,7 +1923,7 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   if (!ws || ws_bytes < size_t(2 * l.plane_bytes + l.w_bytes)) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
   KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  cudaEvent_t* tev = timing.next_slot();
   if (tev) cudaEventRecord(tev[0], stream);
 
   const char* lhs = static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * 2;
@@ -2084,7 +2084,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   TcParams P;
   std::memset(&P, 0, sizeof P);
   KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  cudaEvent_t* tev = timing.next_slot();
   if (tev) cudaEventRecord(tev[0], stream);
   int bn = pick_bn(p->M, p->N);
   bool pair = false;
@@ -2317,7 +2317,7 @@ int launch_mmt4d_tc_sw(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
   TcParams P;
   std::memset(&P, 0, sizeof P);
   KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  cudaEvent_t* tev = timing.next_slot();
   if (tev) { cudaEventRecord(tev[0], stream); cudaEventRecord(tev[1], stream); }
   const int G = p->K0 * ti.es;
   const int bn = pick_bn(p->M, p->N);
@@ -2494,7 +2494,7 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   const DeviceInfo* di = device_info();
   if (!status || !di) return IREE_UK_B200_CUDA_ERROR;
   KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.enabled ? timing.slot() : nullptr;
+  cudaEvent_t* tev = timing.next_slot();
   if (tev) cudaEventRecord(tev[0], stream);
 
   // RHS: transposed once into K-major rows. LHS: used in place when TMA can address it,
