@@ -281,6 +281,14 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         p.flags = flags
         return p
 
+    # a plain device copy of the same 256 MiB, timed the same way on this GPU: what the memory
+    # system gives a kernel that reads and writes each byte once at this size
+    copy_gbs = None
+    if want("pack_") or want("unpack_"):
+        med, _ = _time(lambda: dst.copy_(src))
+        copy_gbs = nbytes / med / 1e6
+        res["device_copy_256MiB_same_timing"] = {"ms": med, "gbs": copy_gbs, "frac_hbm": copy_gbs / hbm}
+
     for name, p in [
         ("pack_f32_8192x8192_to_512x8192x16x1", pack_params(abi.PACK_F32F32, 512, 8192, 16, 1)),
         ("pack_f32_transpose_inner_512x8192x1x16",
@@ -293,7 +301,9 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
             continue
         med, best = _time(lambda: uk.pack(p))
         res[name] = {"ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
-                     "frac_hbm": nbytes / med / 1e6 / hbm, "path": uk.pack_path(p)}
+                     "frac_hbm": nbytes / med / 1e6 / hbm,
+                     "frac_of_same_size_copy": nbytes / med / 1e6 / copy_gbs,
+                     "path": uk.pack_path(p)}
 
     # unpack i32 [512][512][16][16] -> 8192x8192
     q = abi.UnpackParams()
@@ -306,7 +316,8 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         med, best = _time(lambda: uk.unpack(q))
         res["unpack_i32_512x512x16x16_to_8192x8192"] = {
             "ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
-            "frac_hbm": nbytes / med / 1e6 / hbm, "path": uk.unpack_path(q)}
+            "frac_hbm": nbytes / med / 1e6 / hbm,
+            "frac_of_same_size_copy": nbytes / med / 1e6 / copy_gbs, "path": uk.unpack_path(q)}
     return res
 
 
