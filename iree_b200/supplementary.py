@@ -284,7 +284,7 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
     # a plain device copy of the same 256 MiB, timed the same way on this GPU: what the memory
     # system gives a kernel that reads and writes each byte once at this size
     copy_gbs = None
-    if want("pack_") or want("unpack_"):
+    if only is None or "pack" in only:
         med, _ = _time(lambda: dst.copy_(src))
         copy_gbs = nbytes / med / 1e6
         res["device_copy_256MiB_same_timing"] = {"ms": med, "gbs": copy_gbs, "frac_hbm": copy_gbs / hbm}
@@ -302,7 +302,7 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         med, best = _time(lambda: uk.pack(p))
         res[name] = {"ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
                      "frac_hbm": nbytes / med / 1e6 / hbm,
-                     "frac_of_same_size_copy": nbytes / med / 1e6 / copy_gbs,
+                     "frac_of_same_size_copy": (nbytes / med / 1e6 / copy_gbs) if copy_gbs else None,
                      "path": uk.pack_path(p)}
 
     # unpack i32 [512][512][16][16] -> 8192x8192
@@ -317,7 +317,8 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         res["unpack_i32_512x512x16x16_to_8192x8192"] = {
             "ms": med, "ms_best": best, "gbs": nbytes / med / 1e6,
             "frac_hbm": nbytes / med / 1e6 / hbm,
-            "frac_of_same_size_copy": nbytes / med / 1e6 / copy_gbs, "path": uk.unpack_path(q)}
+            "frac_of_same_size_copy": (nbytes / med / 1e6 / copy_gbs) if copy_gbs else None,
+            "path": uk.unpack_path(q)}
     return res
 
 
