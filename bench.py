@@ -293,6 +293,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-supplementary", action="store_true")
+    ap.add_argument("--no-replicated", action="store_true",
+                    help="skip the replicated-output routes measured at N > 1")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -439,72 +441,77 @@ def main():
     # ---- replicated output (N > 1): all-gather + interleave beside the fused route, where
     # the kernel's epilogue stores every tile into all ranks' buffers over NVLink ----
     replicated = None
-    if world > 1:
-        from iree_b200 import sharding
-        rep_steps = max(3, min(10, args.steps))
-        tile = M0 * N0
-
-        def timed(fn):
-            fn()
-            barrier()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            for _ in range(rep_steps):
-                fn()
-            b.record(stream)
-            barrier()
-            tt = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device="cuda")
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            return float(tt.item()) / rep_steps
-
-        gathered_full = [None]
-
-        def gather_route():
-            uk.mmt4d(p, stream, ws)
-            gathered_full[0] = sharding.gather_output(out, M1, N1, tile, stream=stream)
-
-        gather_ms = timed(gather_route)
-        full_out = torch.zeros(M1 * N1 * tile, dtype=torch.float32, device="cuda")
-        full.out_buffer = full_out.data_ptr()
-        pr, _ = uk.shard_params(full, rank, world, rhs_is_local=True, out_is_local=False)
-        peers = sharding.PeerOutputs(full_out)
-        fused_ms = timed(lambda: uk.mmt4d_peers(pr, peers.ptrs, ws, stream))
-        same = bool(torch.equal(full_out, gathered_full[0]))
-        flag = torch.tensor([1 if same else 0], device="cuda")
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        assert int(flag.item()) == 1, "fused replication and all-gather route disagree"
-        barrier()
-        peers.close()
-        # third route: one multimem.st per tile through an NVLink multicast mapping
-        mc_ms, mc_note = None, None
+    if world > 1 and not args.no_replicated:
         try:
-            mc = sharding.MulticastOutput(M1 * N1 * tile, torch.float32)
-            if mc.multicast_ptr:
-                full.out_buffer = mc.tensor.data_ptr()
-                pm, _ = uk.shard_params(full, rank, world, rhs_is_local=True, out_is_local=False)
-                mc_ms = timed(lambda: uk.mmt4d_multicast(pm, mc.multicast_ptr, ws, stream))
-                ok = torch.tensor([1 if torch.equal(mc.tensor, gathered_full[0]) else 0], device="cuda")
-                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-                assert int(ok.item()) == 1, "multicast route and all-gather route disagree"
-            else:
-                mc_note = "no multicast support reported"
+            from iree_b200 import sharding
+            rep_steps = max(3, min(10, args.steps))
+            tile = M0 * N0
+
+            def timed(fn):
+                fn()
+                barrier()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for _ in range(rep_steps):
+                    fn()
+                b.record(stream)
+                barrier()
+                tt = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device="cuda")
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                return float(tt.item()) / rep_steps
+
+            gathered_full = [None]
+
+            def gather_route():
+                uk.mmt4d(p, stream, ws)
+                gathered_full[0] = sharding.gather_output(out, M1, N1, tile, stream=stream)
+
+            gather_ms = timed(gather_route)
+            full_out = torch.zeros(M1 * N1 * tile, dtype=torch.float32, device="cuda")
+            full.out_buffer = full_out.data_ptr()
+            pr, _ = uk.shard_params(full, rank, world, rhs_is_local=True, out_is_local=False)
+            peers = sharding.PeerOutputs(full_out)
+            fused_ms = timed(lambda: uk.mmt4d_peers(pr, peers.ptrs, ws, stream))
+            same = bool(torch.equal(full_out, gathered_full[0]))
+            flag = torch.tensor([1 if same else 0], device="cuda")
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            assert int(flag.item()) == 1, "fused replication and all-gather route disagree"
+            barrier()
+            peers.close()
+            # third route: one multimem.st per tile through an NVLink multicast mapping
+            mc_ms, mc_note = None, None
+            try:
+                mc = sharding.MulticastOutput(M1 * N1 * tile, torch.float32)
+                if mc.multicast_ptr:
+                    full.out_buffer = mc.tensor.data_ptr()
+                    pm, _ = uk.shard_params(full, rank, world, rhs_is_local=True, out_is_local=False)
+                    mc_ms = timed(lambda: uk.mmt4d_multicast(pm, mc.multicast_ptr, ws, stream))
+                    ok = torch.tensor([1 if torch.equal(mc.tensor, gathered_full[0]) else 0], device="cuda")
+                    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                    assert int(ok.item()) == 1, "multicast route and all-gather route disagree"
+                else:
+                    mc_note = "no multicast support reported"
+            except AssertionError:
+                raise
+            except Exception as e:  # symmetric memory unavailable: the other two routes stand
+                mc_note = repr(e)[:200]
+            barrier()
+            nvlink_bytes = (world - 1) * out.numel() * 4  # leaves each GPU per step
+            replicated = {
+                "gather_route_ms": gather_ms, "fused_peer_store_ms": fused_ms,
+                "fused_tflops": total_flops / (fused_ms * 1e-3) / 1e12,
+                "gather_route_tflops": total_flops / (gather_ms * 1e-3) / 1e12,
+                "nvlink_bytes_out_per_gpu": nvlink_bytes,
+                "fused_nvlink_gbs_per_gpu": nvlink_bytes / fused_ms / 1e6,
+                "fused_multicast_ms": mc_ms, "fused_multicast_note": mc_note,
+                "fused_multicast_tflops": (total_flops / (mc_ms * 1e-3) / 1e12) if mc_ms else None,
+                "results_identical_on_all_ranks": True, "steps": rep_steps,
+            }
+            del gathered_full, full_out
         except AssertionError:
-            raise
-        except Exception as e:  # symmetric memory unavailable: the other two routes stand
-            mc_note = repr(e)[:200]
-        barrier()
-        nvlink_bytes = (world - 1) * out.numel() * 4  # leaves each GPU per step
-        replicated = {
-            "gather_route_ms": gather_ms, "fused_peer_store_ms": fused_ms,
-            "fused_tflops": total_flops / (fused_ms * 1e-3) / 1e12,
-            "gather_route_tflops": total_flops / (gather_ms * 1e-3) / 1e12,
-            "nvlink_bytes_out_per_gpu": nvlink_bytes,
-            "fused_nvlink_gbs_per_gpu": nvlink_bytes / fused_ms / 1e6,
-            "fused_multicast_ms": mc_ms, "fused_multicast_note": mc_note,
-            "fused_multicast_tflops": (total_flops / (mc_ms * 1e-3) / 1e12) if mc_ms else None,
-            "results_identical_on_all_ranks": True, "steps": rep_steps,
-        }
-        del gathered_full, full_out
+            raise  # a wrong result is never swallowed
+        except Exception as e:  # an unavailable extra never blocks the headline line
+            replicated = {"error": repr(e)[:300]}
 
     if rank != 0:
         if world > 1:
