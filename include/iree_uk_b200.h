@@ -238,6 +238,30 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* para
                                               void* workspace, size_t workspace_bytes,
                                               void* cu_stream);
 
+/* Weights prepared once. The tensor-core path re-tiles both operands before every call; when
+ * the RHS is a weight matrix that does not change between calls, its re-tiled form can be
+ * produced once and kept by the caller (the analogue of IREE packing constant weights ahead of
+ * time, compiler/.../ConstEval):
+ *   iree_uk_b200_mmt4d_prepared_rhs_size(params)   bytes of the prepared form (0: not applicable;
+ *       depends on N, K, K0 and the type only — M may differ from call to call),
+ *   iree_uk_b200_mmt4d_prepare_rhs(params, buf, bytes, stream)   fills it from params->rhs_buffer,
+ *   iree_uk_b200_mmt4d_ws_prepared(params, buf, ws, ws_bytes, stream)   the mmt4d itself; only the
+ *       LHS is re-tiled, into `ws` of iree_uk_b200_mmt4d_prepared_workspace_size(params) bytes.
+ * `buf` and `ws` are 256-byte aligned device memory. Results are identical to
+ * iree_uk_b200_mmt4d_ws. The prepared form is valid while the RHS contents, N, K, K0 and the type
+ * stay the same; params->rhs_buffer is not read by iree_uk_b200_mmt4d_ws_prepared. Tensor-core
+ * triples with 16x16 tiles only (not s16u4s32, not the f32 mode). */
+IREE_UK_B200_EXPORT size_t
+iree_uk_b200_mmt4d_prepared_rhs_size(const iree_uk_mmt4d_params_t* params);
+IREE_UK_B200_EXPORT size_t
+iree_uk_b200_mmt4d_prepared_workspace_size(const iree_uk_mmt4d_params_t* params);
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_prepare_rhs(const iree_uk_mmt4d_params_t* params,
+                                                       void* prepared_rhs, size_t prepared_bytes,
+                                                       void* cu_stream);
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws_prepared(const iree_uk_mmt4d_params_t* params,
+                                                       const void* prepared_rhs, void* workspace,
+                                                       size_t workspace_bytes, void* cu_stream);
+
 /* How f32f32f32 with 16x16xK0 tiles is computed when scratch is supplied. The reference adds
  * f32 products in k order; the default here does the same on the CUDA cores. TF32X3 moves the
  * work to the tensor cores: each operand is split into a tf32 part and a remainder and every

@@ -32,6 +32,10 @@ SIGNATURES = {
     "iree_uk_b200_mmt4d_host": (C.c_int, [_P, _P, _sz, _P]),
     "iree_uk_b200_mmt4d_ws_peers": (C.c_int, [_P, _P, C.c_int, _P, _sz, _P]),
     "iree_uk_b200_mmt4d_ws_multicast": (C.c_int, [_P, _P, _P, _sz, _P]),
+    "iree_uk_b200_mmt4d_prepared_rhs_size": (_sz, [_P]),
+    "iree_uk_b200_mmt4d_prepared_workspace_size": (_sz, [_P]),
+    "iree_uk_b200_mmt4d_prepare_rhs": (C.c_int, [_P, _P, _sz, _P]),
+    "iree_uk_b200_mmt4d_ws_prepared": (C.c_int, [_P, _P, _P, _sz, _P]),
     "iree_uk_b200_set_f32_mode": (C.c_int, [C.c_int]),
     "iree_uk_b200_mmt4d_sharded": (C.c_int, [C.c_int, _P, _P, _P, _P, _P, C.c_int]),
     "iree_uk_b200_peer_export": (C.c_int, [_P, _P]),

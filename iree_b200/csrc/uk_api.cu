@@ -215,6 +215,38 @@ int iree_uk_b200_mmt4d_ws_multicast(const iree_uk_mmt4d_params_t* params,
                          static_cast<cudaStream_t>(cu_stream), nullptr, 0, multicast_out_buffer);
 }
 
+size_t iree_uk_b200_mmt4d_prepared_rhs_size(const iree_uk_mmt4d_params_t* params) {
+  if (!params || validate_mmt4d(params)) return 0;
+  return mmt4d_tc_prepared_rhs_size(params);
+}
+
+size_t iree_uk_b200_mmt4d_prepared_workspace_size(const iree_uk_mmt4d_params_t* params) {
+  if (!params || validate_mmt4d(params)) return 0;
+  return mmt4d_tc_prepared_workspace_size(params);
+}
+
+int iree_uk_b200_mmt4d_prepare_rhs(const iree_uk_mmt4d_params_t* params, void* prepared_rhs,
+                                   size_t prepared_bytes, void* cu_stream) {
+  const int rc = validate_mmt4d(params);
+  if (rc) return rc;
+  return launch_mmt4d_tc_prepare_rhs(params, prepared_rhs, prepared_bytes,
+                                     static_cast<cudaStream_t>(cu_stream));
+}
+
+int iree_uk_b200_mmt4d_ws_prepared(const iree_uk_mmt4d_params_t* params, const void* prepared_rhs,
+                                   void* workspace, size_t workspace_bytes, void* cu_stream) {
+  if (!prepared_rhs) return IREE_UK_B200_INVALID_ARGUMENT;
+  Mmt4dPath path;
+  const int rc = select_mmt4d(params, true, &path);
+  if (rc) return rc;
+  if (path == Mmt4dPath::None) return IREE_UK_B200_OK;
+  if (path != Mmt4dPath::TcRetile || !mmt4d_tc_prepared_rhs_size(params) ||
+      (params->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
+    return IREE_UK_B200_UNSUPPORTED;
+  return launch_mmt4d_tc(params, workspace, workspace_bytes, kTcVariantDefault,
+                         static_cast<cudaStream_t>(cu_stream), nullptr, 0, nullptr, prepared_rhs);
+}
+
 int iree_uk_b200_mmt4d_sharded(int n_gpus, const int* device_ids,
                                const iree_uk_mmt4d_params_t* per_gpu, void* const* workspaces,
                                const size_t* workspace_bytes, void* const* cu_streams,

@@ -58,7 +58,14 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 // on every GPU of a group; tiles are then stored once, through multimem.st.
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream, const void* const* peer_out_buffers = nullptr,
-                    int num_peers = 0, const void* multicast_out = nullptr);
+                    int num_peers = 0, const void* multicast_out = nullptr,
+                    const void* prepared_rhs = nullptr);
+// `prepared_rhs`: the RHS already re-tiled by launch_mmt4d_tc_prepare_rhs (weights prepared
+// once); the call then re-tiles only the LHS and needs mmt4d_tc_prepared_workspace_size bytes.
+size_t mmt4d_tc_prepared_rhs_size(const iree_uk_mmt4d_params_t* p);
+size_t mmt4d_tc_prepared_workspace_size(const iree_uk_mmt4d_params_t* p);
+int launch_mmt4d_tc_prepare_rhs(const iree_uk_mmt4d_params_t* p, void* prepared, size_t bytes,
+                                cudaStream_t stream);
 // Row-major matmul on the tensor-core kernels (lhs [M][K], rhs [K][N], out [M][N] 32-bit);
 // pitches in bytes, out_stride0 in elements.
 size_t matmul_workspace_size(uint32_t flags, int64_t M, int64_t N, int64_t K);

@@ -2054,6 +2054,40 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
   return ti.triple ? 2 * one : one;  // f32: a hi and a lo plane of both operands
 }
 
+// Re-tiled RHS kept by the caller across calls (weights): its size, the scratch a call then
+// still needs (the LHS part), and the pre-pass that fills it.
+size_t mmt4d_tc_prepared_rhs_size(const iree_uk_mmt4d_params_t* p) {
+  TypeInfo ti;
+  if (!tc_type_info(p->flags, &ti) || ti.triple) return 0;
+  if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->N < 1) return 0;
+  const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
+  return size_t(round_up(p->N * 16 * pitch, 1024));
+}
+size_t mmt4d_tc_prepared_workspace_size(const iree_uk_mmt4d_params_t* p) {
+  TypeInfo ti;
+  if (!tc_type_info(p->flags, &ti) || ti.triple) return 0;
+  if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1) return 0;
+  const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
+  return size_t(round_up(p->M * 16 * pitch, 1024));
+}
+int launch_mmt4d_tc_prepare_rhs(const iree_uk_mmt4d_params_t* p, void* prepared, size_t bytes,
+                                cudaStream_t stream) {
+  TypeInfo ti;
+  if (!tc_type_info(p->flags, &ti) || ti.triple) return IREE_UK_B200_UNSUPPORTED;
+  const size_t need = mmt4d_tc_prepared_rhs_size(p);
+  if (!need) return IREE_UK_B200_UNSUPPORTED;
+  if (!prepared || bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset * ti.es);
+  if ((reinterpret_cast<uintptr_t>(prepared) & 255) || (rhs & 15) || (p->rhs_stride0 * ti.es) % 16)
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  const int G = p->K0 * ti.es;
+  if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return IREE_UK_B200_UNSUPPORTED;
+  const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
+  return launch_retile(nullptr, 0, nullptr, 0, reinterpret_cast<const char*>(rhs),
+                       p->rhs_stride0 * ti.es, static_cast<char*>(prepared), p->N, pitch, p->K, G,
+                       stream);
+}
+
 namespace {
 // The two-CTA kernel works on 256-row tiles with at most 74 CTA pairs in flight; it pays once
 // there are enough 256 x 128 tiles to occupy every pair.
@@ -2065,7 +2099,7 @@ bool pair_kernel_pays(const iree_uk_mmt4d_params_t* p) {
 
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream, const void* const* peer_out_buffers, int num_peers,
-                    const void* multicast_out) {
+                    const void* multicast_out, const void* prepared_rhs) {
   if (multicast_out && num_peers) return IREE_UK_B200_INVALID_ARGUMENT;
   if (num_peers < 0 || num_peers > IREE_UK_B200_MAX_PEERS || (num_peers && !peer_out_buffers))
     return IREE_UK_B200_INVALID_ARGUMENT;
@@ -2105,9 +2139,11 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   if (variant == 5 || variant == 6) {
     // K-major operands from the re-tiled scratch: the one-CTA kernel (6) on 128 x bn tiles, or
     // the two-CTA kernel (5) on 256 x bn tiles per CTA pair.
-    const size_t need = mmt4d_tc_workspace_size(p);
+    if (prepared_rhs && ti.triple) return IREE_UK_B200_UNSUPPORTED;
+    const size_t need = prepared_rhs ? mmt4d_tc_prepared_workspace_size(p) : mmt4d_tc_workspace_size(p);
     if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
-    if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(prepared_rhs)) & 255)
+      return IREE_UK_B200_INVALID_ARGUMENT;
     pair = variant == 5;
     if (pair) {
       pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0];
@@ -2118,10 +2154,12 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     const int64_t pitch = round_up(kelems * ti.es, 128);
     const int64_t a_bytes = round_up(p->M * 16 * pitch, 1024), b_bytes = round_up(p->N * 16 * pitch, 1024);
     char* ws_a = static_cast<char*>(ws);
-    char* ws_b = ws_a + a_bytes;
+    // A prepared RHS is this pre-pass's output kept by the caller: only the LHS is re-tiled.
+    char* ws_b = prepared_rhs ? const_cast<char*>(static_cast<const char*>(prepared_rhs)) : ws_a + a_bytes;
     const int G = p->K0 * ti.es;
     const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, p->M, rhs,
-                                 p->rhs_stride0 * ti.es, ws_b, p->N, pitch, p->K, G, stream);
+                                 p->rhs_stride0 * ti.es, ws_b, prepared_rhs ? 0 : p->N, pitch,
+                                 p->K, G, stream);
     if (rc) return rc;
     const int64_t plane_bytes = a_bytes + b_bytes;  // [A hi | B hi][A lo | B lo]
     if (ti.triple) {

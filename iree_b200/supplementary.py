@@ -259,6 +259,23 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         mm, mn, mk = custom_matmul
         res["matmul_rowmajor_bf16_custom_%dx%dx%d" % (mm, mn, mk)] = _matmul_rowmajor_case(
             mm, mn, mk, bf16_peak)
+    # the headline problem with the weights prepared once (RHS re-tiled outside the call)
+    if want("mmt4d_bf16_prepared_rhs_8192x28672x8192"):
+        M1, N1, K1 = 512, 1792, 4096
+        lhs = torch.randn(M1 * K1 * 32, device="cuda").to(torch.bfloat16)
+        rhs = (torch.randn(N1 * K1 * 32, device="cuda") * 0.02).to(torch.bfloat16)
+        out = torch.empty(M1 * N1 * 256, device="cuda")
+        p = _mmt4d_params(abi.MMT4D_BF16BF16F32, M1, N1, K1, 16, 16, 2, lhs, rhs, out)
+        prepared = torch.empty(uk.mmt4d_prepared_rhs_size(p), dtype=torch.uint8, device="cuda")
+        ws = torch.empty(uk.mmt4d_prepared_workspace_size(p), dtype=torch.uint8, device="cuda")
+        prep_ms, _ = _time(lambda: uk.mmt4d_prepare_rhs(p, prepared))
+        med, best = _time(lambda: uk.mmt4d_prepared(p, prepared, ws))
+        ops = 2.0 * 8192 * 28672 * 8192
+        res["mmt4d_bf16_prepared_rhs_8192x28672x8192"] = {
+            "ms": med, "ms_best": best, "tops": ops / med / 1e9, "prepare_rhs_once_ms": prep_ms,
+            "frac_of_bf16_burst": ops / med / 1e9 / bf16_peak}
+        del lhs, rhs, out, prepared, ws
+
     # row-major matmul at the headline dimensions: the fused entry point beside the chain
     # pack LHS, pack RHS (TRANSPOSE_INNER | TRANSPOSE_OUTER), mmt4d, unpack run on this library
     if want("matmul_rowmajor_bf16_8192x28672x8192"):

@@ -100,6 +100,33 @@ def mmt4d_sharded(device_ids, per_gpu_params, workspaces, streams, replicate_out
                                           1 if replicate_output else 0), "mmt4d_sharded")
 
 
+def mmt4d_prepared_rhs_size(params):
+    """Bytes of the re-tiled RHS a caller may keep across calls (0: not applicable)."""
+    return int(lib.iree_uk_b200_mmt4d_prepared_rhs_size(C.addressof(params)))
+
+
+def mmt4d_prepared_workspace_size(params):
+    """Scratch bytes ``mmt4d_prepared`` needs (the LHS part only)."""
+    return int(lib.iree_uk_b200_mmt4d_prepared_workspace_size(C.addressof(params)))
+
+
+def mmt4d_prepare_rhs(params, prepared, stream=None):
+    """Re-tiles ``params.rhs_buffer`` once into ``prepared`` (a torch uint8 CUDA tensor of at
+    least ``mmt4d_prepared_rhs_size(params)`` bytes) for later ``mmt4d_prepared`` calls."""
+    _check(lib.iree_uk_b200_mmt4d_prepare_rhs(C.addressof(params), prepared.data_ptr(),
+                                              prepared.numel() * prepared.element_size(),
+                                              _stream_handle(stream)), "mmt4d_prepare_rhs")
+
+
+def mmt4d_prepared(params, prepared, workspace, stream=None):
+    """mmt4d with the RHS already re-tiled (weights prepared once): only the LHS is re-tiled
+    per call. Same results as ``mmt4d(..., workspace=...)``."""
+    _check(lib.iree_uk_b200_mmt4d_ws_prepared(C.addressof(params), prepared.data_ptr(),
+                                              workspace.data_ptr(),
+                                              workspace.numel() * workspace.element_size(),
+                                              _stream_handle(stream)), "mmt4d_prepared")
+
+
 def mmt4d_multicast(params, multicast_out_ptr, workspace, stream=None):
     """mmt4d whose output tiles are stored once through an NVLink multicast mapping and
     replicated by the switch into every GPU's buffer; ``multicast_out_ptr`` is the address in

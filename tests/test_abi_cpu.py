@@ -79,19 +79,32 @@ def test_mmt4d_early_outs_and_paths():
     assert uk.mmt4d_path(_mmt4d(N=0)) == abi.PATH_NONE
     assert uk.mmt4d_path(_mmt4d(abi.MMT4D_S8S8S32 | abi.MMT4D_ACCUMULATE, K=0)) == abi.PATH_NONE
     assert uk.mmt4d_path(_mmt4d(K=0)) == abi.PATH_ZERO_FILL
-    # without a workspace the tensor-core path is not taken
-    assert uk.mmt4d_path(_mmt4d(), with_workspace=False) == abi.PATH_GENERIC
-    # ... except for 16-bit K0 = 1 operands, which TMA can stage as they are
+    # with a workspace: the re-tile pre-pass and the TMA-fed tensor-core kernels
+    assert uk.mmt4d_path(_mmt4d(), with_workspace=True) == abi.PATH_TCGEN05_RETILE
+    # without one the tensor-core triples still run on the tensor cores, operands read as they
+    # lie (TMA staging for 16-bit K0 = 1, the scratch-free kernel for everything else)
+    assert uk.mmt4d_path(_mmt4d(), with_workspace=False) == abi.PATH_TCGEN05
     assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F16F16F32, K0=1), with_workspace=False) == abi.PATH_TCGEN05
-    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_BF16BF16F32, K0=2), with_workspace=False) == abi.PATH_GENERIC
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_BF16BF16F32, K0=2), with_workspace=False) == abi.PATH_TCGEN05
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F32F32F32, K0=1), with_workspace=False) == abi.PATH_GENERIC
     # odd tile shapes and misaligned operands go to the generic kernel
     assert uk.mmt4d_path(_mmt4d(M0=9, N0=6, K0=3)) == abi.PATH_GENERIC
     p = _mmt4d()
     p.lhs_offset = 1
     assert uk.mmt4d_path(p) == abi.PATH_GENERIC
     assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F32F32F32, K0=1)) == abi.PATH_GENERIC
-    # 16-bit-output triples run on the generic kernel
+    # 16-bit-output triples: generic kernel when every step is rounded, tensor cores when only
+    # the final sum is (SKIP_INTERMEDIATE_ROUNDINGS)
     assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F16F16F16, K0=1)) == abi.PATH_GENERIC
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F16F16F16 | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS,
+                                K0=1)) == abi.PATH_TCGEN05_RETILE
+    # f32: CUDA cores unless the process opts into the tf32 x 3 mode
+    prev = uk.set_f32_mode(uk.F32_MODE_TF32X3)
+    try:
+        assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F32F32F32, K0=1)) == abi.PATH_TCGEN05_RETILE
+    finally:
+        uk.set_f32_mode(prev)
+    assert uk.mmt4d_path(_mmt4d(abi.MMT4D_F32F32F32, K0=1)) == abi.PATH_GENERIC
     assert uk.mmt4d_path(_mmt4d(abi.MMT4D_BF16BF16BF16 | abi.MMT4D_SKIP_INTERMEDIATE_ROUNDINGS,
                                 K=0)) == abi.PATH_ZERO_FILL
 
@@ -199,3 +212,27 @@ def test_shard_params_partition_n():
 def test_status_strings():
     assert lib.iree_uk_b200_status_string(0) == b"OK"
     assert lib.iree_uk_b200_status_string(abi.DEVICE_TIMEOUT) == b"DEVICE_TIMEOUT"
+
+
+def test_scratch_sizes_are_consistent():
+    """Sizes depend on the shape and type only: the ordinary scratch is the LHS part plus the
+    RHS part that a caller may instead prepare once; f32 in its tensor-core mode needs two
+    planes of each; triples without a tensor-core path need none."""
+    p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
+    whole = uk.mmt4d_workspace_size(p)
+    assert whole == (512 + 1792) * 16 * 8192 * 2          # the headline problem: 576 MiB
+    assert uk.mmt4d_prepared_rhs_size(p) + uk.mmt4d_prepared_workspace_size(p) == whole
+    assert uk.mmt4d_prepared_rhs_size(p) == 1792 * 16 * 8192 * 2
+    q = _mmt4d(abi.MMT4D_BF16BF16F32, M=7, N=1792, K=4096)   # another M, the same weights
+    assert uk.mmt4d_prepared_rhs_size(q) == uk.mmt4d_prepared_rhs_size(p)
+    assert uk.mmt4d_workspace_size(_mmt4d(M0=8, N0=8)) == 0
+    s = _mmt4d(abi.MMT4D_S16U4S32, M=64, N=4, K=16, M0=1, N0=32, K0=8)
+    assert uk.mmt4d_workspace_size(s) > 0 and uk.mmt4d_prepared_rhs_size(s) == 0
+    f = _mmt4d(abi.MMT4D_F32F32F32, K0=1)
+    assert uk.mmt4d_workspace_size(f) == 0
+    prev = uk.set_f32_mode(uk.F32_MODE_TF32X3)
+    try:
+        assert uk.mmt4d_workspace_size(f) == 2 * (4 + 4) * 16 * 128
+        assert uk.mmt4d_prepared_rhs_size(f) == 0
+    finally:
+        uk.set_f32_mode(prev)

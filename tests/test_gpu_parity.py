@@ -361,6 +361,42 @@ def test_mmt4d_scratch_free_kernel_normal_values():
     assert cases.rel_frobenius(got.view(np.float32), want.view(np.float32)) <= 1e-3
 
 
+@pytest.mark.parametrize("t,K0", [(abi.MMT4D_S8S8S32, 2), (abi.MMT4D_BF16BF16F32, 2),
+                                  (abi.MMT4D_F16F16F32, 1)], ids=["s8", "bf16", "f16"])
+def test_mmt4d_with_prepared_rhs(t, K0):
+    """Weights re-tiled once and kept: the prepared form serves calls with different LHS row
+    counts, and every result is identical to the ordinary workspace call (and the oracle)."""
+    import torch
+    from iree_b200 import ukernel as uk
+    N, K = 40, 70
+    prepared = None
+    for M, acc in [(24, 0), (3, 1), (160, 0)]:
+        case = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, acc, seed=41, mode="exact", loose=False)
+        if prepared is None:
+            rhs_host = case.rhs  # the weights: the same for every M below
+        case.rhs = rhs_host
+        want = G.oracle_mmt4d(case)
+        lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
+        p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+        if prepared is None:
+            prepared = torch.empty(uk.mmt4d_prepared_rhs_size(p), dtype=torch.uint8, device="cuda")
+            assert prepared.numel() > 0
+            uk.mmt4d_prepare_rhs(p, prepared)
+        ws = torch.empty(uk.mmt4d_prepared_workspace_size(p), dtype=torch.uint8, device="cuda")
+        assert 0 < ws.numel() < uk.mmt4d_workspace_size(p)
+        p.rhs_buffer = 0  # not read once the RHS is prepared
+        uk.mmt4d_prepared(p, prepared, ws)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want), (M, acc)
+    G.check_device_status()
+    # not applicable: s16u4s32, and an undersized scratch
+    c = cases.Mmt4dCase(abi.MMT4D_S16U4S32, 1, 32, 8, 64, 4, 16, 0, seed=1, mode="normal", loose=False)
+    assert uk.mmt4d_prepared_rhs_size(c.params(0, 0, 0)) == 0
+    with pytest.raises(uk.UkernelError) as e:
+        uk.mmt4d_prepared(p, prepared, ws[:256])
+    assert e.value.status == abi.WORKSPACE_TOO_SMALL
+
+
 def test_concurrent_host_threads_on_their_own_streams():
     """The library keeps per-device caches behind mutexes and no per-call state: two host
     threads enqueue different problems on their own streams with their own scratch at the
