@@ -37,7 +37,7 @@ def _newer(target, deps):
 def build(verbose=False, ptxas_info=False):
     """Compile and link the library; returns its path."""
     os.makedirs(OBJ_DIR, exist_ok=True)
-    headers = glob.glob(os.path.join(CSRC, "*.h")) + \
+    headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + \
         [os.path.join(_HERE, "..", "include", "iree_uk_b200.h")]
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cc")))
     objs = []
