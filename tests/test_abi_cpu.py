@@ -236,3 +236,26 @@ def test_scratch_sizes_are_consistent():
         assert uk.mmt4d_prepared_rhs_size(f) == 0
     finally:
         uk.set_f32_mode(prev)
+
+
+def test_header_compiles_as_c_and_cxx_and_struct_sizes_match_the_reference(tmp_path):
+    """include/iree_uk_b200.h is plain C usable from C++ (the reference's own common.h refuses
+    C++, ukernel/common.h:10-12), and a C program sees the reference's struct sizes: 120 / 136 /
+    128 bytes (mmt4d_internal.h:14-32, pack_internal.h:12-30, unpack_internal.h:12-29)."""
+    import shutil
+    import subprocess
+    header = os.path.join(ROOT, "include", "iree_uk_b200.h")
+    if not shutil.which("gcc") or not shutil.which("g++"):
+        pytest.skip("no host compiler")
+    subprocess.check_call(["gcc", "-std=c11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", header])
+    subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", header])
+    src = tmp_path / "sizes.c"
+    src.write_text('#include <stdio.h>\n#include "iree_uk_b200.h"\n'
+                   'int main(void) { printf("%zu %zu %zu %zu\\n", sizeof(iree_uk_mmt4d_params_t), '
+                   'sizeof(iree_uk_pack_params_t), sizeof(iree_uk_unpack_params_t), '
+                   'sizeof(iree_uk_b200_matmul_params_t)); return 0; }\n')
+    exe = tmp_path / "sizes"
+    subprocess.check_call(["gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)])
+    out = subprocess.check_output([str(exe)], text=True).split()
+    assert out[:3] == ["120", "136", "128"]
+    assert int(out[3]) == C.sizeof(abi.MatmulParams)
