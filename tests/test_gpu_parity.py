@@ -439,11 +439,13 @@ def test_concurrent_host_threads_on_their_own_streams():
     G.check_device_status()
 
 
-def test_bounded_waits_report_a_timeout_instead_of_hanging():
-    """Failure detection without faulting the GPU: a test hook makes the TMA producer never fill
-    a stage, so the MMA warp's wait on the full barrier runs out (about a second); the kernel
-    must record the timeout, return, leave the context usable, and the next call must be
-    correct. Runs in a child process because the hook is read from the environment."""
+@pytest.mark.parametrize("use_ws", [True, False], ids=["tma_kernel", "scratch_free_kernel"])
+def test_bounded_waits_report_a_timeout_instead_of_hanging(use_ws):
+    """Failure detection without faulting the GPU: a test hook makes the producer (TMA, or the
+    producer warps of the scratch-free kernel) never fill a stage, so the MMA warp's wait on the
+    full barrier runs out (about a second); the kernel must record the timeout, return, leave
+    the context usable, and the next call must be correct. Runs in a child process because the
+    hook is read from the environment."""
     import subprocess
     import sys
     code = r"""
@@ -451,6 +453,7 @@ import os, sys
 os.environ["IREE_UK_B200_DEBUG"] = "1"
 os.environ["IREE_UK_B200_DEBUG_FLAGS"] = "8"
 sys.path.insert(0, %r)
+USE_WS = %r
 import numpy as np, torch
 import oracle
 from oracle import cases
@@ -459,8 +462,8 @@ case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 64, 0, seed=5, loose
 def run():
     lhs, rhs, out = (torch.from_numpy(x).cuda() for x in (case.lhs, case.rhs, case.out_init))
     p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
-    ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda")
-    assert uk.mmt4d_path(p, True) == abi.PATH_TCGEN05_RETILE
+    ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda") if USE_WS else None
+    assert uk.mmt4d_path(p, USE_WS) == (abi.PATH_TCGEN05_RETILE if USE_WS else abi.PATH_TCGEN05)
     uk.mmt4d(p, workspace=ws)
     st, detail = uk.device_status()
     return st, detail, out.cpu().numpy()
@@ -472,6 +475,6 @@ assert st == abi.OK and detail == 0, (st, detail)
 want = case.out_init.copy(); oracle.mmt4d(case.params(case.lhs, case.rhs, want))
 assert np.array_equal(got, want)
 print("TIMEOUT_REPORTED_AND_RECOVERED")
-""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+""" % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), use_ws)
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
     assert "TIMEOUT_REPORTED_AND_RECOVERED" in r.stdout, r.stdout + r.stderr
