@@ -238,6 +238,19 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* para
                                               void* workspace, size_t workspace_bytes,
                                               void* cu_stream);
 
+/* mmt4d followed by the unpack of its result, as one call: the tiles never exist in memory, the
+ * epilogue writes the row-major matrix that iree_uk_unpack (ukernel/unpack.c:259-285, type
+ * I32I32 / F32F32, no transposes) would produce from them. params->out_buffer, out_offset and
+ * out_stride0 describe that matrix ([out_size0][out_size1], out_stride0 = its row pitch in
+ * elements, out_size0 <= M * M0, out_size1 <= N * N0; elements outside it are never written,
+ * exactly as unpack does). With ACCUMULATE the matrix holds the accumulator on entry (what
+ * packing it into tiles first would feed mmt4d). Tensor-core triples with a 32-bit output and
+ * 16x16 tiles only; scratch as for iree_uk_b200_mmt4d_ws. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws_unpacked(const iree_uk_mmt4d_params_t* params,
+                                                       iree_uk_index_t out_size0,
+                                                       iree_uk_index_t out_size1, void* workspace,
+                                                       size_t workspace_bytes, void* cu_stream);
+
 /* Weights prepared once. The tensor-core path re-tiles both operands before every call; when
  * the RHS is a weight matrix that does not change between calls, its re-tiled form can be
  * produced once and kept by the caller (the analogue of IREE packing constant weights ahead of

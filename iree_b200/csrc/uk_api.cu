@@ -215,6 +215,35 @@ int iree_uk_b200_mmt4d_ws_multicast(const iree_uk_mmt4d_params_t* params,
                          static_cast<cudaStream_t>(cu_stream), nullptr, 0, multicast_out_buffer);
 }
 
+int iree_uk_b200_mmt4d_ws_unpacked(const iree_uk_mmt4d_params_t* params, iree_uk_index_t out_size0,
+                                   iree_uk_index_t out_size1, void* workspace,
+                                   size_t workspace_bytes, void* cu_stream) {
+  const int rc = validate_mmt4d(params);
+  if (rc) return rc;
+  const iree_uk_mmt4d_params_t& p = *params;
+  if (out_size0 < 0 || out_size1 < 0 || out_size0 > p.M * p.M0 || out_size1 > p.N * p.N0 ||
+      p.out_stride0 < out_size1)
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  const bool acc = (p.flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) != 0;
+  if (out_size0 == 0 || out_size1 == 0 || (p.K == 0 && acc)) return IREE_UK_B200_OK;
+  const uint32_t type = p.flags & IREE_UK_FLAG_MMT4D_TYPE_MASK;
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 || !mmt4d_tc_operands_eligible(params)) {
+    if (p.K == 0 || p.K0 == 0) {
+      // an empty reduction without ACCUMULATE: zeros, for any type with a 32-bit output
+      Mmt4dTypes t;
+      if (!mmt4d_types(p.flags, &t) || elem_bits(t.out) != 32) return IREE_UK_B200_UNSUPPORTED;
+      return cudaMemset2DAsync(static_cast<char*>(p.out_buffer) + p.out_offset * 4,
+                               size_t(p.out_stride0) * 4, 0, size_t(out_size1) * 4,
+                               size_t(out_size0), static_cast<cudaStream_t>(cu_stream)) == cudaSuccess
+                 ? IREE_UK_B200_OK : IREE_UK_B200_CUDA_ERROR;
+    }
+    return IREE_UK_B200_UNSUPPORTED;
+  }
+  const RowMajorOut rm = {out_size0, out_size1};
+  return launch_mmt4d_tc(params, workspace, workspace_bytes, kTcVariantDefault,
+                         static_cast<cudaStream_t>(cu_stream), nullptr, 0, nullptr, nullptr, &rm);
+}
+
 size_t iree_uk_b200_mmt4d_prepared_rhs_size(const iree_uk_mmt4d_params_t* params) {
   if (!params || validate_mmt4d(params)) return 0;
   return mmt4d_tc_prepared_rhs_size(params);

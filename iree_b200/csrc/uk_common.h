@@ -47,6 +47,12 @@ int launch_mmt4d_zero_fill(const iree_uk_mmt4d_params_t* p, cudaStream_t stream)
 int launch_mmt4d_gemv_s16u4(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
 bool mmt4d_gemv_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
 
+// Output of a tensor-core mmt4d written as a row-major rows x cols matrix (the unpack folded
+// into the epilogue); p->out_buffer / out_offset / out_stride0 then describe that matrix.
+struct RowMajorOut {
+  int64_t rows, cols;
+};
+bool mmt4d_tc_operands_eligible(const iree_uk_mmt4d_params_t* p);
 // Tensor-core path. `variant` selects the operand staging layout (see uk_mmt4d_tc.cu).
 bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p);
 // s16u4s32 1x32x8 with enough rows to fill tensor-core tiles (two byte planes x u8 weights).
@@ -59,7 +65,7 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream, const void* const* peer_out_buffers = nullptr,
                     int num_peers = 0, const void* multicast_out = nullptr,
-                    const void* prepared_rhs = nullptr);
+                    const void* prepared_rhs = nullptr, const RowMajorOut* row_major_out = nullptr);
 // `prepared_rhs`: the RHS already re-tiled by launch_mmt4d_tc_prepare_rhs (weights prepared
 // once); the call then re-tiles only the LHS and needs mmt4d_tc_prepared_workspace_size bytes.
 size_t mmt4d_tc_prepared_rhs_size(const iree_uk_mmt4d_params_t* p);

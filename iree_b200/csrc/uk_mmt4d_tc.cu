@@ -403,7 +403,9 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
 
 }  // namespace
 
-bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
+// Operand side of the tensor-core path's conditions: a tensor-core triple, 16x16 tiles, a K0
+// whose granule the re-tile handles, 16-byte aligned operand panels.
+bool mmt4d_tc_operands_eligible(const iree_uk_mmt4d_params_t* p) {
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti)) return false;
   if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1 || p->N < 1) return false;
@@ -411,13 +413,18 @@ bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
   if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return false;
   const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * ti.es);
   const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset * ti.es);
-  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * ti.out_es);
-  if ((lhs | rhs | out) & 15) return false;
-  if ((p->lhs_stride0 * ti.es) % 16 || (p->rhs_stride0 * ti.es) % 16 ||
-      (p->out_stride0 * ti.out_es) % 16)
-    return false;
+  if ((lhs | rhs) & 15) return false;
+  if ((p->lhs_stride0 * ti.es) % 16 || (p->rhs_stride0 * ti.es) % 16) return false;
   if ((p->M + 7) / 8 * ((p->N + 3) / 4) > 0x3FFFFFFF) return false;
   return true;
+}
+
+bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p) {
+  TypeInfo ti;
+  if (!mmt4d_tc_operands_eligible(p) || !tc_type_info(p->flags, &ti)) return false;
+  // tiled output: every 16-value tile row is accessed with 16-byte vectors
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * ti.out_es);
+  return (out & 15) == 0 && (p->out_stride0 * ti.out_es) % 16 == 0;
 }
 
 bool mmt4d_tc_direct_eligible(const iree_uk_mmt4d_params_t* p) {
@@ -484,8 +491,9 @@ bool pair_kernel_pays(const iree_uk_mmt4d_params_t* p) {
 
 int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
                     cudaStream_t stream, const void* const* peer_out_buffers, int num_peers,
-                    const void* multicast_out, const void* prepared_rhs) {
+                    const void* multicast_out, const void* prepared_rhs, const RowMajorOut* rm) {
   if (multicast_out && num_peers) return IREE_UK_B200_INVALID_ARGUMENT;
+  if (rm && (num_peers || multicast_out)) return IREE_UK_B200_INVALID_ARGUMENT;
   if (num_peers < 0 || num_peers > IREE_UK_B200_MAX_PEERS || (num_peers && !peer_out_buffers))
     return IREE_UK_B200_INVALID_ARGUMENT;
   // Peer copies exist for the plain tiled epilogue only.
@@ -494,8 +502,12 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
     return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
   TypeInfo ti;
-  if (!tc_type_info(p->flags, &ti) || !mmt4d_tc_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
-  if ((num_peers || multicast_out) && ti.out_es != 4) return IREE_UK_B200_UNSUPPORTED;  // 32-bit tiles only
+  if (!tc_type_info(p->flags, &ti) || !(rm ? mmt4d_tc_operands_eligible(p) : mmt4d_tc_eligible(p)))
+    return IREE_UK_B200_UNSUPPORTED;
+  if ((num_peers || multicast_out || rm) && ti.out_es != 4) return IREE_UK_B200_UNSUPPORTED;  // 32-bit only
+  if (rm && (rm->rows < 0 || rm->cols < 0 || rm->rows > p->M * 16 || rm->cols > p->N * 16 ||
+             (reinterpret_cast<uintptr_t>(p->out_buffer) & 3)))
+    return IREE_UK_B200_INVALID_ARGUMENT;
   uint32_t* status = device_status_word();
   const DeviceInfo* di = device_info();
   if (!status || !di) return IREE_UK_B200_CUDA_ERROR;
@@ -629,6 +641,12 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   P.out_is_int = ti.is_int ? 1 : 0;
   P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * ti.out_es) % 32 == 0) ? 1 : 0;
   P.out16 = ti.out_es == 2 ? (ti.fmt == 0u ? 1 : 2) : 0;
+  if (rm) {  // the unpack folded into the epilogue: rows x cols of a row-major matrix
+    P.out_row_major = 1;
+    P.rows = rm->rows;
+    P.cols = rm->cols;
+    P.out_vec16 = ((reinterpret_cast<uintptr_t>(P.out) & 15) == 0 && (p->out_stride0 * 4) % 16 == 0) ? 1 : 0;
+  }
   if (multicast_out) {
     P.use_multicast = 1;
     P.mc_delta = int64_t(reinterpret_cast<intptr_t>(multicast_out) -

@@ -100,6 +100,15 @@ def mmt4d_sharded(device_ids, per_gpu_params, workspaces, streams, replicate_out
                                           1 if replicate_output else 0), "mmt4d_sharded")
 
 
+def mmt4d_unpacked(params, out_size0, out_size1, workspace, stream=None):
+    """mmt4d whose epilogue writes the row-major ``out_size0 x out_size1`` matrix that
+    ``unpack`` would produce from the output tiles; ``params.out_*`` describe that matrix."""
+    _check(lib.iree_uk_b200_mmt4d_ws_unpacked(C.addressof(params), out_size0, out_size1,
+                                              workspace.data_ptr(),
+                                              workspace.numel() * workspace.element_size(),
+                                              _stream_handle(stream)), "mmt4d_unpacked")
+
+
 def mmt4d_prepared_rhs_size(params):
     """Bytes of the re-tiled RHS a caller may keep across calls (0: not applicable)."""
     return int(lib.iree_uk_b200_mmt4d_prepared_rhs_size(C.addressof(params)))

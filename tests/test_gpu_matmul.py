@@ -8,6 +8,8 @@ import oracle
 from iree_b200 import abi
 from oracle import cases
 
+import gpu_util as G
+
 pytestmark = pytest.mark.gpu
 
 FLOAT_TOL = 1e-3  # relative Frobenius error allowed for the f16 / bf16 triples
@@ -185,3 +187,70 @@ def test_matmul_column_shards_equal_the_whole():
     torch.cuda.synchronize()
     assert uk.device_status() == (0, 0)
     assert np.array_equal(out.cpu().numpy(), whole)
+
+
+@pytest.mark.parametrize("t,K0", [(abi.MMT4D_S8S8S32, 2), (abi.MMT4D_BF16BF16F32, 2)], ids=["s8", "bf16"])
+@pytest.mark.parametrize("spec", [
+    # M tiles, N tiles, K tiles, rows, cols, row pad, out offset
+    (9, 17, 33, 9 * 16, 17 * 16, 0, 0),        # whole tiles, aligned: vector stores
+    (9, 17, 33, 9 * 16 - 5, 17 * 16 - 3, 0, 0),  # ragged: the last tiles are cut
+    (20, 24, 5, 20 * 16 - 15, 24 * 16 - 1, 7, 3),  # odd pitch and base: element stores
+    (160, 64, 9, 160 * 16, 64 * 16 - 8, 8, 4),  # two-CTA kernel
+], ids=["whole", "ragged", "odd_layout", "pair"])
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_with_unpack_folded_into_the_epilogue(t, K0, spec, accumulate):
+    """iree_uk_b200_mmt4d_ws_unpacked against the reference's own sequence on the CPU oracle:
+    (pack the accumulator,) mmt4d into tiles, unpack the tiles into the row-major matrix."""
+    import torch
+    from iree_b200 import ukernel as uk
+    M, N, K, rows, cols, pad, off = spec
+    is_int = t == abi.MMT4D_S8S8S32
+    case = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, 0, seed=33, mode="exact" if is_int else "normal",
+                           loose=False)
+    out_dtype = np.int32 if is_int else np.float32
+    rng = np.random.default_rng(3)
+    acc = (rng.integers(-1000, 1000, (rows, cols)).astype(np.int32) if is_int
+           else rng.standard_normal((rows, cols), dtype=np.float32))
+    # oracle: tiles <- pack(acc) when accumulating; mmt4d; unpack
+    tiles = np.zeros(M * N * 256, dtype=out_dtype)
+    if accumulate:
+        pp = abi.PackParams()
+        pp.in_buffer, pp.out_buffer = acc.ctypes.data, tiles.ctypes.data
+        pp.in_size0, pp.in_size1, pp.in_stride0, pp.in_stride1 = rows, cols, cols, 1
+        pp.out_size0, pp.out_size1, pp.out_size2, pp.out_size3 = M, N, 16, 16
+        pp.out_stride1, pp.out_stride0 = 256, N * 256
+        pp.flags = abi.PACK_I32I32 if is_int else abi.PACK_F32F32
+        oracle.pack(pp)
+    q = case.params(case.lhs, case.rhs, tiles)
+    q.out_offset, q.out_stride0 = 0, N * 256
+    q.flags = t | (abi.MMT4D_ACCUMULATE if accumulate else 0)
+    oracle.mmt4d(q)
+    want = np.zeros((rows, cols), dtype=out_dtype)
+    u = abi.UnpackParams()
+    u.in_buffer, u.out_buffer = tiles.ctypes.data, want.ctypes.data
+    u.in_size0, u.in_size1, u.in_size2, u.in_size3 = M, N, 16, 16
+    u.in_stride1, u.in_stride0 = 256, N * 256
+    u.out_size0, u.out_size1, u.out_stride0, u.out_stride1 = rows, cols, cols, 1
+    u.flags = abi.UNPACK_I32I32 if is_int else abi.UNPACK_F32F32
+    oracle.unpack(u)
+    # device: row-major output embedded in a larger buffer
+    pitch = cols + pad
+    host = np.full(off + rows * pitch + 5, 55, dtype=out_dtype)
+    view = host[off:off + rows * pitch].reshape(rows, pitch)
+    view[:, :cols] = acc if accumulate else 77
+    init = host.copy()
+    lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), torch.from_numpy(host).cuda()
+    p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+    p.out_offset, p.out_stride0 = off, pitch
+    p.flags = q.flags
+    ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda")
+    uk.mmt4d_unpacked(p, rows, cols, ws)
+    torch.cuda.synchronize()
+    assert uk.device_status() == (0, 0)
+    whole = out.cpu().numpy()
+    got = whole[off:off + rows * pitch].reshape(rows, pitch)[:, :cols]
+    if is_int:
+        assert np.array_equal(got, want)
+    else:
+        assert cases.rel_frobenius(got, want) <= FLOAT_TOL
+    assert _untouched_outside(whole, init, rows, cols, pad, off)
