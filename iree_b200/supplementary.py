@@ -183,6 +183,10 @@ def _matmul_rowmajor_case(M, N, K, bf16_peak):
         uk.unpack(u)
 
     chain_ms, chain_best = _time(chain)
+    # the halfway form: packed operands in, row-major result out (unpack folded into the epilogue)
+    qu = _mmt4d_params(abi.MMT4D_BF16BF16F32, M1, N1, K1, 16, 16, 2, plhs, prhs, out)
+    qu.out_stride0 = N
+    unpacked_ms, _ = _time(lambda: uk.mmt4d_unpacked(qu, M, N, ws))
     parts = {}
     for name, fn in [("pack_lhs", lambda: uk.pack(pl)), ("pack_rhs", lambda: uk.pack(pr)),
                      ("mmt4d", lambda: uk.mmt4d(q, workspace=ws)), ("unpack", lambda: uk.unpack(u))]:
@@ -190,7 +194,8 @@ def _matmul_rowmajor_case(M, N, K, bf16_peak):
     return {"fused_ms": fused, "fused_ms_best": fused_best, "fused_tflops": ops / fused / 1e9,
             "fused_frac_of_bf16_burst": ops / fused / 1e9 / bf16_peak,
             "chain_ms": chain_ms, "chain_ms_best": chain_best, "chain_tflops": ops / chain_ms / 1e9,
-            "chain_parts_ms": parts, "chain_tiles": "16x16x2"}
+            "chain_parts_ms": parts, "chain_tiles": "16x16x2",
+            "mmt4d_with_unpack_folded_ms": unpacked_ms}
 
 
 def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
