@@ -14,8 +14,6 @@
 // ukernel/unpack.c:190-257): opaque elements of 1, 2 or 4 bytes; padding writes the low
 // element-size bytes of padding_value; unpack never writes outside out_size0 x out_size1.
 #include <algorithm>
-#include <cstdlib>
-
 #include "uk_common.h"
 
 namespace uk {
@@ -39,6 +37,7 @@ struct RelayoutArgs {
   int32_t vec_mat;       // 1: 16-byte vector access to the matrix side is legal
   int32_t vec_tiled;     // 1: 16-byte vector access to the tiled side is legal
   int64_t nblk1;         // blocks along dim 1
+  int32_t use_bulk;      // constant-shape kernels: move whole matrix rows with bulk async copies
 };
 
 template <int ES> struct ElemT;
@@ -255,6 +254,57 @@ __global__ void __launch_bounds__(256) relayout_staged_kernel(RelayoutArgs a) {
     }
   };
 
+  // Constant-shape blocks that lie wholly inside the matrix move their matrix-side rows (one
+  // contiguous, 16-byte aligned segment per row) with bulk asynchronous copies: no registers,
+  // no per-vector instructions, every row of the block in flight at once.
+  __shared__ __align__(8) uint64_t row_bar;
+  const bool bulk = kSpec && a.use_bulk && row_base + rows <= a.mat_size0 &&
+                    col_base + cols <= a.mat_size1;
+  const uint32_t row_bytes = uint32_t(cols) * ES;
+  if (IS_PACK && bulk) {
+    const uint32_t bar = static_cast<uint32_t>(__cvta_generic_to_shared(&row_bar));
+    if (threadIdx.x == 0) {
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(rows) : "memory");
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+      const char* g = mat_src + ((row_base + r) * a.mat_stride0 + col_base) * ES;
+      const uint32_t sdst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_b + r * pitch_b));
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(row_bytes) : "memory");
+      asm volatile(
+          "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+          :: "r"(sdst), "l"(g), "r"(row_bytes), "r"(bar) : "memory");
+    }
+    // bounded wait for all rows of the block
+    const long long deadline = clock64() + (1ll << 31);
+    uint32_t done = 0;
+    while (!done && clock64() < deadline) {
+      asm volatile(
+          "{\n.reg .pred p;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n"
+          "selp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(done) : "r"(bar) : "memory");
+    }
+    __syncthreads();
+    tiled_phase();
+    return;
+  }
+  if (!IS_PACK && bulk) {
+    tiled_phase();   // whole tiles -> shared memory (generic-proxy stores)
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+      char* g = mat_dst + ((row_base + r) * a.mat_stride0 + col_base) * ES;
+      const uint32_t ssrc = static_cast<uint32_t>(__cvta_generic_to_shared(smem_b + r * pitch_b));
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                   :: "l"(g), "r"(ssrc), "r"(row_bytes) : "memory");
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory is released at exit
+    return;
+  }
+
   if (IS_PACK) {
     matrix_phase();  // matrix rows -> shared memory, padding filled in
     __syncthreads();
@@ -422,6 +472,7 @@ template <int ES, bool IS_PACK, class Shape>
 int launch_fixed(RelayoutArgs a, cudaStream_t stream) {
   a.R0 = Shape::R0; a.R1 = Shape::R1;
   a.nblk1 = a.outer1 / Shape::R1;
+  a.use_bulk = env_flag("IREE_UK_B200_NO_BULK_ROWS") ? 0 : 1;
   const int64_t blocks = a.nblk1 * (a.outer0 / Shape::R0);
   constexpr int pitch = staged_pitch_words(Shape::R1 * Shape::T1 * ES);
   constexpr size_t smem = size_t(Shape::R0) * Shape::T0 * pitch * 4;
