@@ -668,7 +668,13 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   const int smem_budget = 200 * 1024;
   P.num_stages = std::max(2, std::min(kMaxStages, smem_budget / stage_bytes));
-  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 + ((num_peers || multicast_out) ? 4 * kEpiStageBytes : 0);
+  // In the two-CTA kernel, 32-bit output tiles that are only written leave through shared memory as
+  // whole 1 KB bulk copies (1-2 % faster than 32-byte stores from registers on the headline
+  // shape; no gain for small problems or when the old tile is read first).
+  P.staged_epilogue = (pair && !rm && !P.out16 && !multicast_out && !P.accumulate &&
+                       debug_int("IREE_UK_B200_DEBUG_STAGED_EPILOGUE", 1)) ? 1 : 0;
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 +
+                      ((num_peers || multicast_out || P.staged_epilogue) ? 4 * kEpiStageBytes : 0);
 
   if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
   cudaError_t e;

@@ -65,6 +65,7 @@ struct TcParams {
   int32_t out16;         // 0: 32-bit output; 1: f16 output, 2: bf16 output (rounded once, RNE)
   int32_t use_multicast; // output tiles are stored through an NVLink multicast mapping
   int64_t mc_delta;      // byte distance from `out` to that mapping
+  int32_t staged_epilogue;  // local output through shared memory and 1 KB bulk copies too
   int32_t num_peers;     // copies of every output tile also stored to this many peer buffers
   int64_t peer_delta[IREE_UK_B200_MAX_PEERS];  // byte distance from `out` to each peer's buffer
   int32_t out_row_major; // fused matmul: the output is a row-major rows x cols matrix
@@ -396,7 +397,7 @@ __device__ __forceinline__ void bulk_wait_read() {
 
 constexpr int kEpiStageBytes = 4096;  // per epilogue warp: two buffers of 32 rows x 64 bytes
 
-// Epilogue with peer copies: the warp's 32 rows x 16 columns (two whole 16x16 output tiles of
+// Epilogue through shared memory, with or without peer copies: the warp's 32 rows x 16 columns (two whole 16x16 output tiles of
 // 1 KB each) are staged in shared memory and leave as 1 KB bulk copies, one per tile and
 // destination: the local output and every peer buffer. Whole-tile writes are what NVLink
 // carries efficiently; 32-byte stores from registers reach a fraction of the link rate.
@@ -567,7 +568,7 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
     epilogue_rows_multicast(P, taddr0, row, n1_0, chunks, epi_stage, lane);
     return;
   }
-  if (P.num_peers) {
+  if (P.num_peers || P.staged_epilogue) {
     epilogue_rows_peers(P, taddr0, row, n1_0, chunks, epi_stage, lane);
     return;
   }
