@@ -634,7 +634,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   P.bn = bn;
   P.m_tiles = int((p->M * 16 + tile_m - 1) / tile_m);
   P.n_tiles = int((p->N * 16 + bn - 1) / bn);
-  P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
+  P.group_m = std::min(P.m_tiles, debug_int("IREE_UK_B200_DEBUG_GROUP_M", pair ? 8 : 16));
   P.out = static_cast<char*>(p->out_buffer) + p->out_offset * ti.out_es;
   P.out_stride0 = p->out_stride0;
   P.M1 = p->M;
