@@ -648,6 +648,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     P.rows = rm->rows;
     P.cols = rm->cols;
     P.out_vec16 = ((reinterpret_cast<uintptr_t>(P.out) & 15) == 0 && (p->out_stride0 * 4) % 16 == 0) ? 1 : 0;
+    P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * 4) % 32 == 0) ? 1 : 0;
   }
   if (multicast_out) {
     P.use_multicast = 1;
@@ -1056,6 +1057,7 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   P.cols = N;
   P.out_row_major = 1;
   P.out_vec16 = ((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (out_stride0 * 4) % 16 == 0) ? 1 : 0;
+  P.out_vec32 = ((reinterpret_cast<uintptr_t>(out) & 31) == 0 && (out_stride0 * 4) % 32 == 0) ? 1 : 0;
   P.accumulate = (flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
   P.out_is_int = ti.is_int ? 1 : 0;
   P.status = status;

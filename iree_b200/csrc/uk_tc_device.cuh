@@ -351,7 +351,11 @@ __device__ __forceinline__ void epilogue_rows_rowmajor(const TcParams& P, uint32
     const int64_t col = col0 + c * 16;
     if (row >= P.rows || col >= P.cols || (P.debug_flags & 1u)) continue;
     uint32_t* dst = reinterpret_cast<uint32_t*>(P.out) + row * P.out_stride0 + col;
-    if (P.out_vec16 && col + 16 <= P.cols) {
+    if (P.out_vec32 && !P.accumulate && col + 16 <= P.cols) {
+      // write-only, 32-byte aligned rows: two whole-sector stores
+      st_global_v8(dst, &r[0]);
+      st_global_v8(dst + 8, &r[8]);
+    } else if (P.out_vec16 && col + 16 <= P.cols) {
       uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
