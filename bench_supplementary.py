@@ -1,4 +1,5 @@
-"""Device-timed figures for the other configurations of the path (single GPU): the small
+"""Benchmark harness, not part of the library: device-timed figures for the other
+configurations of the path (single GPU): the small
 s8s8s32 GEMM, an s8s8s32 GEMM at the prefill dimensions, the f16 GEMM with ACCUMULATE, the
 s16u4s32 decode GEMV, and the pack / unpack relayouts. Used by ``bench.py`` to report them
 beside the headline line; every figure is CUDA-event time per call. Configurations whose
@@ -7,10 +8,17 @@ total footprint exceeds L2.
 
 Bytes for pack / unpack count what is read plus what is written.
 """
+import os
+import sys
+
 import torch
 
-from . import abi
-from . import ukernel as uk
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from iree_b200 import abi  # noqa: E402
+from iree_b200 import ukernel as uk  # noqa: E402
 
 
 ITERS, WARMUP = 10, 3
@@ -61,7 +69,6 @@ def _time_rotating(fns, iters=None, warmup=None):
 
 
 def _mmt4d_params(flags, M, N, K, M0, N0, K0, lhs, rhs, out):
-    from .abi import MMT4D_BITS
     p = abi.Mmt4dParams()
     p.lhs_buffer, p.rhs_buffer, p.out_buffer = lhs.data_ptr(), rhs.data_ptr(), out.data_ptr()
     p.M, p.N, p.K, p.M0, p.N0, p.K0, p.flags = M, N, K, M0, N0, K0, flags
@@ -345,7 +352,7 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
 
 
 def main():
-    """``python -m iree_b200.supplementary [--only SUBSTR] [--mmt4d bf16,M1,N1,K1 [--no-ws]]
+    """``python bench_supplementary.py [--only SUBSTR] [--mmt4d bf16,M1,N1,K1 [--no-ws]]
     [--matmul M,N,K] [--iters N] [--warmup N]``: prints one JSON object. Small, single-kernel runs of this
     command are what the profiles under ``profiles/`` were captured from."""
     import argparse
@@ -365,8 +372,7 @@ def main():
     if a.mmt4d:
         t, m, n, k = a.mmt4d.split(",")
         custom = (t, int(m), int(n), int(k))
-    peaks_path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
-                              "MEASURED_PEAKS.json")
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         peaks = json.load(open(peaks_path))
     except OSError:

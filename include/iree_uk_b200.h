@@ -220,7 +220,7 @@ typedef enum iree_uk_b200_path_t {
 /* Replaces iree_uk_mmt4d_p (ukernel/mmt4d.c:115-141). Uses no scratch memory. The
  * tensor-core triples with 16x16 tiles still run on the tensor cores: 16-bit K0 = 1
  * operands are staged by TMA as they lie, every other layout by a kernel whose producer warps
- * re-tile the operands on their way into shared memory (about 40 % of the rate that
+ * re-tile the operands on their way into shared memory (measured 0.38 of the rate that
  * iree_uk_b200_mmt4d_ws reaches with its pre-pass into caller-owned scratch). Everything
  * else runs the generic CUDA-core kernel. */
 IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d(const iree_uk_mmt4d_params_t* params,
@@ -233,7 +233,11 @@ iree_uk_b200_mmt4d_workspace_size(const iree_uk_mmt4d_params_t* params);
 
 /* Same operation as iree_uk_b200_mmt4d with caller-owned scratch (256-byte aligned
  * device memory, at least iree_uk_b200_mmt4d_workspace_size bytes, free to reuse once
- * the enqueued work has completed). Replaces iree_uk_mmt4d_p (ukernel/mmt4d.c:115-141). */
+ * the enqueued work has completed). Replaces iree_uk_mmt4d_p (ukernel/mmt4d.c:115-141).
+ * workspace == NULL (or workspace_bytes == 0) is the scratch-free call above. A workspace that
+ * is offered but smaller than the kernel that would use it needs is refused with
+ * IREE_UK_B200_WORKSPACE_TOO_SMALL and nothing is launched; the call never falls back to a
+ * slower kernel on its own. */
 IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* params,
                                               void* workspace, size_t workspace_bytes,
                                               void* cu_stream);
@@ -372,7 +376,11 @@ IREE_UK_B200_EXPORT int iree_uk_b200_peer_close(void* device_ptr);
  * the library image in each GPU's memory (every GPU that loads the library holds those
  * 32 MiB until the process exits). The call itself allocates nothing, on host or device.
  *
- * Same operation, arguments and results as iree_uk_b200_mmt4d_ws. Differences:
+ * Same operation, arguments and results as iree_uk_b200_mmt4d_ws, and the same choice of
+ * kernel: whatever iree_uk_b200_mmt4d_ws would run with scratch (the tensor-core triples with
+ * 16x16 tiles, and s16u4s32 1x32x8 with at least 32 rows) runs here on the array; problems
+ * that use no scratch anyway (the weight-streaming s16u4s32 kernel below 32 rows, the generic
+ * kernel, the zero fill) are served exactly as by iree_uk_b200_mmt4d. Differences:
  *  - a problem whose scratch need (iree_uk_b200_mmt4d_workspace_size) exceeds the array is
  *    refused with IREE_UK_B200_WORKSPACE_TOO_SMALL and nothing is launched; it is never
  *    silently served by a slower kernel;
@@ -551,6 +559,23 @@ IREE_UK_B200_EXPORT int iree_uk_b200_query_tile_sizes_2d(
  * IREE_UK_B200_OK or IREE_UK_B200_DEVICE_TIMEOUT; *detail (may be NULL) receives the raw
  * word. It is the only entry point that synchronises. No counterpart in the reference. */
 IREE_UK_B200_EXPORT int iree_uk_b200_device_status(void* cu_stream, uint32_t* detail);
+
+/*===----------------------------------------------------------------------===*/
+/* Kernel timing (benchmarks)                                                  */
+/*===----------------------------------------------------------------------===*/
+
+/* Off by default. iree_uk_b200_kernel_timing(n) with n > 0 makes every n-th later tensor-core
+ * mmt4d call on the CURRENT device record three CUDA events on its stream: before its pre-pass,
+ * between pre-pass and main kernel, and after the main kernel (a recorded call therefore runs
+ * its two kernels without their usual overlap); n = 0 switches it off. The last 64 recorded
+ * calls are remembered per device. iree_uk_b200_kernel_timing_mean_ms waits for the last
+ * recorded call and returns the mean pre-pass and main-kernel milliseconds over the remembered
+ * calls and their number (IREE_UK_B200_INVALID_ARGUMENT when nothing was recorded). This is how
+ * a benchmark separates the main kernel's duration from the step it is part of. No counterpart
+ * in the reference. */
+IREE_UK_B200_EXPORT int iree_uk_b200_kernel_timing(int every);
+IREE_UK_B200_EXPORT int iree_uk_b200_kernel_timing_mean_ms(float* prepass_ms, float* main_ms,
+                                                           int* count);
 
 /* Library build identification: "iree_uk_b200 <version> sm_100a". */
 IREE_UK_B200_EXPORT const char* iree_uk_b200_version(void);

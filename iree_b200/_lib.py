@@ -60,6 +60,8 @@ SIGNATURES = {
     "iree_uk_b200_unpack_path": (C.c_int, [_P]),
     "iree_uk_b200_query_tile_sizes_2d": (C.c_int, [_P, _P]),
     "iree_uk_b200_device_status": (C.c_int, [_P, _P]),
+    "iree_uk_b200_kernel_timing": (C.c_int, [C.c_int]),
+    "iree_uk_b200_kernel_timing_mean_ms": (C.c_int, [_P, _P, _P]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():
@@ -67,12 +69,12 @@ for _name, (_res, _args) in SIGNATURES.items():
     _fn.restype = _res
     _fn.argtypes = _args
 
-# internal entry point (not in the public header): explicit operand-staging variant
-lib.iree_uk_b200_debug_mmt4d_variant.restype = C.c_int
-lib.iree_uk_b200_debug_mmt4d_variant.argtypes = [_P, _P, _sz, C.c_int, _P]
-lib.iree_uk_b200_debug_kernel_timing.restype = C.c_int
-lib.iree_uk_b200_debug_kernel_timing.argtypes = [C.c_int]
-lib.iree_uk_b200_debug_last_kernel_ms.restype = C.c_int
-lib.iree_uk_b200_debug_last_kernel_ms.argtypes = [_P, _P]
-lib.iree_uk_b200_debug_mean_kernel_ms.restype = C.c_int
-lib.iree_uk_b200_debug_mean_kernel_ms.argtypes = [_P, _P, _P]
+# test hooks, declared in include/iree_uk_b200_testing.h
+TESTING_SIGNATURES = {
+    "iree_uk_b200_testing_starve_producers": (C.c_int, [C.c_int]),
+    "iree_uk_b200_testing_mmt4d_form": (C.c_int, [_P, _P, _sz, C.c_int, _P]),
+}
+for _name, (_res, _args) in TESTING_SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args

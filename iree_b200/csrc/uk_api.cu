@@ -8,6 +8,7 @@
 #include <cuda.h>
 
 #include "uk_common.h"
+#include "../../include/iree_uk_b200_testing.h"
 
 namespace uk {
 
@@ -33,10 +34,16 @@ uint32_t* device_status_word() {
 static std::atomic<int> g_f32_mode{0};
 int f32_mode() { return g_f32_mode.load(std::memory_order_relaxed); }
 
-KernelTiming& kernel_timing() {
-  static KernelTiming t;
-  return t;
+KernelTiming* kernel_timing() {
+  constexpr int kMaxDevices = 64;
+  static KernelTiming rings[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  return &rings[dev];
 }
+
+static std::atomic<int> g_starve{0};
+bool testing_starve_producers() { return g_starve.load(std::memory_order_relaxed) != 0; }
 
 namespace {
 
@@ -136,9 +143,15 @@ size_t iree_uk_b200_mmt4d_workspace_size(const iree_uk_mmt4d_params_t* params) {
 
 int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* params, void* workspace,
                           size_t workspace_bytes, void* cu_stream) {
-  const bool have_ws = workspace != nullptr && workspace_bytes > 0 &&
-                       workspace_bytes >= mmt4d_tc_workspace_size(params);
-  return run_mmt4d(params, workspace, workspace_bytes, have_ws, cu_stream);
+  // No workspace at all is the scratch-free call. A workspace that is offered but too small for
+  // the kernel that would use it is reported, never quietly replaced by a slower kernel.
+  if (!workspace || workspace_bytes == 0) return run_mmt4d(params, nullptr, 0, false, cu_stream);
+  Mmt4dPath path;
+  const int rc = select_mmt4d(params, true, &path);
+  if (rc) return rc;
+  if (path == Mmt4dPath::TcRetile && workspace_bytes < mmt4d_tc_workspace_size(params))
+    return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  return run_mmt4d(params, workspace, workspace_bytes, true, cu_stream);
 }
 
 int iree_uk_b200_mmt4d_flat(const void* lhs_buffer, iree_uk_index_t lhs_offset,
@@ -610,48 +623,36 @@ int iree_uk_b200_device_status(void* cu_stream, uint32_t* detail) {
   return IREE_UK_B200_OK;
 }
 
-// Internal, not declared in the public header: runs the tensor-core kernel with an explicit
-// kernel form (0 = automatic, 5 = two-CTA, 6 = one-CTA, 3 = scratch-free MN-major staging). Used
-// by tests and probes to pin the form that runs.
-IREE_UK_B200_EXPORT int iree_uk_b200_debug_mmt4d_variant(const iree_uk_mmt4d_params_t* params,
-                                                         void* workspace, size_t workspace_bytes,
-                                                         int variant, void* cu_stream) {
-  const int rc = validate_mmt4d(params);
-  if (rc) return rc;
-  if (!mmt4d_tc_eligible(params) && !mmt4d_tc_s16u4_eligible(params)) return IREE_UK_B200_UNSUPPORTED;
-  return launch_mmt4d_tc(params, workspace, workspace_bytes, variant,
-                         static_cast<cudaStream_t>(cu_stream));
-}
+// ---- kernel timing (benchmarks) ----
 
-// Internal, not declared in the public header: benchmark timing of the tensor-core path.
-// enable != 0 creates the CUDA events (once) and makes every later (enable = 1) or every n-th
-// later (enable = n) tensor-core mmt4d call
-// record three of them: before the re-tile pre-pass, before the main kernel and after it.
-// The last 64 calls are remembered.
-IREE_UK_B200_EXPORT int iree_uk_b200_debug_kernel_timing(int enable) {
-  KernelTiming& t = kernel_timing();
-  if (enable && !t.ev[0][0]) {
+int iree_uk_b200_kernel_timing(int every) {
+  KernelTiming* t = kernel_timing();
+  if (!t) return IREE_UK_B200_CUDA_ERROR;
+  t->enabled.store(false);
+  if (every > 0 && !t->ev[0][0]) {
     for (int c = 0; c < KernelTiming::kRing; ++c)
       for (int i = 0; i < 3; ++i)
-        if (cudaEventCreate(&t.ev[c][i]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+        if (cudaEventCreate(&t->ev[c][i]) != cudaSuccess) {
+          cudaGetLastError();
+          return IREE_UK_B200_CUDA_ERROR;
+        }
   }
-  t.enabled = enable != 0;
-  t.every = enable > 1 ? enable : 1;  // enable = n > 1: record every n-th call only
-  t.calls = 0;
-  t.seen = 0;
+  t->every.store(every > 1 ? every : 1);
+  t->calls.store(0);
+  t->seen.store(0);
+  t->enabled.store(every > 0);
   return IREE_UK_B200_OK;
 }
 
-// Mean milliseconds of pre-pass and main kernel over the remembered calls (at most the last
-// 64 since timing was enabled); *count receives how many. Synchronises on the last event.
-IREE_UK_B200_EXPORT int iree_uk_b200_debug_mean_kernel_ms(float* prepass_ms, float* main_ms,
-                                                          int* count) {
-  KernelTiming& t = kernel_timing();
-  if (!t.enabled || t.calls == 0) return IREE_UK_B200_INVALID_ARGUMENT;
-  const long long n = t.calls < KernelTiming::kRing ? t.calls : KernelTiming::kRing;
+int iree_uk_b200_kernel_timing_mean_ms(float* prepass_ms, float* main_ms, int* count) {
+  KernelTiming* t = kernel_timing();
+  if (!t) return IREE_UK_B200_CUDA_ERROR;
+  const long long calls = t->calls.load();
+  if (!t->enabled.load() || calls == 0) return IREE_UK_B200_INVALID_ARGUMENT;
+  const long long n = calls < KernelTiming::kRing ? calls : KernelTiming::kRing;
   double a = 0.0, b = 0.0;
   for (long long i = 0; i < n; ++i) {
-    cudaEvent_t* e = t.ev[(t.calls - 1 - i) % KernelTiming::kRing];
+    cudaEvent_t* e = t->ev[(calls - 1 - i) % KernelTiming::kRing];
     if (cudaEventSynchronize(e[2]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
     float x = 0.f, y = 0.f;
     if (cudaEventElapsedTime(&x, e[0], e[1]) != cudaSuccess ||
@@ -666,19 +667,21 @@ IREE_UK_B200_EXPORT int iree_uk_b200_debug_mean_kernel_ms(float* prepass_ms, flo
   return IREE_UK_B200_OK;
 }
 
-// Milliseconds of the last recorded call: pre-pass and main kernel.
-IREE_UK_B200_EXPORT int iree_uk_b200_debug_last_kernel_ms(float* prepass_ms, float* main_ms) {
-  KernelTiming& t = kernel_timing();
-  if (!t.enabled || t.calls == 0) return IREE_UK_B200_INVALID_ARGUMENT;
-  cudaEvent_t* e = t.ev[(t.calls - 1) % KernelTiming::kRing];
-  if (cudaEventSynchronize(e[2]) != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
-  float a = 0.f, b = 0.f;
-  if (cudaEventElapsedTime(&a, e[0], e[1]) != cudaSuccess ||
-      cudaEventElapsedTime(&b, e[1], e[2]) != cudaSuccess)
-    return IREE_UK_B200_CUDA_ERROR;
-  if (prepass_ms) *prepass_ms = a;
-  if (main_ms) *main_ms = b;
-  return IREE_UK_B200_OK;
+// ---- test hooks (include/iree_uk_b200_testing.h) ----
+
+int iree_uk_b200_testing_starve_producers(int enable) { return g_starve.exchange(enable ? 1 : 0); }
+
+int iree_uk_b200_testing_mmt4d_form(const iree_uk_mmt4d_params_t* params, void* workspace,
+                                    size_t workspace_bytes, int form, void* cu_stream) {
+  const int rc = validate_mmt4d(params);
+  if (rc) return rc;
+  if (form != IREE_UK_B200_TESTING_FORM_ONE_CTA && form != IREE_UK_B200_TESTING_FORM_TWO_CTA &&
+      form != IREE_UK_B200_TESTING_FORM_TWO_CTA_HYBRID)
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  if (params->M < 1 || params->N < 1 || params->K < 1) return IREE_UK_B200_UNSUPPORTED;
+  if (!mmt4d_tc_eligible(params)) return IREE_UK_B200_UNSUPPORTED;
+  return launch_mmt4d_tc(params, workspace, workspace_bytes, form,
+                         static_cast<cudaStream_t>(cu_stream));
 }
 
 }  // extern "C"

@@ -3,6 +3,8 @@
 #define IREE_UK_B200_CSRC_UK_COMMON_H_
 
 #include <cuda_runtime.h>
+
+#include <atomic>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -109,22 +111,38 @@ inline int cuda_status(cudaError_t e) {
   return e == cudaSuccess ? IREE_UK_B200_OK : IREE_UK_B200_CUDA_ERROR;
 }
 
-// Optional kernel timing for benchmarks (off by default): when enabled, launchers that run a
-// pre-pass plus a main kernel record CUDA events between them on the launching stream.
+// Optional kernel timing for benchmarks (off by default, see iree_uk_b200_kernel_timing): when
+// enabled on a device, launchers that run a pre-pass plus a main kernel record CUDA events
+// between them on the launching stream. One ring per device, created on that device; the
+// counters are atomics, so concurrent callers lose no slot. A recorded call runs without the
+// overlap of its pre-pass and main kernel (the event between them serialises the two), which is
+// why only every n-th call is recorded.
 struct KernelTiming {
   static constexpr int kRing = 64;  // calls remembered
-  bool enabled = false;
-  int every = 1;                  // record one call in `every` (the others run unobserved)
-  long long seen = 0;             // tensor-core calls since timing was enabled
-  cudaEvent_t ev[kRing][3] = {};  // per recorded call: before pre-pass, before main, after main
-  long long calls = 0;            // calls recorded since timing was enabled
+  std::atomic<bool> enabled{false};
+  std::atomic<int> every{1};          // record one call in `every` (the others run unobserved)
+  std::atomic<long long> seen{0};     // tensor-core calls since timing was enabled
+  cudaEvent_t ev[kRing][3] = {};      // per recorded call: before pre-pass, before main, after main
+  std::atomic<long long> calls{0};    // calls recorded since timing was enabled
   // The event triple for this call, or nullptr when the call is not to be recorded.
   cudaEvent_t* next_slot() {
-    if (!enabled) return nullptr;
-    return (seen++ % every == 0) ? ev[calls % kRing] : nullptr;
+    if (!enabled.load(std::memory_order_relaxed)) return nullptr;
+    const long long n = seen.fetch_add(1, std::memory_order_relaxed);
+    if (n % every.load(std::memory_order_relaxed)) return nullptr;
+    return ev[calls.load(std::memory_order_relaxed) % kRing];
+  }
+  // Records `e` on `stream`; a failure is cleared so that it cannot be mistaken for a launch
+  // error by the caller's own cudaGetLastError().
+  static void record(cudaEvent_t e, cudaStream_t stream) {
+    if (cudaEventRecord(e, stream) != cudaSuccess) cudaGetLastError();
   }
 };
-KernelTiming& kernel_timing();
+// The timing ring of the current device (nullptr when the device cannot be determined).
+KernelTiming* kernel_timing();
+
+// Test hook (iree_uk_b200_testing_starve_producers): true while the producers of the
+// tensor-core kernels are told to fill nothing, which makes the bounded waits run out.
+bool testing_starve_producers();
 
 // True when the environment variable is set to a non-empty value other than "0".
 bool env_flag(const char* name);

@@ -260,7 +260,21 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
       }
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) {
-        if (lane == 0) atomicOr(status, 1u << 4);
+        if (lane == 0) {
+          atomicOr(status, 1u << 4);
+          // one more bounded wait: the copy must not still be in flight into this warp's
+          // buffer when the block's shared memory is released
+          const long long drain = clock64() + (1ll << 31);
+          uint32_t landed = 0;
+          while (!landed && clock64() < drain) {
+            asm volatile(
+                "{\n.reg .pred p;\n"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                "selp.u32 %0, 1, 0, p;\n}\n"
+                : "=r"(landed) : "r"(my_bar), "r"(parity) : "memory");
+          }
+        }
+        __syncwarp();
         break;
       }
     }

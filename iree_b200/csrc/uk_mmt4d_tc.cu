@@ -39,12 +39,23 @@ namespace {
 // host side: tensor maps, descriptors, launch
 // ---------------------------------------------------------------------------------------
 
-// Experiment knobs, honoured only when IREE_UK_B200_DEBUG is set in the environment.
+// Tuning overrides read from the environment. They exist only in a build made with
+// -DIREE_UK_B200_EXPERIMENTS (parameter sweeps); the shipped library always takes `fallback`.
+#ifdef IREE_UK_B200_EXPERIMENTS
 int debug_int(const char* name, int fallback) {
-  static const bool enabled = std::getenv("IREE_UK_B200_DEBUG") != nullptr;
-  if (!enabled) return fallback;
   const char* v = std::getenv(name);
   return v ? std::atoi(v) : fallback;
+}
+#else
+constexpr int debug_int(const char*, int fallback) { return fallback; }
+#endif
+
+// Wait policy of a launch: every device-side wait gives up after about a second; with the
+// starve test hook set, the producers fill nothing and the limit drops to a few tens of
+// milliseconds, because several waits then run out one after the other.
+void set_wait_policy(TcParams* P) {
+  P->starve = testing_starve_producers() ? 1 : 0;
+  P->wait_cycles = P->starve ? (1ll << 26) : kWaitCycles;
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -309,9 +320,9 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   const S16U4Layout l = s16u4_layout(p);
   if (!ws || ws_bytes < size_t(2 * l.plane_bytes + l.w_bytes)) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
-  KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.next_slot();
-  if (tev) cudaEventRecord(tev[0], stream);
+  KernelTiming* timing = kernel_timing();
+  cudaEvent_t* tev = timing ? timing->next_slot() : nullptr;
+  if (tev) KernelTiming::record(tev[0], stream);
 
   const char* lhs = static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * 2;
   const char* rhs = static_cast<const char*>(p->rhs_buffer) + p->rhs_offset / 2;
@@ -381,12 +392,12 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
   P.out_is_int = 1;
   P.status = status;
-  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
+  set_wait_policy(&P);
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
   const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
   if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
-  if (tev) cudaEventRecord(tev[1], stream);
+  if (tev) KernelTiming::record(tev[1], stream);
   cudaError_t e;
   if (pair) {
     const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
@@ -397,8 +408,8 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   }
   if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   if (tev) {
-    cudaEventRecord(tev[2], stream);
-    ++timing.calls;
+    KernelTiming::record(tev[2], stream);
+    timing->calls.fetch_add(1, std::memory_order_relaxed);
   }
   return cuda_status(cudaGetLastError());
 }
@@ -516,9 +527,9 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
 
   TcParams P;
   std::memset(&P, 0, sizeof P);
-  KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.next_slot();
-  if (tev) cudaEventRecord(tev[0], stream);
+  KernelTiming* timing = kernel_timing();
+  cudaEvent_t* tev = timing ? timing->next_slot() : nullptr;
+  if (tev) KernelTiming::record(tev[0], stream);
   int bn = pick_bn(p->M, p->N);
   bool pair = false;
   int pair_clusters = 0;
@@ -666,7 +677,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     if (P.peer_delta[g] % (P.out_vec32 ? 32 : 16)) return IREE_UK_B200_INVALID_ARGUMENT;
   }
   P.status = status;
-  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
+  set_wait_policy(&P);
 
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   const int smem_budget = 200 * 1024;
@@ -681,7 +692,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
 
   if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
   cudaError_t e;
-  if (tev) cudaEventRecord(tev[1], stream);
+  if (tev) KernelTiming::record(tev[1], stream);
   if (pair) {
     const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
     e = ti.is_int ? launch_main(mmt4d_tc2_kernel<true>, grid, 2, smem, stream, P)
@@ -693,8 +704,8 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   }
   if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   if (tev) {
-    cudaEventRecord(tev[2], stream);
-    ++timing.calls;
+    KernelTiming::record(tev[2], stream);
+    timing->calls.fetch_add(1, std::memory_order_relaxed);
   }
   return cuda_status(cudaGetLastError());
 }
@@ -766,9 +777,9 @@ int launch_mmt4d_tc_sw(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
   if (!status || !di || !sw_kernels_ready(di, &max_dyn)) return IREE_UK_B200_CUDA_ERROR;
   TcParams P;
   std::memset(&P, 0, sizeof P);
-  KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.next_slot();
-  if (tev) { cudaEventRecord(tev[0], stream); cudaEventRecord(tev[1], stream); }
+  KernelTiming* timing = kernel_timing();
+  cudaEvent_t* tev = timing ? timing->next_slot() : nullptr;
+  if (tev) { KernelTiming::record(tev[0], stream); KernelTiming::record(tev[1], stream); }
   const int G = p->K0 * ti.es;
   const int bn = pick_bn(p->M, p->N);
   P.src_a = static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * ti.es;
@@ -801,7 +812,7 @@ int launch_mmt4d_tc_sw(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
   P.out_vec32 = ((reinterpret_cast<uintptr_t>(P.out) & 31) == 0 && (p->out_stride0 * ti.out_es) % 32 == 0) ? 1 : 0;
   P.out16 = ti.out_es == 2 ? (ti.fmt == 0u ? 1 : 2) : 0;
   P.status = status;
-  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
+  set_wait_policy(&P);
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
   const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
@@ -809,8 +820,8 @@ int launch_mmt4d_tc_sw(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
   const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
   sw_kernel(ti.is_int, G)<<<grid, kSwThreads, smem, stream>>>(P);
   if (tev) {
-    cudaEventRecord(tev[2], stream);
-    ++timing.calls;
+    KernelTiming::record(tev[2], stream);
+    timing->calls.fetch_add(1, std::memory_order_relaxed);
   }
   return cuda_status(cudaGetLastError());
 }
@@ -851,11 +862,13 @@ extern "C" int iree_uk_b200_mmt4d_static_scratch(const iree_uk_mmt4d_params_t* p
                                                  void* cu_stream) {
   const int rc = uk::validate_mmt4d(params);
   if (rc) return rc;
-  // Only the tensor-core path uses scratch; everything else goes the usual way.
-  const bool trivial = params->M == 0 || params->N == 0 || params->K == 0 ||
-                       params->M0 == 0 || params->N0 == 0 || params->K0 == 0;
-  if (trivial || uk::mmt4d_gemv_s16u4_eligible(params) || !uk::mmt4d_tc_eligible(params))
-    return iree_uk_b200_mmt4d(params, cu_stream);
+  // Only the kernels that iree_uk_b200_mmt4d_ws would run with scratch need the array: the
+  // tensor-core triples with 16x16 tiles, and s16u4s32 1x32x8 once there are 32 rows (below
+  // that the weight-streaming kernel serves it, without scratch). Everything else goes the
+  // usual way.
+  const int path = iree_uk_b200_mmt4d_path(params, 1);
+  if (path < 0) return -path;
+  if (path != IREE_UK_B200_PATH_TCGEN05_RETILE) return iree_uk_b200_mmt4d(params, cu_stream);
   if (uk::mmt4d_tc_workspace_size(params) > size_t(IREE_UK_B200_STATIC_SCRATCH_BYTES))
     return IREE_UK_B200_WORKSPACE_TOO_SMALL;
   void* scratch = uk::static_scratch_address();
@@ -943,9 +956,9 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   uint32_t* status = device_status_word();
   const DeviceInfo* di = device_info();
   if (!status || !di) return IREE_UK_B200_CUDA_ERROR;
-  KernelTiming& timing = kernel_timing();
-  cudaEvent_t* tev = timing.next_slot();
-  if (tev) cudaEventRecord(tev[0], stream);
+  KernelTiming* timing = kernel_timing();
+  cudaEvent_t* tev = timing ? timing->next_slot() : nullptr;
+  if (tev) KernelTiming::record(tev[0], stream);
 
   // RHS: transposed once into K-major rows. LHS: used in place when TMA can address it,
   // else copied with a TMA-friendly pitch.
@@ -1061,11 +1074,11 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   P.accumulate = (flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
   P.out_is_int = ti.is_int ? 1 : 0;
   P.status = status;
-  P.debug_flags = uint32_t(debug_int("IREE_UK_B200_DEBUG_FLAGS", 0));
+  set_wait_policy(&P);
   const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
   P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
   const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
-  if (tev) cudaEventRecord(tev[1], stream);
+  if (tev) KernelTiming::record(tev[1], stream);
   cudaError_t e;
   if (pair) {
     const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
@@ -1078,8 +1091,8 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   }
   if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   if (tev) {
-    cudaEventRecord(tev[2], stream);
-    ++timing.calls;
+    KernelTiming::record(tev[2], stream);
+    timing->calls.fetch_add(1, std::memory_order_relaxed);
   }
   return cuda_status(cudaGetLastError());
 }

@@ -38,7 +38,10 @@ struct RelayoutArgs {
   int32_t vec_tiled;     // 1: 16-byte vector access to the tiled side is legal
   int64_t nblk1;         // blocks along dim 1
   int32_t use_bulk;      // constant-shape kernels: move whole matrix rows with bulk async copies
+  uint32_t* status;      // per-device status word; bit kStatusRelayoutTimeout on an expired wait
 };
+
+constexpr uint32_t kStatusRelayoutTimeout = 1u << 5;
 
 template <int ES> struct ElemT;
 template <> struct ElemT<1> { using type = uint8_t; };
@@ -276,17 +279,31 @@ __global__ void __launch_bounds__(256) relayout_staged_kernel(RelayoutArgs a) {
           "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
           :: "r"(sdst), "l"(g), "r"(row_bytes), "r"(bar) : "memory");
     }
-    // bounded wait for all rows of the block
-    const long long deadline = clock64() + (1ll << 31);
-    uint32_t done = 0;
-    while (!done && clock64() < deadline) {
-      asm volatile(
-          "{\n.reg .pred p;\n"
-          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n"
-          "selp.u32 %0, 1, 0, p;\n}\n"
-          : "=r"(done) : "r"(bar) : "memory");
+    // Bounded wait for all rows of the block. If it runs out, the block records that in the
+    // status word, writes nothing (its tiles would hold whatever had landed), gives its copies
+    // a second bounded wait so that none is still in flight into shared memory that is about
+    // to be released, and returns.
+    auto wait_rows = [&]() {
+      const long long deadline = clock64() + (1ll << 31);
+      uint32_t done = 0;
+      while (!done && clock64() < deadline) {
+        asm volatile(
+            "{\n.reg .pred p;\n"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n"
+            "selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(bar) : "memory");
+      }
+      return done != 0;
+    };
+    const bool landed = __syncthreads_and(wait_rows() ? 1 : 0) != 0;
+    if (!landed) {
+      if (threadIdx.x == 0) {
+        atomicOr(a.status, kStatusRelayoutTimeout);
+        wait_rows();
+      }
+      __syncthreads();
+      return;
     }
-    __syncthreads();
     tiled_phase();
     return;
   }
@@ -472,7 +489,8 @@ template <int ES, bool IS_PACK, class Shape>
 int launch_fixed(RelayoutArgs a, cudaStream_t stream) {
   a.R0 = Shape::R0; a.R1 = Shape::R1;
   a.nblk1 = a.outer1 / Shape::R1;
-  a.use_bulk = env_flag("IREE_UK_B200_NO_BULK_ROWS") ? 0 : 1;
+  a.status = device_status_word();
+  a.use_bulk = a.status ? 1 : 0;  // the bulk-row path reports an expired wait through the status word
   const int64_t blocks = a.nblk1 * (a.outer0 / Shape::R0);
   constexpr int pitch = staged_pitch_words(Shape::R1 * Shape::T1 * ES);
   constexpr size_t smem = size_t(Shape::R0) * Shape::T0 * pitch * 4;

@@ -71,8 +71,8 @@ struct TcParams {
   int32_t out_row_major; // fused matmul: the output is a row-major rows x cols matrix
   int32_t out_vec16;     // row-major output rows may be accessed with 16-byte vectors
   int64_t rows, cols;    // extent of the row-major output
-  uint32_t debug_flags;  // experiments only: 1 = no output stores, 2 = no TMEM reads, 4 = no TMA
-                         // loads, 8 = the producer never fills a stage (exercises the bounded waits)
+  int32_t starve;        // test hook: the producers never fill a stage, so the bounded waits run out
+  int64_t wait_cycles;   // clock64 ticks a device-side wait may take before it gives up
   uint32_t* status;
 };
 
@@ -123,9 +123,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. False when the deadline passed or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
-  const long long deadline = clock64() + kWaitCycles;
+  const long long deadline = clock64() + limit;
   while (!mbar_try_wait(bar, parity)) {
     if (*abort_flag || clock64() > deadline) return false;
   }
@@ -133,8 +134,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // The same wait executed by a whole converged warp with one shared verdict.
-__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag));
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               long long limit) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, limit));
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -221,6 +223,14 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
+}
+// Raises the abort flag of this CTA and of its peer in the pair, so that every role of both
+// CTAs leaves its loop at its next bounded wait instead of running its own wait out. The peer
+// cannot have exited: it leaves only through the cluster barrier that this CTA has not reached.
+__device__ __forceinline__ void raise_abort_pair(int* flag, uint32_t rank) {
+  *reinterpret_cast<volatile int*>(flag) = 1;
+  const uint32_t remote = mapa_shared(smem_u32(flag), rank ^ 1u);
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(1) : "memory");
 }
 // TMA load of one CTA of a pair; the completion bytes go to the mbarrier at `bar`, a
 // shared::cluster address that may belong to the peer CTA. No multicast.
@@ -349,7 +359,7 @@ __device__ __forceinline__ void epilogue_rows_rowmajor(const TcParams& P, uint32
     tmem_ld16(taddr0 + uint32_t(c * 16), r);
     tmem_ld_wait();
     const int64_t col = col0 + c * 16;
-    if (row >= P.rows || col >= P.cols || (P.debug_flags & 1u)) continue;
+    if (row >= P.rows || col >= P.cols) continue;
     uint32_t* dst = reinterpret_cast<uint32_t*>(P.out) + row * P.out_stride0 + col;
     if (P.out_vec32 && !P.accumulate && col + 16 <= P.cols) {
       // write-only, 32-byte aligned rows: two whole-sector stores
@@ -442,7 +452,7 @@ __device__ __forceinline__ void epilogue_rows_peers(const TcParams& P, uint32_t 
                       "r"(r[4 * v + 1]), "r"(r[4 * v + 2]), "r"(r[4 * v + 3]) : "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncwarp();
-    if (n1 < P.N1 && !(P.debug_flags & 1u)) {
+    if (n1 < P.N1) {
       for (int j = lane; j < copies; j += 32) {
         const int t = j & 1, g = (j >> 1) - 1;  // g = -1: the local output
         if (m1_first + t < P.M1) {
@@ -495,7 +505,7 @@ __device__ __forceinline__ void epilogue_rows_multicast(const TcParams& P, uint3
                    :: "r"(stage + uint32_t(lane) * 64u + uint32_t(v) * 16u), "r"(r[4 * v + 0]),
                       "r"(r[4 * v + 1]), "r"(r[4 * v + 2]), "r"(r[4 * v + 3]) : "memory");
     __syncwarp();
-    if (n1 < P.N1 && !(P.debug_flags & 1u)) {
+    if (n1 < P.N1) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {  // 4 x 512 bytes = the two 1 KB tiles
         const int t = i >> 1;
@@ -538,7 +548,7 @@ __device__ __forceinline__ void epilogue_rows_out16(const TcParams& P, uint32_t 
     tmem_ld16(taddr0 + uint32_t(c * 16), r);
     tmem_ld_wait();
     const int64_t n1 = n1_0 + c;
-    if (m1 < P.M1 && n1 < P.N1 && !(P.debug_flags & 1u)) {
+    if (m1 < P.M1 && n1 < P.N1) {
       uint4* d4 = reinterpret_cast<uint4*>(P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 2);
       uint32_t w[8];
       if (P.accumulate) {
@@ -567,7 +577,6 @@ __device__ __forceinline__ void epilogue_rows_out16(const TcParams& P, uint32_t 
 __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0, int64_t row,
                                               int64_t n1_0, int chunks, uint32_t epi_stage,
                                               int lane) {
-  if (P.debug_flags & 2u) return;
   if (P.use_multicast) {
     epilogue_rows_multicast(P, taddr0, row, n1_0, chunks, epi_stage, lane);
     return;
@@ -591,7 +600,7 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
     tmem_ld16(taddr0 + uint32_t(c * 16), r);
     tmem_ld_wait();
     const int64_t n1 = n1_0 + c;
-    if (m1 < P.M1 && n1 < P.N1 && !(P.debug_flags & 1u)) {
+    if (m1 < P.M1 && n1 < P.N1) {
       char* dst = P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4;
       if (P.out_vec32) {
         // 32-byte accesses: every store fills a whole 32-byte sector.
@@ -636,7 +645,6 @@ __device__ __forceinline__ void epilogue_rows(const TcParams& P, uint32_t taddr0
 __device__ __forceinline__ void epilogue_rows_dual(const TcParams& P, uint32_t taddr_hi,
                                                    uint32_t taddr_lo, int64_t row, int64_t col0,
                                                    int chunks) {
-  if (P.debug_flags & 2u) return;
   const int64_t ncols = P.N1 * 32;
   for (int c = 0; c < chunks; ++c) {
     uint32_t h[16], r[16];
@@ -646,7 +654,7 @@ __device__ __forceinline__ void epilogue_rows_dual(const TcParams& P, uint32_t t
 #pragma unroll
     for (int j = 0; j < 16; ++j) r[j] += h[j] << 8;
     const int64_t col = col0 + c * 16;
-    if (row < P.M1 && col < ncols && !(P.debug_flags & 1u)) {
+    if (row < P.M1 && col < ncols) {
       uint4* d4 = reinterpret_cast<uint4*>(P.out + (row * P.out_stride0 + col) * 4);
       if (P.accumulate) {
 #pragma unroll

@@ -58,6 +58,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
+  const long long wait_limit = P.wait_cycles;
   pdl_wait();
 
   if (warp == 0) {
@@ -76,7 +77,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
         int ca[3] = {mt * sa_st.tstep[0], mt * sa_st.tstep[1], mt * sa_st.tstep[2]};
         int cb[3] = {nt * sb_st.tstep[0], nt * sb_st.tstep[1], nt * sb_st.tstep[2]};
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_warp(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
+          if (!mbar_wait_warp(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, wait_limit)) {
             if (lane == 0) atomicOr(P.status, kStatusProducerTimeout);
             abort_flag = 1;
             ok = false;
@@ -84,15 +85,11 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           }
           const uint32_t bar = smem_u32(&full_bar[stage]);
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
-          const bool starve = (P.debug_flags & 8u) != 0;  // test hook: nothing ever arrives
+          const bool starve = P.starve != 0;  // test hook: nothing ever arrives
           if (!starve && elect_one()) {
-            if (P.debug_flags & 4u) {
-              mbar_arrive(bar);
-            } else {
-              mbar_expect_tx(bar, stage_bytes);
-              issue_operand_loads<false>(&P.map_a, sa_st, sa, bar, ca);
-              issue_operand_loads<false>(&P.map_b, sb_st, sa + a_bytes, bar, cb);
-            }
+            mbar_expect_tx(bar, stage_bytes);
+            issue_operand_loads<false>(&P.map_a, sa_st, sa, bar, ca);
+            issue_operand_loads<false>(&P.map_b, sb_st, sa + a_bytes, bar, cb);
           }
           __syncwarp();
 #pragma unroll
@@ -108,7 +105,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           const long long idx = issued - 1 - i;
           const int s = int(idx % S);
           const uint32_t par = uint32_t((idx / S) & 1);
-          const long long deadline = clock64() + kWaitCycles;
+          const long long deadline = clock64() + wait_limit;
           while (!mbar_try_wait(smem_u32(&full_bar[s]), par)) {
             if (clock64() > deadline) { atomicOr(P.status, kStatusDrainTimeout); break; }
           }
@@ -127,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
       const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
       const int num_kb = P.num_kb;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
+        if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp, wait_limit)) {
           if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
           abort_flag = 1;
           break;
@@ -135,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn * (mi.dual ? 2 : 1));
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
+          if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp, wait_limit)) {
             if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
             abort_flag = 1;
             ok = false;
@@ -170,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
       int mt, nt;
       tile_coords(P, tile, &mt, &nt);
       // Warp-uniform outcome: tcgen05.ld below needs all 32 lanes.
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp))) {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp, wait_limit))) {
         if (lane == 0) atomicOr(P.status, kStatusEpilogueTimeout);
         abort_flag = 1;
         break;
@@ -357,6 +354,7 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
+  const long long wait_limit = P.wait_cycles;
   pdl_wait();
 
   if (warp < kSwProducerWarps) {
@@ -378,14 +376,14 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
         if (int(seq % kSwGroups) != group) continue;
         const int stage = int(seq % S);
         const uint32_t phase = uint32_t((seq / S) & 1);
-        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
+        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, wait_limit)) {
           atomicOr(P.status, kStatusProducerTimeout);
           abort_flag = 1;
           ok = false;
           break;
         }
         const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
-        if (!(P.debug_flags & 4u)) {
+        {
           const int64_t k1_0 = int64_t(kb) * kps;
           SwStageSrc src;
           src.a = P.src_a + a0 * P.src_stride_a + k1_0 * (16 * G);
@@ -400,7 +398,7 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
         }
         // make the generic-proxy stores visible to the tensor core (async proxy), then signal
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (!(P.debug_flags & 8u)) mbar_arrive(smem_u32(&full_bar[stage]));
+        if (!P.starve) mbar_arrive(smem_u32(&full_bar[stage]));
       }
     }
   } else if (warp == kSwMmaWarp) {
@@ -414,7 +412,7 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
     const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
     const int num_kb = P.num_kb;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
+      if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp, wait_limit)) {
         if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
         abort_flag = 1;
         break;
@@ -422,7 +420,7 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn);
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
+        if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp, wait_limit)) {
           if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
           abort_flag = 1;
           ok = false;
@@ -452,7 +450,7 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int mt, nt;
       tile_coords(P, tile, &mt, &nt);
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp))) {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp, wait_limit))) {
         if (lane == 0) atomicOr(P.status, kStatusEpilogueTimeout);
         abort_flag = 1;
         break;
@@ -532,6 +530,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
+  const long long wait_limit = P.wait_cycles;
   pdl_wait();
 
   if (warp == 0) {
@@ -555,30 +554,35 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
           cb[i] = nt * sb_st.tstep[i] + r * sb_st.rstep[i];
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_warp(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp)) {
+          if (!mbar_wait_warp(smem_u32(&empty_bar[stage]), phase ^ 1u, abortp, wait_limit)) {
             if (lane == 0) atomicOr(P.status, kStatusProducerTimeout);
-            abort_flag = 1;
+            raise_abort_pair(&abort_flag, rank);
             ok = false;
             break;
           }
           const uint32_t own_bar = smem_u32(&full_bar[stage]);
           const uint32_t bar = mapa_shared(own_bar, 0);
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
-          if (elect_one()) {
-            if (P.debug_flags & 4u) {
-              if (leader) mbar_arrive(own_bar);
-            } else {
-              if (leader) mbar_expect_tx(own_bar, 2u * stage_bytes);
-              issue_operand_loads<true>(&P.map_a, sa_st, sa, bar, ca);
-              issue_operand_loads<true>(&P.map_b, sb_st, sa + a_bytes, bar, cb);
-            }
+          const bool starve = P.starve != 0;  // test hook: nothing ever arrives
+          if (!starve && elect_one()) {
+            if (leader) mbar_expect_tx(own_bar, 2u * stage_bytes);
+            issue_operand_loads<true>(&P.map_a, sa_st, sa, bar, ca);
+            issue_operand_loads<true>(&P.map_b, sb_st, sa + a_bytes, bar, cb);
           }
           __syncwarp();
 #pragma unroll
           for (int i = 0; i < 3; ++i) { ca[i] += sa_st.kstep[i]; cb[i] += sb_st.kstep[i]; }
-          ++issued;
+          if (!starve) ++issued;
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
+      }
+      if ((!ok || *abortp) && !leader && lane == 0 && issued > 0) {
+        // Aborting: this CTA's copies complete on the leader's barriers, which only the leader can
+        // wait on, and the two producers may have left their loops at different stages. Give the
+        // copies this CTA issued last a fixed grace period (a TMA load lands within microseconds)
+        // before the cluster barrier below lets its shared memory go.
+        const long long until = clock64() + (1ll << 18);
+        while (clock64() < until) {}
       }
       if ((!ok || *abortp) && leader && lane == 0) {
         // Aborting: the leader's full barriers count the copies of both CTAs; let them land
@@ -589,7 +593,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
           const long long idx = issued - 1 - i;
           const int s = int(idx % S);
           const uint32_t par = uint32_t((idx / S) & 1);
-          const long long deadline = clock64() + kWaitCycles;
+          const long long deadline = clock64() + wait_limit;
           while (!mbar_try_wait(smem_u32(&full_bar[s]), par)) {
             if (clock64() > deadline) { atomicOr(P.status, kStatusDrainTimeout); break; }
           }
@@ -608,17 +612,17 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
       const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
       const int num_kb = P.num_kb;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp)) {
+        if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp, wait_limit)) {
           if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
-          abort_flag = 1;
+          raise_abort_pair(&abort_flag, rank);
           break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn * (mi.dual ? 2 : 1));
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp)) {
+          if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp, wait_limit)) {
             if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
-            abort_flag = 1;
+            raise_abort_pair(&abort_flag, rank);
             ok = false;
             break;
           }
@@ -649,9 +653,9 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc2_kernel(const __grid_con
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
       int mt, nt;
       tile_coords(P, tile, &mt, &nt);
-      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp))) {
+      if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp, wait_limit))) {
         if (lane == 0) atomicOr(P.status, kStatusEpilogueTimeout);
-        abort_flag = 1;
+        raise_abort_pair(&abort_flag, rank);
         break;
       }
       tc_fence_after();

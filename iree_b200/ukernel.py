@@ -249,6 +249,36 @@ def device_status(stream=None):
     return st, int(detail.value)
 
 
+def kernel_timing(every):
+    """Every ``every``-th later tensor-core mmt4d call on the current device records CUDA events
+    around its pre-pass and its main kernel (0 switches the recording off)."""
+    _check(lib.iree_uk_b200_kernel_timing(int(every)), "kernel_timing")
+
+
+def kernel_timing_mean_ms():
+    """(mean pre-pass ms, mean main-kernel ms, calls) over the remembered recorded calls."""
+    a, b, n = C.c_float(0), C.c_float(0), C.c_int(0)
+    _check(lib.iree_uk_b200_kernel_timing_mean_ms(C.addressof(a), C.addressof(b), C.addressof(n)),
+           "kernel_timing_mean_ms")
+    return float(a.value), float(b.value), int(n.value)
+
+
+FORM_TWO_CTA, FORM_ONE_CTA, FORM_TWO_CTA_HYBRID = 5, 6, 7
+
+
+def testing_starve_producers(enable):
+    """Test hook: the producers of the tensor-core kernels fill nothing while enabled, so the
+    bounded device-side waits run out. Returns the previous setting."""
+    return int(lib.iree_uk_b200_testing_starve_producers(1 if enable else 0))
+
+
+def testing_mmt4d_form(params, workspace, form, stream=None):
+    """Test hook: a tensor-core mmt4d on one given kernel form (``FORM_*``)."""
+    _check(lib.iree_uk_b200_testing_mmt4d_form(C.addressof(params), workspace.data_ptr(),
+                                               workspace.numel() * workspace.element_size(), form,
+                                               _stream_handle(stream)), "testing_mmt4d_form")
+
+
 def shard_params(full, rank, world, rhs_is_local=False, out_is_local=True):
     """Parameters of ``rank`` when the RHS tile rows (N) are split across ``world`` GPUs.
     Returns (params, first owned tile row)."""

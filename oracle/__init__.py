@@ -21,7 +21,17 @@ from iree_b200 import abi
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ORACLE_SO = os.path.join(_HERE, "libuk_oracle.so")
 _REF_SO = os.path.join(_HERE, "_ref", "libiree_uk_ref.so")
-_DEFAULT_REF_SRC = "/root/reference/runtime/src"
+
+
+def _reference_src():
+    """``runtime/src`` of a reference checkout: the IREE_REFERENCE_SRC environment variable, or
+    a checkout named ``reference`` beside this repository; None when neither exists."""
+    cands = [os.environ.get("IREE_REFERENCE_SRC"),
+             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference", "runtime", "src")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "iree", "builtins", "ukernel")):
+            return c
+    return None
 
 _oracle = None
 _ref = None
@@ -31,8 +41,8 @@ def build(reference_src=None, quiet=True):
     """Compile the C restatement, and the reference ukernels when a checkout is present."""
     out = subprocess.DEVNULL if quiet else None
     subprocess.check_call(["make", "-C", _HERE, "oracle"], stdout=out)
-    src = reference_src or os.environ.get("IREE_REFERENCE_SRC", _DEFAULT_REF_SRC)
-    if os.path.isdir(os.path.join(src, "iree", "builtins", "ukernel")):
+    src = reference_src or _reference_src()
+    if src:
         subprocess.check_call(["make", "-C", _HERE, "ref", "REF=" + src], stdout=out)
 
 

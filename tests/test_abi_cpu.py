@@ -15,14 +15,39 @@ from oracle import cases
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _declared(header_name):
+    header = open(os.path.join(ROOT, "include", header_name)).read()
+    return set(re.findall(r"\b(iree_uk_b200_[a-z0-9_]+)\s*\(", header))
+
+
 def test_library_exports_every_declared_symbol():
-    header = open(os.path.join(ROOT, "include", "iree_uk_b200.h")).read()
-    declared = set(re.findall(r"\b(iree_uk_b200_[a-z0-9_]+)\s*\(", header))
+    from iree_b200._lib import TESTING_SIGNATURES
+    declared = _declared("iree_uk_b200.h")
     assert declared, "no declarations found"
     assert declared == set(SIGNATURES), declared ^ set(SIGNATURES)
-    for name in declared:
+    testing = _declared("iree_uk_b200_testing.h")
+    assert testing == set(TESTING_SIGNATURES), testing ^ set(TESTING_SIGNATURES)
+    for name in declared | testing:
         assert getattr(lib, name) is not None
     assert b"sm_100a" in lib.iree_uk_b200_version()
+    # and nothing else is exported under the library's prefix
+    import subprocess
+    from iree_b200._lib import LIB_PATH
+    out = subprocess.run(["nm", "-D", "--defined-only", LIB_PATH], capture_output=True, text=True)
+    if out.returncode == 0:
+        exported = set(re.findall(r"\b(iree_uk_b200_[a-z0-9_]+)\b", out.stdout))
+        assert exported == declared | testing, exported ^ (declared | testing)
+
+
+def test_workspace_entry_point_reports_bad_arguments_without_launching():
+    """A NULL params pointer is an invalid argument, not a crash; an offered workspace that is
+    too small for the kernel that would use it is refused instead of being ignored."""
+    assert lib.iree_uk_b200_mmt4d_ws(None, 0x40000, 1 << 20, None) == abi.INVALID_ARGUMENT
+    assert lib.iree_uk_b200_mmt4d_ws(None, None, 0, None) == abi.INVALID_ARGUMENT
+    p = _mmt4d()
+    need = uk.mmt4d_workspace_size(p)
+    assert need > 256
+    assert lib.iree_uk_b200_mmt4d_ws(C.addressof(p), 0x40000, need - 1, None) == abi.WORKSPACE_TOO_SMALL
 
 
 def test_struct_layouts_match_reference():

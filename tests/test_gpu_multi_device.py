@@ -75,6 +75,11 @@ def test_sharded_with_replication_every_buffer_holds_everything(world, t, K0):
 
 
 def _multicast_worker(rank, world, port):
+    """One rank of the multicast test. No rank raises, leaves or tears the process group down
+    while any rank's buffer is still bound to the multicast object or any kernel may still be
+    storing through it: each rank computes a local verdict without raising, the verdicts are
+    combined with an all-reduce so that every rank takes the same path, the multicast object
+    is released after a last barrier, and only then does a failed rank assert."""
     import os
     import torch
     import torch.distributed as dist
@@ -83,28 +88,47 @@ def _multicast_worker(rank, world, port):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world,
                             device_id=torch.device("cuda", rank))
+    from iree_b200 import sharding, ukernel as uk
+    ok, why, mc = True, "", None
     try:
-        from iree_b200 import sharding, ukernel as uk
         case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 20, 24, 40, 0, seed=21, mode="normal",
                                loose=False)
         want = G.oracle_mmt4d(case)
         mc = sharding.MulticastOutput(case.out_init.nbytes, torch.uint8)
-        assert mc.multicast_ptr, "no multicast mapping on this system"
-        mc.tensor.copy_(torch.from_numpy(case.out_init.view(np.uint8)))
-        lhs, rhs = G.to_device(case.lhs), G.to_device(case.rhs)
-        torch.cuda.synchronize()
-        dist.barrier()
-        full = case.params(lhs.data_ptr(), rhs.data_ptr(), mc.tensor.data_ptr())
-        p, _ = uk.shard_params(full, rank, world, rhs_is_local=False, out_is_local=False)
-        ws = torch.empty(max(uk.mmt4d_workspace_size(p), 256), dtype=torch.uint8, device="cuda")
-        uk.mmt4d_multicast(p, mc.multicast_ptr, ws)
-        torch.cuda.synchronize()
-        dist.barrier()   # every rank's tiles have landed in every buffer
-        assert uk.device_status() == (0, 0)
-        assert np.array_equal(mc.tensor.cpu().numpy(), want.view(np.uint8))
-        dist.barrier()
-    finally:
-        dist.destroy_process_group()
+        have_mc = torch.tensor([1 if mc.multicast_ptr else 0], device="cuda")
+        dist.all_reduce(have_mc, op=dist.ReduceOp.MIN)
+        if int(have_mc.item()) == 0:
+            ok, why = False, "no multicast mapping on this system"
+        else:
+            mc.tensor.copy_(torch.from_numpy(case.out_init.view(np.uint8)))
+            lhs, rhs = G.to_device(case.lhs), G.to_device(case.rhs)
+            torch.cuda.synchronize()
+            dist.barrier()
+            full = case.params(lhs.data_ptr(), rhs.data_ptr(), mc.tensor.data_ptr())
+            p, _ = uk.shard_params(full, rank, world, rhs_is_local=False, out_is_local=False)
+            ws = torch.empty(max(uk.mmt4d_workspace_size(p), 256), dtype=torch.uint8, device="cuda")
+            try:
+                uk.mmt4d_multicast(p, mc.multicast_ptr, ws)
+            except uk.UkernelError as e:
+                ok, why = False, repr(e)
+            torch.cuda.synchronize()
+            dist.barrier()   # every rank's tiles have landed in every buffer
+            if ok and uk.device_status() != (0, 0):
+                ok, why = False, "device status"
+            if ok and not np.array_equal(mc.tensor.cpu().numpy(), want.view(np.uint8)):
+                ok, why = False, "rank %d: buffer differs from the reference result" % rank
+    except Exception as e:  # reported after the orderly teardown below
+        ok, why = False, repr(e)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    dist.barrier()
+    mc = None  # released only now: no rank is still storing through the mapping
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    assert ok, why
+    assert int(flag.item()) == 1, "another rank failed"
 
 
 def test_multicast_replication_two_processes():

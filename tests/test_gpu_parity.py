@@ -439,42 +439,76 @@ def test_concurrent_host_threads_on_their_own_streams():
     G.check_device_status()
 
 
-@pytest.mark.parametrize("use_ws", [True, False], ids=["tma_kernel", "scratch_free_kernel"])
-def test_bounded_waits_report_a_timeout_instead_of_hanging(use_ws):
-    """Failure detection without faulting the GPU: a test hook makes the producer (TMA, or the
-    producer warps of the scratch-free kernel) never fill a stage, so the MMA warp's wait on the
-    full barrier runs out (about a second); the kernel must record the timeout, return, leave
-    the context usable, and the next call must be correct. Runs in a child process because the
-    hook is read from the environment."""
-    import subprocess
-    import sys
-    code = r"""
-import os, sys
-os.environ["IREE_UK_B200_DEBUG"] = "1"
-os.environ["IREE_UK_B200_DEBUG_FLAGS"] = "8"
-sys.path.insert(0, %r)
-USE_WS = %r
-import numpy as np, torch
-import oracle
-from oracle import cases
-from iree_b200 import abi, ukernel as uk
-case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 64, 0, seed=5, loose=False)
-def run():
-    lhs, rhs, out = (torch.from_numpy(x).cuda() for x in (case.lhs, case.rhs, case.out_init))
+@pytest.mark.parametrize("kernel", ["one_cta", "two_cta", "scratch_free"])
+def test_bounded_waits_report_a_timeout_instead_of_hanging(kernel):
+    """Failure detection without faulting the GPU: a test hook makes the producers (the TMA warp,
+    or the producer warps of the scratch-free kernel) never fill a stage, so the waits of the
+    other roles run out (tens of milliseconds with the hook set); every kernel form must record
+    the timeout, return, leave the context usable, and the next call must be correct. The
+    two-CTA case has more tiles than CTA pairs, so both CTAs of every pair are mid-schedule
+    when their waits expire."""
+    import torch
+    from iree_b200 import ukernel as uk
+    if kernel == "two_cta":
+        case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 320, 96, 4, 0, seed=5, loose=False)
+    else:
+        case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 64, 0, seed=5, loose=False)
+    want = G.oracle_mmt4d(case)
+
+    def run():
+        lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
+        p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+        if kernel == "scratch_free":
+            assert uk.mmt4d_path(p, False) == abi.PATH_TCGEN05
+            uk.mmt4d(p)
+        else:
+            ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda")
+            uk.testing_mmt4d_form(p, ws, uk.FORM_TWO_CTA if kernel == "two_cta" else uk.FORM_ONE_CTA)
+        st, detail = uk.device_status()
+        return st, detail, out.cpu().numpy()
+
+    G.check_device_status()
+    uk.testing_starve_producers(True)
+    try:
+        st, detail, _ = run()
+    finally:
+        uk.testing_starve_producers(False)
+    assert st == abi.DEVICE_TIMEOUT and detail != 0, (st, detail)
+    st, detail, got = run()
+    assert st == abi.OK and detail == 0, (st, detail)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("form", ["one_cta", "two_cta"])
+@pytest.mark.parametrize("t,K0,mode", [(abi.MMT4D_S8S8S32, 2, "exact"), (abi.MMT4D_BF16BF16F32, 2, "exact"),
+                                       (abi.MMT4D_F16F16F32, 1, "exact")], ids=["s8", "bf16", "f16"])
+@pytest.mark.parametrize("shape", [(1, 1, 1), (17, 9, 65), (40, 33, 130)], ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_every_kernel_form_on_small_problems(form, t, K0, mode, shape, accumulate):
+    """The library picks the kernel form by problem size; here both TMA-fed forms run the same
+    small, ragged problems and must give the reference's bytes."""
+    import torch
+    from iree_b200 import ukernel as uk
+    M, N, K = shape
+    case = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, accumulate, seed=31, mode=mode, loose=False)
+    lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
     p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
-    ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda") if USE_WS else None
-    assert uk.mmt4d_path(p, USE_WS) == (abi.PATH_TCGEN05_RETILE if USE_WS else abi.PATH_TCGEN05)
-    uk.mmt4d(p, workspace=ws)
-    st, detail = uk.device_status()
-    return st, detail, out.cpu().numpy()
-st, detail, _ = run()
-assert st == abi.DEVICE_TIMEOUT and detail != 0, (st, detail)
-os.environ["IREE_UK_B200_DEBUG_FLAGS"] = "0"
-st, detail, got = run()
-assert st == abi.OK and detail == 0, (st, detail)
-want = case.out_init.copy(); oracle.mmt4d(case.params(case.lhs, case.rhs, want))
-assert np.array_equal(got, want)
-print("TIMEOUT_REPORTED_AND_RECOVERED")
-""" % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), use_ws)
-    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
-    assert "TIMEOUT_REPORTED_AND_RECOVERED" in r.stdout, r.stdout + r.stderr
+    ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda")
+    uk.testing_mmt4d_form(p, ws, uk.FORM_TWO_CTA if form == "two_cta" else uk.FORM_ONE_CTA)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), G.oracle_mmt4d(case)), case.label()
+
+
+def test_undersized_workspace_is_refused_not_served_by_a_slower_kernel():
+    import torch
+    from iree_b200 import ukernel as uk
+    case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 64, 0, seed=5, loose=False)
+    lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
+    p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+    need = uk.mmt4d_workspace_size(p)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    with pytest.raises(uk.UkernelError) as e:
+        uk.mmt4d(p, workspace=ws[:need - 256])
+    assert e.value.status == abi.WORKSPACE_TOO_SMALL
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), case.out_init)

@@ -55,6 +55,33 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
     G.check_device_status()
 
 
+def test_static_scratch_runs_s16u4_with_many_rows_on_the_tensor_cores():
+    """s16u4s32 1x32x8 with at least 32 rows is a scratch-using tensor-core problem for
+    iree_uk_b200_mmt4d_ws, so it must be one here too (same kernel choice, same bytes), and a
+    problem of that kind that does not fit the array must be refused."""
+    case = cases.Mmt4dCase(abi.MMT4D_S16U4S32, 1, 32, 8, 200, 7, 33, 1, seed=24, mode="normal",
+                           loose=False)
+    for _ in range(2):
+        got, want = _run_both(case)
+        assert np.array_equal(got, want)
+        assert np.array_equal(got, G.oracle_mmt4d(case))
+    G.check_device_status()
+    M, N, K = 4096, 448, 512  # 2 x 16 MiB byte planes + 56 MiB of widened weights
+    lhs = torch.zeros(M * K * 8, dtype=torch.int16, device="cuda")
+    rhs = torch.zeros(N * K * 128, dtype=torch.uint8, device="cuda")
+    out = torch.full((M * N * 32,), 7, dtype=torch.int32, device="cuda")
+    p = abi.Mmt4dParams()
+    p.lhs_buffer, p.rhs_buffer, p.out_buffer = lhs.data_ptr(), rhs.data_ptr(), out.data_ptr()
+    p.M, p.N, p.K, p.M0, p.N0, p.K0, p.flags = M, N, K, 1, 32, 8, abi.MMT4D_S16U4S32
+    p.lhs_stride0, p.rhs_stride0, p.out_stride0 = K * 8, K * 256, N * 32
+    assert uk.mmt4d_workspace_size(p) > uk.STATIC_SCRATCH_BYTES
+    with pytest.raises(uk.UkernelError) as e:
+        uk.mmt4d_static_scratch(p)
+    assert e.value.status == abi.WORKSPACE_TOO_SMALL
+    torch.cuda.synchronize()
+    assert bool((out == 7).all())
+
+
 def test_static_scratch_refuses_oversized_problem():
     M, N, K = 256, 256, 4096  # needs 64 MiB of re-tiled operands
     lhs = torch.zeros(M * K * 16, dtype=torch.float16, device="cuda")
