@@ -24,9 +24,9 @@ IREE_UK_B200_EXPORT int iree_uk_b200_testing_starve_producers(int enable);
  * instead of the form the library would choose by problem size, so that every form can be
  * checked on small problems. IREE_UK_B200_UNSUPPORTED when the problem is not a tensor-core
  * problem or the form cannot run it. */
-#define IREE_UK_B200_TESTING_FORM_TWO_CTA 5        /* CTA pairs, both operands by TMA */
-#define IREE_UK_B200_TESTING_FORM_ONE_CTA 6        /* one CTA per tile */
-#define IREE_UK_B200_TESTING_FORM_TWO_CTA_HYBRID 7 /* CTA pairs, LHS re-tiled in the kernel */
+#define IREE_UK_B200_TESTING_FORM_TWO_CTA 5          /* CTA pairs, whole re-tile in the pre-pass */
+#define IREE_UK_B200_TESTING_FORM_ONE_CTA 6          /* one CTA per tile */
+#define IREE_UK_B200_TESTING_FORM_TWO_CTA_STREAMED 7 /* CTA pairs, re-tile finished by the kernel */
 IREE_UK_B200_EXPORT int iree_uk_b200_testing_mmt4d_form(const iree_uk_mmt4d_params_t* params,
                                                         void* workspace, size_t workspace_bytes,
                                                         int form, void* cu_stream);

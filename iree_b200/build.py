@@ -35,8 +35,18 @@ def _newer(target, deps):
 
 
 def build(verbose=False, ptxas_info=False):
-    """Compile and link the library; returns its path."""
+    """Compile and link the library; returns its path. With IREE_UK_B200_EXPERIMENTS set in the
+    environment the tuning overrides (environment variables read at run time, used for
+    parameter sweeps) are compiled in; the ordinary build has none."""
     os.makedirs(OBJ_DIR, exist_ok=True)
+    experiments = bool(os.environ.get("IREE_UK_B200_EXPERIMENTS"))
+    stamp = os.path.join(OBJ_DIR, "experiments" if experiments else "product")
+    other = os.path.join(OBJ_DIR, "product" if experiments else "experiments")
+    if os.path.exists(other) or not os.path.exists(stamp):  # flavour changed: rebuild everything
+        for f in glob.glob(os.path.join(OBJ_DIR, "*.o")) + [other]:
+            if os.path.exists(f):
+                os.remove(f)
+        open(stamp, "w").close()
     headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh")) + \
         [os.path.join(_HERE, "..", "include", "iree_uk_b200.h")]
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cc")))
@@ -46,6 +56,7 @@ def build(verbose=False, ptxas_info=False):
         objs.append(obj)
         if _newer(obj, [src] + headers):
             cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + \
+                (["-DIREE_UK_B200_EXPERIMENTS"] if experiments else []) + \
                 ["-x", "cu", "-c", src, "-o", obj]
             if verbose:
                 print(" ".join(cmd), flush=True)

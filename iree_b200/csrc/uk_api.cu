@@ -676,7 +676,7 @@ int iree_uk_b200_testing_mmt4d_form(const iree_uk_mmt4d_params_t* params, void* 
   const int rc = validate_mmt4d(params);
   if (rc) return rc;
   if (form != IREE_UK_B200_TESTING_FORM_ONE_CTA && form != IREE_UK_B200_TESTING_FORM_TWO_CTA &&
-      form != IREE_UK_B200_TESTING_FORM_TWO_CTA_HYBRID)
+      form != IREE_UK_B200_TESTING_FORM_TWO_CTA_STREAMED)
     return IREE_UK_B200_INVALID_ARGUMENT;
   if (params->M < 1 || params->N < 1 || params->K < 1) return IREE_UK_B200_UNSUPPORTED;
   if (!mmt4d_tc_eligible(params)) return IREE_UK_B200_UNSUPPORTED;

@@ -88,6 +88,9 @@ int launch_mmt4d_tc_sw(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
 int f32_mode();
 constexpr int kTcVariantDefault = 0;
 constexpr int kTcVariantDirect = 3;  // MN-major, 32-byte swizzle, straight from the operand
+constexpr int kTcVariantTwoCta = 5;  // CTA pairs, both operands by TMA from re-tiled scratch
+constexpr int kTcVariantOneCta = 6;  // one CTA per tile, both operands by TMA
+constexpr int kTcVariantStreamed = 7;  // CTA pairs; the kernel's own workers finish the re-tile
 // f16f16f32 / bf16bf16f32 with M0 = N0 = 16 and K0 = 1: served by the tensor cores without scratch.
 bool mmt4d_tc_direct_eligible(const iree_uk_mmt4d_params_t* p);
 

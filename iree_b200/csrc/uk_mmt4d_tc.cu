@@ -29,8 +29,8 @@
 
 #include "uk_common.h"
 #include "uk_tc_device.cuh"
-#include "uk_tc_kernels.cuh"
 #include "uk_tc_prepass.cuh"
+#include "uk_tc_kernels.cuh"
 
 namespace uk {
 namespace {
@@ -107,12 +107,25 @@ uint32_t make_idesc(const TypeInfo& ti, int n, bool mn_major, int m = BM) {
          (uint32_t(mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
-// Co-resident 2-CTA clusters of the pair kernel on the current device (0 on failure).
-template <bool IS_INT>
-int max_pair_clusters(size_t smem) {
+// The two-CTA kernel's instantiations: [is_int][form], form 0 = everything re-tiled by the
+// pre-pass kernel, 1 / 2 = streamed pre-pass (the kernel's own workers finish the re-tile) for
+// 2- / 4-byte granules.
+using PairKernel = void (*)(const TcParams);
+constexpr int kPairForms = 3;
+int streamed_form_of_granule(int G) { return G == 2 ? 1 : (G == 4 ? 2 : 0); }
+PairKernel pair_kernel(bool is_int, int form) {
+  static const PairKernel table[2][kPairForms] = {
+      {mmt4d_tc2_kernel<false, 0>, mmt4d_tc2_kernel<false, 2>, mmt4d_tc2_kernel<false, 4>},
+      {mmt4d_tc2_kernel<true, 0>, mmt4d_tc2_kernel<true, 2>, mmt4d_tc2_kernel<true, 4>}};
+  return table[is_int ? 1 : 0][form];
+}
+int pair_threads(int form) { return form ? kStreamedThreads : kThreads; }
+
+// Co-resident 2-CTA clusters of a pair kernel on the current device (0 on failure).
+int max_pair_clusters(PairKernel kernel, int threads, size_t smem) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2, 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(unsigned(threads), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -122,7 +135,7 @@ int max_pair_clusters(size_t smem) {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, mmt4d_tc2_kernel<IS_INT>, &cfg) != cudaSuccess) return 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) return 0;
   return n;
 }
 
@@ -133,7 +146,7 @@ struct DeviceInfo {
   bool ok = false;
   int sms = 0;
   int max_smem = 0;           // dynamic shared memory per block the kernels may be launched with
-  int pair_clusters[2] = {};  // co-resident CTA pairs of mmt4d_tc2_kernel<false / true>
+  int pair_clusters[2][kPairForms] = {};  // co-resident CTA pairs of mmt4d_tc2_kernel [is_int][form]
 };
 
 const DeviceInfo* device_info() {
@@ -157,17 +170,20 @@ const DeviceInfo* device_info() {
       dyn_limit = std::min(dyn_limit, dyn);
       return cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn) == cudaSuccess;
     };
-    if (!raise_limit(reinterpret_cast<const void*>(mmt4d_tc_kernel<false>)) ||
-        !raise_limit(reinterpret_cast<const void*>(mmt4d_tc_kernel<true>)) ||
-        !raise_limit(reinterpret_cast<const void*>(mmt4d_tc2_kernel<false>)) ||
-        !raise_limit(reinterpret_cast<const void*>(mmt4d_tc2_kernel<true>))) {
+    bool raised = raise_limit(reinterpret_cast<const void*>(mmt4d_tc_kernel<false>)) &&
+                  raise_limit(reinterpret_cast<const void*>(mmt4d_tc_kernel<true>));
+    for (int i = 0; i < 2 && raised; ++i)
+      for (int f = 0; f < kPairForms && raised; ++f)
+        raised = raise_limit(reinterpret_cast<const void*>(pair_kernel(i != 0, f)));
+    if (!raised) {
       cudaGetLastError();
       return nullptr;
     }
     d.max_smem = dyn_limit;
     const size_t smem_probe = size_t(6) * (BM * 128 + 128 * 128) + 1024;
-    d.pair_clusters[0] = max_pair_clusters<false>(smem_probe);
-    d.pair_clusters[1] = max_pair_clusters<true>(smem_probe);
+    for (int i = 0; i < 2; ++i)
+      for (int f = 0; f < kPairForms; ++f)
+        d.pair_clusters[i][f] = max_pair_clusters(pair_kernel(i != 0, f), pair_threads(f), smem_probe);
     d.ok = true;
   }
   return &d;
@@ -289,10 +305,10 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(uint4* __restrict__ hi,
 // enqueued just before it (see pdl_wait).
 template <typename Kernel>
 cudaError_t launch_main(Kernel kernel, int grid, int cluster, size_t smem, cudaStream_t stream,
-                        const TcParams& P) {
+                        const TcParams& P, int threads = kThreads) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(unsigned(grid), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(unsigned(threads), 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -352,7 +368,7 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   // buffered = all 512 TMEM columns) once every pair has a tile; the one-CTA form otherwise.
   const DeviceInfo* di = device_info();
   if (!di) return IREE_UK_B200_CUDA_ERROR;
-  const int pair_clusters = di->pair_clusters[1];
+  const int pair_clusters = di->pair_clusters[1][0];
   const bool pair = bn == 128 && p->M >= 256 && pair_clusters >= 1 &&
                     ((p->M + 255) / 256) * ((ncols + 127) / 128) >= 74 &&
                     !debug_int("IREE_UK_B200_DEBUG_S16U4_ONE_CTA", 0);
@@ -401,7 +417,7 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   cudaError_t e;
   if (pair) {
     const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
-    e = launch_main(mmt4d_tc2_kernel<true>, grid, 2, smem, stream, P);
+    e = launch_main(pair_kernel(true, 0), grid, 2, smem, stream, P);
   } else {
     const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
     e = launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P);
@@ -445,6 +461,13 @@ bool mmt4d_tc_direct_eligible(const iree_uk_mmt4d_params_t* p) {
   return tc_type_info(p->flags, &ti) && ti.es == 2 && p->K0 == 1 && mmt4d_tc_eligible(p);
 }
 
+namespace {
+// Job cursor + one ready counter per LHS and per RHS tile row (streamed pre-pass).
+size_t sync_block_bytes(const iree_uk_mmt4d_params_t* p) {
+  return size_t((4 * (1 + p->M + p->N) + 1023) / 1024 * 1024);
+}
+}  // namespace
+
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
   if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) {
     if (p->M0 != 1 || p->N0 != 32 || p->K0 != 8 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
@@ -456,7 +479,9 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
   if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
   const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
   const size_t one = size_t(round_up(p->M * 16 * pitch, 1024) + round_up(p->N * 16 * pitch, 1024));
-  return ti.triple ? 2 * one : one;  // f32: a hi and a lo plane of both operands
+  // f32: a hi and a lo plane of both operands. Behind the operands: the job cursor and the
+  // per-tile-row ready counters of the streamed pre-pass.
+  return (ti.triple ? 2 * one : one) + sync_block_bytes(p);
 }
 
 // Re-tiled RHS kept by the caller across calls (weights): its size, the scratch a call then
@@ -473,7 +498,7 @@ size_t mmt4d_tc_prepared_workspace_size(const iree_uk_mmt4d_params_t* p) {
   if (!tc_type_info(p->flags, &ti) || ti.triple) return 0;
   if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1) return 0;
   const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
-  return size_t(round_up(p->M * 16 * pitch, 1024));
+  return size_t(round_up(p->M * 16 * pitch, 1024)) + sync_block_bytes(p);
 }
 int launch_mmt4d_tc_prepare_rhs(const iree_uk_mmt4d_params_t* p, void* prepared, size_t bytes,
                                 cudaStream_t stream) {
@@ -540,13 +565,27 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   // Variant 0 = automatic: the two-CTA kernel when the problem gives every CTA pair work,
   // the one-CTA kernel otherwise. 5 / 6 force the two-CTA / one-CTA kernel; 3 is the
   // scratch-free MN-major staging of 16-bit K0 = 1 operands.
-  if (variant == 0) variant = pair_kernel_pays(p) ? 5 : 6;
+  // Variant 0 = automatic (below). kTcVariantTwoCta / kTcVariantOneCta force a kernel with the
+  // whole re-tile in the pre-pass; kTcVariantStreamed forces the two-CTA kernel with the
+  // streamed pre-pass.
+  const int streamed_granule_form = ti.triple ? 0 : streamed_form_of_granule(p->K0 * ti.es);
+  bool want_streamed = false;
+  if (variant == 0) {
+    variant = pair_kernel_pays(p) ? kTcVariantTwoCta : kTcVariantOneCta;
+    want_streamed = variant == kTcVariantTwoCta && streamed_granule_form != 0 &&
+                    !debug_int("IREE_UK_B200_DEBUG_NO_STREAMED", 0);
+  } else if (variant == kTcVariantStreamed) {
+    if (!streamed_granule_form) return IREE_UK_B200_UNSUPPORTED;
+    variant = kTcVariantTwoCta;
+    want_streamed = true;
+  }
+  int stream_form = 0;  // set below once the startup set is known to leave work for the workers
   // K boxes per stage: two for the two-CTA kernel (64 KB stages, half the barrier round trips
   // per MMA), one for the one-CTA kernel (its stage is already 48 KB).
-  int kboxes = debug_int("IREE_UK_B200_DEBUG_KBOXES", variant == 5 ? 2 : 1) == 2 ? 2 : 1;
+  int kboxes = debug_int("IREE_UK_B200_DEBUG_KBOXES", variant == kTcVariantTwoCta ? 2 : 1) == 2 ? 2 : 1;
   const int mma_k = 32 / ti.es;        // K per tcgen05.mma: 16 (16-bit) or 32 (8-bit)
 
-  if (variant == 5 || variant == 6) {
+  if (variant == kTcVariantTwoCta || variant == kTcVariantOneCta) {
     // K-major operands from the re-tiled scratch: the one-CTA kernel (6) on 128 x bn tiles, or
     // the two-CTA kernel (5) on 256 x bn tiles per CTA pair.
     if (prepared_rhs && ti.triple) return IREE_UK_B200_UNSUPPORTED;
@@ -554,9 +593,9 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     if (!ws || ws_bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
     if ((reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(prepared_rhs)) & 255)
       return IREE_UK_B200_INVALID_ARGUMENT;
-    pair = variant == 5;
+    pair = variant == kTcVariantTwoCta;
     if (pair) {
-      pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0];
+      pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0][want_streamed ? streamed_granule_form : 0];
       if (pair_clusters < 1) return IREE_UK_B200_CUDA_ERROR;
       bn = pick_bn_pair(p->M, p->N, pair_clusters);
     }
@@ -567,9 +606,47 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     // A prepared RHS is this pre-pass's output kept by the caller: only the LHS is re-tiled.
     char* ws_b = prepared_rhs ? const_cast<char*>(static_cast<const char*>(prepared_rhs)) : ws_a + a_bytes;
     const int G = p->K0 * ti.es;
-    const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, p->M, rhs,
-                                 p->rhs_stride0 * ti.es, ws_b, prepared_rhs ? 0 : p->N, pitch,
-                                 p->K, G, stream);
+    // Streamed pre-pass: the pre-pass kernel re-tiles only what the first wave of tiles reads -
+    // the LHS rows of the first group of m-tiles and the RHS rows of as many n-tiles as the CTA
+    // pairs can have in flight over that group, plus two - and the main kernel's workers the rest.
+    int64_t a_first = p->M, b_first = p->N;
+    if (want_streamed) {
+      const int m_tiles = int((p->M * 16 + 2 * BM - 1) / (2 * BM));
+      const int gm = std::min(m_tiles, debug_int("IREE_UK_B200_DEBUG_GROUP_M", 8));
+      a_first = std::min<int64_t>(p->M, int64_t(gm) * (2 * BM / 16));
+      if (!prepared_rhs)
+        b_first = std::min<int64_t>(p->N, int64_t((pair_clusters + gm - 1) / gm + 2) * (bn / 16));
+      constexpr int64_t kMaxJobs = 1ll << 31;
+      const int kj = G == 4 ? warp_job_k1<4>() : warp_job_k1<2>();
+      const int64_t kch = (p->K + kj - 1) / kj;
+      const int64_t jobs_b = (p->N - b_first) * kch, jobs_a = (p->M - a_first) * kch;
+      if (jobs_a + jobs_b > 0 && jobs_a + jobs_b < kMaxJobs && p->M + p->N < kMaxJobs) {
+        stream_form = streamed_granule_form;
+        P.src_a = lhs;
+        P.src_b = rhs;
+        P.src_stride_a = p->lhs_stride0 * ti.es;
+        P.src_stride_b = p->rhs_stride0 * ti.es;
+        P.K1 = p->K;
+        P.rt_dst_a = ws_a;
+        P.rt_dst_b = ws_b;
+        P.rt_pitch = pitch;
+        P.rt_sync = reinterpret_cast<uint32_t*>(ws_a + a_bytes + (prepared_rhs ? 0 : b_bytes));
+        P.rt_a_first = a_first;
+        P.rt_b_first = b_first;
+        P.rt_jobs_b = uint32_t(jobs_b);
+        P.rt_jobs = uint32_t(jobs_a + jobs_b);
+        P.rt_kchunks = int32_t(kch);
+      } else {
+        a_first = p->M;
+        b_first = p->N;
+        if (want_streamed && pair)  // occupancy of the plain form decides the tile width
+          pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0][0];
+      }
+    }
+    const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, a_first, rhs,
+                                 p->rhs_stride0 * ti.es, ws_b, prepared_rhs ? 0 : b_first, pitch,
+                                 p->K, G, stream, stream_form ? P.rt_sync : nullptr,
+                                 stream_form ? int(1 + p->M + p->N) : 0);
     if (rc) return rc;
     const int64_t plane_bytes = a_bytes + b_bytes;  // [A hi | B hi][A lo | B lo]
     if (ti.triple) {
@@ -687,16 +764,16 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   // shape; no gain for small problems or when the old tile is read first).
   P.staged_epilogue = (pair && !rm && !P.out16 && !multicast_out && !P.accumulate &&
                        debug_int("IREE_UK_B200_DEBUG_STAGED_EPILOGUE", 1)) ? 1 : 0;
-  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 +
-                      ((num_peers || multicast_out || P.staged_epilogue) ? 4 * kEpiStageBytes : 0);
+  const size_t epi_bytes = (num_peers || multicast_out || P.staged_epilogue) ? 4 * kEpiStageBytes : 0;
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024 + epi_bytes;
 
   if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
   cudaError_t e;
   if (tev) KernelTiming::record(tev[1], stream);
   if (pair) {
     const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
-    e = ti.is_int ? launch_main(mmt4d_tc2_kernel<true>, grid, 2, smem, stream, P)
-                  : launch_main(mmt4d_tc2_kernel<false>, grid, 2, smem, stream, P);
+    e = launch_main(pair_kernel(ti.is_int, stream_form), grid, 2, smem, stream, P,
+                    pair_threads(stream_form));
   } else {
     const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
     e = ti.is_int ? launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P)
@@ -995,7 +1072,7 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   bool pair = false;
   int pair_clusters = 0, bn = pick_bn(M1, N1), kboxes = 1;
   if (want_pair) {
-    pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0];
+    pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0][0];
     if (pair_clusters >= 1) {
       pair = true;
       kboxes = 2;
@@ -1082,8 +1159,7 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   cudaError_t e;
   if (pair) {
     const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
-    e = ti.is_int ? launch_main(mmt4d_tc2_kernel<true>, grid, 2, smem, stream, P)
-                  : launch_main(mmt4d_tc2_kernel<false>, grid, 2, smem, stream, P);
+    e = launch_main(pair_kernel(ti.is_int, 0), grid, 2, smem, stream, P);
   } else {
     const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
     e = ti.is_int ? launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P)

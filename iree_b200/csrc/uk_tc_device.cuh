@@ -61,6 +61,15 @@ struct TcParams {
   const char* src_b;
   int64_t src_stride_a, src_stride_b;  // bytes between tile rows
   int64_t K1;
+  // streamed pre-pass (two-CTA kernel): what the kernel's own worker warps re-tile, from
+  // src_a / src_b above into the scratch the tensor maps describe
+  char* rt_dst_a;
+  char* rt_dst_b;
+  int64_t rt_pitch;        // row pitch of the scratch, bytes
+  uint32_t* rt_sync;       // [0]: job cursor; [1 + r]: jobs done for LHS tile row r; [1 + M1 + r]: RHS
+  int64_t rt_a_first, rt_b_first;  // first tile row of each operand that the workers re-tile
+  uint32_t rt_jobs, rt_jobs_b;     // jobs in all, and how many of them (the first) are RHS jobs
+  int32_t rt_kchunks;      // jobs per tile row
   int32_t triple;        // f32 operands as hi/lo tf32 planes, three MMAs per K slice
   int32_t out16;         // 0: 32-bit output; 1: f16 output, 2: bf16 output (rounded once, RNE)
   int32_t use_multicast; // output tiles are stored through an NVLink multicast mapping
@@ -334,6 +343,8 @@ enum : uint32_t {
   kStatusMmaTimeout = 1u << 1,
   kStatusEpilogueTimeout = 1u << 2,
   kStatusDrainTimeout = 1u << 3,
+  // bits 4 and 5: the weight-streaming GEMV and the pack bulk-row wait (other files)
+  kStatusRetileTimeout = 1u << 6,  // rows re-tiled by the kernel's own workers never became ready
 };
 
 __device__ __forceinline__ void st_global_v8(void* p, const uint32_t* r) {

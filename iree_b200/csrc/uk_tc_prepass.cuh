@@ -31,37 +31,31 @@ struct RetileOperand {
   int64_t blocks;        // tile rows x k chunks
 };
 
-// Both operands of a mmt4d call in one launch: blocks [0, a.blocks) re-tile the LHS, the rest
-// the RHS.
-template <int G>
-__global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOperand opb,
-                                                     int64_t dst_pitch_b, int64_t K1, int kchunks) {
-  pdl_launch_dependents();
-  const bool is_a = int64_t(blockIdx.x) < opa.blocks;
-  const char* __restrict__ src = is_a ? opa.src : opb.src;
-  const int64_t src_stride_b = is_a ? opa.src_stride_b : opb.src_stride_b;
-  char* __restrict__ dst = is_a ? opa.dst : opb.dst;
-  const int64_t block = is_a ? int64_t(blockIdx.x) : int64_t(blockIdx.x) - opa.blocks;
-  constexpr int KC = 1024 / G;            // k1 steps per block: 16 KB in, 16 rows x 1 KB out
+// One re-tile job: k1 steps [chunk * KC, +KC) of tile row `tile` (16 rows), through the
+// shared-memory buffer `sm` (KC * (16 * G + 4) bytes). Executed by `nthreads` threads that
+// synchronise through `sync()` (the whole block in the pre-pass kernel, a named barrier among the
+// worker warps of the main kernel). KC = k1 steps per job.
+template <int G, int KC, class Sync>
+__device__ __forceinline__ void retile_job(const char* __restrict__ src, int64_t src_stride_b,
+                                           char* __restrict__ dst, int64_t dst_pitch_b, int64_t K1,
+                                           int64_t tile, int chunk, unsigned char* sm, int tid,
+                                           int nthreads, Sync sync) {
   constexpr int PITCH = 16 * G + 4;       // bytes per k1 in shared memory
   constexpr int GV = 16 / G;              // granules per 16-byte vector
-  __shared__ __align__(16) unsigned char sm[KC * PITCH];
-  const int64_t tile = block / kchunks;
-  const int chunk = int(block - tile * kchunks);
   const int64_t k_base = int64_t(chunk) * KC;
   const int kn = int(min(int64_t(KC), K1 - k_base));
   const char* sp = src + tile * src_stride_b + k_base * (16 * G);
   // load: kn * 16 granules contiguous = kn * G vectors of 16 bytes
   const int nvec = kn * G;
 #pragma unroll 4
-  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+  for (int v = tid; v < nvec; v += nthreads) {
     const uint4 x = __ldg(reinterpret_cast<const uint4*>(sp) + v);
     const int byte = v * 16;
     const int k = byte / (16 * G), within = byte - k * (16 * G);
     uint32_t* d = reinterpret_cast<uint32_t*>(sm + k * PITCH + within);
     d[0] = x.x; d[1] = x.y; d[2] = x.z; d[3] = x.w;
   }
-  __syncthreads();
+  sync();
   // store: 16 rows x kn granules; a thread builds 16 bytes = GV consecutive k1 of one row
   if (G == 2) {
     // 2-byte granules: a 32-bit shared-memory word holds one k of two neighbouring rows, so a
@@ -70,7 +64,7 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOp
     const int full = kn / GV;  // whole vectors per row
     const int full8 = (full + 7) & ~7;
 #pragma unroll 2
-    for (int v = threadIdx.x; v < 8 * full8; v += blockDim.x) {
+    for (int v = tid; v < 8 * full8; v += nthreads) {
       const int rp = (v >> 3) & 7, kv = ((v >> 6) << 3) | (v & 7);
       if (kv >= full) continue;
       const int k0 = kv * GV;
@@ -88,7 +82,7 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOp
       *reinterpret_cast<uint4*>(dp + dst_pitch_b) = odd;
     }
     const int rem = kn - full * GV;  // trailing k of a ragged last chunk
-    for (int e = threadIdx.x; e < 16 * rem; e += blockDim.x) {
+    for (int e = tid; e < 16 * rem; e += nthreads) {
       const int r = e / rem, k = full * GV + (e - r * rem);
       *reinterpret_cast<uint16_t*>(dst + (tile * 16 + r) * dst_pitch_b + (k_base + k) * G) =
           *reinterpret_cast<const uint16_t*>(sm + k * PITCH + r * G);
@@ -100,7 +94,7 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOp
   const int vec_per_row = (kn + GV - 1) / GV;
   const int vec_per_row8 = (vec_per_row + 7) & ~7;
 #pragma unroll 4
-  for (int v = threadIdx.x; v < 16 * vec_per_row8; v += blockDim.x) {
+  for (int v = tid; v < 16 * vec_per_row8; v += nthreads) {
     const int r = (v >> 3) & 15, kv = ((v >> 7) << 3) | (v & 7);
     if (kv >= vec_per_row) continue;
     const int k0 = kv * GV;
@@ -120,13 +114,6 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOp
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           w[j] = *reinterpret_cast<const uint32_t*>(sm + (k0 + j) * PITCH + r * G);
-      } else if (G == 2) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t lo = *reinterpret_cast<const uint16_t*>(sm + (k0 + 2 * j) * PITCH + r * G);
-          const uint32_t hi = *reinterpret_cast<const uint16_t*>(sm + (k0 + 2 * j + 1) * PITCH + r * G);
-          w[j] = lo | (hi << 16);
-        }
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -144,10 +131,104 @@ __global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOp
   }
 }
 
+// The same re-tile done by one warp entirely in registers, for 2- and 4-byte granules: 8 KB of
+// one tile row (16 rows x warp_job_k1<G>() k1 steps). Every lane loads sixteen 16-byte vectors
+// - a vector holds one k1 step of 16 / G neighbouring rows - such that 16 / G of them are
+// consecutive k1 steps of the same rows; transposing those inside the thread yields, per row,
+// 16 contiguous bytes of that row's K-major form. No shared memory, no barrier: a warp is an
+// independent worker with all of its loads in flight at once. Vectors past K1 are read as zero
+// and not stored (a stored vector may reach past K1 * G inside the row's padded pitch).
+template <int G>
+__host__ __device__ constexpr int warp_job_k1() { return 2048 / (4 * G); }  // G = 4: 128, G = 2: 256
+
+template <int G>
+__device__ __forceinline__ void retile_warp_job(const char* __restrict__ src_row,
+                                                char* __restrict__ dst, int64_t dst_pitch_b,
+                                                int64_t tile_row, int64_t K1, int64_t k1_begin,
+                                                int lane) {
+  static_assert(G == 2 || G == 4, "register re-tile: 2- and 4-byte granules");
+  constexpr int RPV = 16 / G;        // rows per vector = k1 steps gathered per output vector
+  constexpr int RG = 16 / RPV;       // row groups of a tile: lanes rg = lane % RG
+  constexpr int KQ = 32 / RG;        // k1 groups per sub-pass: kq = lane / RG
+  constexpr int SUB = 16 / RPV;      // sub-passes: 16 vectors per lane in all
+  const int rg = lane % RG, kq = lane / RG;
+  auto load_sub = [&](uint4 (&v)[RPV], int s) {
+    const int64_t base = k1_begin + int64_t(s) * (KQ * RPV) + int64_t(kq) * RPV;
+#pragma unroll
+    for (int i = 0; i < RPV; ++i) {
+      const int64_t k1 = base + i;
+      v[i] = k1 < K1 ? __ldg(reinterpret_cast<const uint4*>(src_row + k1 * (16 * G) + rg * 16))
+                     : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  auto store_sub = [&](const uint4 (&v)[RPV], int s) {
+    const int64_t base = k1_begin + int64_t(s) * (KQ * RPV) + int64_t(kq) * RPV;
+    if (base >= K1) return;
+    char* drow = dst + (tile_row * 16 + rg * RPV) * dst_pitch_b + base * G;
+#pragma unroll
+    for (int c = 0; c < RPV; ++c) {
+      uint4 o;
+      if (G == 4) {
+        // row c of the group: word c of each of the four k1 steps
+        const uint32_t w[4][4] = {{v[0].x, v[0].y, v[0].z, v[0].w},
+                                  {v[1].x, v[1].y, v[1].z, v[1].w},
+                                  {v[2].x, v[2].y, v[2].z, v[2].w},
+                                  {v[3].x, v[3].y, v[3].z, v[3].w}};
+        o = make_uint4(w[0][c], w[1][c], w[2][c], w[3][c]);
+      } else {
+        // row c of the group: halfword c of each of the eight k1 steps (even rows in the low half)
+        const uint32_t sel = (c & 1) ? 0x7632u : 0x5410u;
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 x = v[i];
+          const uint32_t words[4] = {x.x, x.y, x.z, x.w};
+          w[i] = words[c >> 1];
+        }
+        o = make_uint4(__byte_perm(w[0], w[1], sel), __byte_perm(w[2], w[3], sel),
+                       __byte_perm(w[4], w[5], sel), __byte_perm(w[6], w[7], sel));
+      }
+      *reinterpret_cast<uint4*>(drow + int64_t(c) * dst_pitch_b) = o;
+    }
+  };
+  uint4 v[SUB][RPV];
+#pragma unroll
+  for (int s = 0; s < SUB; ++s) load_sub(v[s], s);
+#pragma unroll
+  for (int s = 0; s < SUB; ++s) store_sub(v[s], s);
+}
+
+// Both operands of a mmt4d call in one launch: blocks [0, a.blocks) re-tile the LHS, the rest
+// the RHS. `clear` / `clear_words` (optional): 32-bit words that block 0 zeroes - the ready
+// counters and the job cursor of a main kernel that finishes the re-tile itself (see
+// StreamedRetile); nothing else touches them while this kernel runs.
+template <int G>
+__global__ void __launch_bounds__(256) retile_kernel(RetileOperand opa, RetileOperand opb,
+                                                     int64_t dst_pitch_b, int64_t K1, int kchunks,
+                                                     uint32_t* clear, int clear_words) {
+  pdl_launch_dependents();
+  constexpr int KC = 1024 / G;            // k1 steps per block: 16 KB in, 16 rows x 1 KB out
+  __shared__ __align__(16) unsigned char sm[KC * (16 * G + 4)];
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i < clear_words; i += blockDim.x) clear[i] = 0u;
+  const bool is_a = int64_t(blockIdx.x) < opa.blocks;
+  const RetileOperand& op = is_a ? opa : opb;
+  const int64_t block = is_a ? int64_t(blockIdx.x) : int64_t(blockIdx.x) - opa.blocks;
+  const int64_t tile = block / kchunks;
+  const int chunk = int(block - tile * kchunks);
+  retile_job<G, KC>(op.src, op.src_stride_b, op.dst, dst_pitch_b, K1, tile, chunk, sm,
+                    int(threadIdx.x), int(blockDim.x), [] { __syncthreads(); });
+}
+
 int launch_retile(const char* lhs, int64_t lhs_stride_b, char* dst_a, int64_t tiles_a,
                   const char* rhs, int64_t rhs_stride_b, char* dst_b, int64_t tiles_b,
-                  int64_t dst_pitch_b, int64_t K1, int G, cudaStream_t stream) {
-  if (K1 <= 0 || tiles_a + tiles_b <= 0) return IREE_UK_B200_OK;
+                  int64_t dst_pitch_b, int64_t K1, int G, cudaStream_t stream,
+                  uint32_t* clear = nullptr, int clear_words = 0) {
+  if (K1 <= 0 || tiles_a + tiles_b <= 0) {
+    if (clear_words > 0 && cudaMemsetAsync(clear, 0, size_t(clear_words) * 4, stream) != cudaSuccess)
+      return IREE_UK_B200_CUDA_ERROR;
+    return IREE_UK_B200_OK;
+  }
   const int KC = 1024 / G;
   const int64_t kchunks = (K1 + KC - 1) / KC;
   const RetileOperand a = {lhs, lhs_stride_b, dst_a, tiles_a * kchunks};
@@ -155,11 +236,11 @@ int launch_retile(const char* lhs, int64_t lhs_stride_b, char* dst_a, int64_t ti
   const int64_t blocks = a.blocks + b.blocks;
   if (blocks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
   switch (G) {
-    case 1: retile_kernel<1><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
-    case 2: retile_kernel<2><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
-    case 4: retile_kernel<4><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
-    case 8: retile_kernel<8><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
-    case 16: retile_kernel<16><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks)); break;
+    case 1: retile_kernel<1><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks), clear, clear_words); break;
+    case 2: retile_kernel<2><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks), clear, clear_words); break;
+    case 4: retile_kernel<4><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks), clear, clear_words); break;
+    case 8: retile_kernel<8><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks), clear, clear_words); break;
+    case 16: retile_kernel<16><<<int(blocks), 256, 0, stream>>>(a, b, dst_pitch_b, K1, int(kchunks), clear, clear_words); break;
     default: return IREE_UK_B200_UNSUPPORTED;
   }
   return cuda_status(cudaGetLastError());

@@ -263,7 +263,7 @@ def kernel_timing_mean_ms():
     return float(a.value), float(b.value), int(n.value)
 
 
-FORM_TWO_CTA, FORM_ONE_CTA, FORM_TWO_CTA_HYBRID = 5, 6, 7
+FORM_TWO_CTA, FORM_ONE_CTA, FORM_TWO_CTA_STREAMED = 5, 6, 7
 
 
 def testing_starve_producers(enable):

@@ -146,8 +146,10 @@ def test_mmt4d_info_and_workspace_size():
     assert uk.mmt4d_path(big, with_workspace=False) == abi.PATH_GEMV
     assert uk.mmt4d_workspace_size(big) == 2 * 64 * 128 + 4 * 32 * 128
     p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
-    # row-major copies of both operands, 128-byte row pitch
-    assert uk.mmt4d_workspace_size(p) == (512 + 1792) * 16 * 4096 * 2 * 2
+    # row-major copies of both operands, 128-byte row pitch; behind them the job cursor and
+    # one ready counter per LHS / RHS tile row of the streamed pre-pass
+    sync = (4 * (1 + 512 + 1792) + 1023) // 1024 * 1024
+    assert uk.mmt4d_workspace_size(p) == (512 + 1792) * 16 * 4096 * 2 * 2 + sync
     assert uk.mmt4d_workspace_size(_mmt4d(M0=9, N0=6, K0=3)) == 0
 
 
@@ -241,11 +243,13 @@ def test_status_strings():
 
 def test_scratch_sizes_are_consistent():
     """Sizes depend on the shape and type only: the ordinary scratch is the LHS part plus the
-    RHS part that a caller may instead prepare once; f32 in its tensor-core mode needs two
-    planes of each; triples without a tensor-core path need none."""
+    RHS part that a caller may instead prepare once (each scratch ends with the small block of
+    counters of the streamed pre-pass); f32 in its tensor-core mode needs two planes of each;
+    triples without a tensor-core path need none."""
     p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
+    sync = (4 * (1 + 512 + 1792) + 1023) // 1024 * 1024
     whole = uk.mmt4d_workspace_size(p)
-    assert whole == (512 + 1792) * 16 * 8192 * 2          # the headline problem: 576 MiB
+    assert whole == (512 + 1792) * 16 * 8192 * 2 + sync   # the headline problem: 576 MiB
     assert uk.mmt4d_prepared_rhs_size(p) + uk.mmt4d_prepared_workspace_size(p) == whole
     assert uk.mmt4d_prepared_rhs_size(p) == 1792 * 16 * 8192 * 2
     q = _mmt4d(abi.MMT4D_BF16BF16F32, M=7, N=1792, K=4096)   # another M, the same weights
@@ -257,7 +261,7 @@ def test_scratch_sizes_are_consistent():
     assert uk.mmt4d_workspace_size(f) == 0
     prev = uk.set_f32_mode(uk.F32_MODE_TF32X3)
     try:
-        assert uk.mmt4d_workspace_size(f) == 2 * (4 + 4) * 16 * 128
+        assert uk.mmt4d_workspace_size(f) == 2 * (4 + 4) * 16 * 128 + 1024
         assert uk.mmt4d_prepared_rhs_size(f) == 0
     finally:
         uk.set_f32_mode(prev)

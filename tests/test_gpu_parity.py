@@ -439,7 +439,7 @@ def test_concurrent_host_threads_on_their_own_streams():
     G.check_device_status()
 
 
-@pytest.mark.parametrize("kernel", ["one_cta", "two_cta", "scratch_free"])
+@pytest.mark.parametrize("kernel", ["one_cta", "two_cta", "two_cta_streamed", "scratch_free"])
 def test_bounded_waits_report_a_timeout_instead_of_hanging(kernel):
     """Failure detection without faulting the GPU: a test hook makes the producers (the TMA warp,
     or the producer warps of the scratch-free kernel) never fill a stage, so the waits of the
@@ -449,7 +449,7 @@ def test_bounded_waits_report_a_timeout_instead_of_hanging(kernel):
     when their waits expire."""
     import torch
     from iree_b200 import ukernel as uk
-    if kernel == "two_cta":
+    if kernel.startswith("two_cta"):
         case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 320, 96, 4, 0, seed=5, loose=False)
     else:
         case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 8, 16, 64, 0, seed=5, loose=False)
@@ -463,7 +463,7 @@ def test_bounded_waits_report_a_timeout_instead_of_hanging(kernel):
             uk.mmt4d(p)
         else:
             ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda")
-            uk.testing_mmt4d_form(p, ws, uk.FORM_TWO_CTA if kernel == "two_cta" else uk.FORM_ONE_CTA)
+            uk.testing_mmt4d_form(p, ws, FORMS[kernel])
         st, detail = uk.device_status()
         return st, detail, out.cpu().numpy()
 
@@ -479,14 +479,22 @@ def test_bounded_waits_report_a_timeout_instead_of_hanging(kernel):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("form", ["one_cta", "two_cta"])
+FORMS = {"one_cta": 6, "two_cta": 5, "two_cta_streamed": 7}
+
+
+@pytest.mark.parametrize("form", list(FORMS))
 @pytest.mark.parametrize("t,K0,mode", [(abi.MMT4D_S8S8S32, 2, "exact"), (abi.MMT4D_BF16BF16F32, 2, "exact"),
                                        (abi.MMT4D_F16F16F32, 1, "exact")], ids=["s8", "bf16", "f16"])
-@pytest.mark.parametrize("shape", [(1, 1, 1), (17, 9, 65), (40, 33, 130)], ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("shape", [(1, 1, 1), (17, 9, 65), (40, 33, 130), (100, 40, 257),
+                                   # more LHS / RHS tile rows than the pre-pass of the streamed
+                                   # form covers: its workers re-tile the rest
+                                   (200, 40, 130), (40, 500, 33)],
+                         ids=lambda s: "%dx%dx%d" % s)
 @pytest.mark.parametrize("accumulate", [0, 1])
 def test_mmt4d_every_kernel_form_on_small_problems(form, t, K0, mode, shape, accumulate):
-    """The library picks the kernel form by problem size; here both TMA-fed forms run the same
-    small, ragged problems and must give the reference's bytes."""
+    """The library picks the kernel form by problem size; here every form (one CTA per tile, CTA
+    pairs after a full pre-pass, CTA pairs whose own workers finish the re-tile behind ready
+    counters) runs the same ragged problems and must give the reference's bytes."""
     import torch
     from iree_b200 import ukernel as uk
     M, N, K = shape
@@ -494,9 +502,10 @@ def test_mmt4d_every_kernel_form_on_small_problems(form, t, K0, mode, shape, acc
     lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
     p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
     ws = torch.empty(uk.mmt4d_workspace_size(p), dtype=torch.uint8, device="cuda")
-    uk.testing_mmt4d_form(p, ws, uk.FORM_TWO_CTA if form == "two_cta" else uk.FORM_ONE_CTA)
+    uk.testing_mmt4d_form(p, ws, FORMS[form])
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), G.oracle_mmt4d(case)), case.label()
+    G.check_device_status()
 
 
 def test_undersized_workspace_is_refused_not_served_by_a_slower_kernel():
