@@ -462,9 +462,9 @@ bool mmt4d_tc_direct_eligible(const iree_uk_mmt4d_params_t* p) {
 }
 
 namespace {
-// Job cursor + one ready counter per LHS and per RHS tile row (streamed pre-pass).
+// Job cursor + one ready counter per LHS tile row (streamed LHS pre-pass).
 size_t sync_block_bytes(const iree_uk_mmt4d_params_t* p) {
-  return size_t((4 * (1 + p->M + p->N) + 1023) / 1024 * 1024);
+  return size_t((4 * (1 + p->M) + 1023) / 1024 * 1024);
 }
 }  // namespace
 
@@ -480,7 +480,7 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
   const int64_t pitch = round_up(p->K * p->K0 * ti.es, 128);
   const size_t one = size_t(round_up(p->M * 16 * pitch, 1024) + round_up(p->N * 16 * pitch, 1024));
   // f32: a hi and a lo plane of both operands. Behind the operands: the job cursor and the
-  // per-tile-row ready counters of the streamed pre-pass.
+  // per-tile-row ready counters of the streamed LHS pre-pass.
   return (ti.triple ? 2 * one : one) + sync_block_bytes(p);
 }
 
@@ -569,7 +569,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   // whole re-tile in the pre-pass; kTcVariantStreamed forces the two-CTA kernel with the
   // streamed pre-pass.
   const int streamed_granule_form = ti.triple ? 0 : streamed_form_of_granule(p->K0 * ti.es);
-  bool want_streamed = false;
+  bool want_streamed = false, variant_forced_streamed = false;
   if (variant == 0) {
     variant = pair_kernel_pays(p) ? kTcVariantTwoCta : kTcVariantOneCta;
     want_streamed = variant == kTcVariantTwoCta && streamed_granule_form != 0 &&
@@ -578,6 +578,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     if (!streamed_granule_form) return IREE_UK_B200_UNSUPPORTED;
     variant = kTcVariantTwoCta;
     want_streamed = true;
+    variant_forced_streamed = true;
   }
   int stream_form = 0;  // set below once the startup set is known to leave work for the workers
   // K boxes per stage: two for the two-CTA kernel (64 KB stages, half the barrier round trips
@@ -606,47 +607,41 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     // A prepared RHS is this pre-pass's output kept by the caller: only the LHS is re-tiled.
     char* ws_b = prepared_rhs ? const_cast<char*>(static_cast<const char*>(prepared_rhs)) : ws_a + a_bytes;
     const int G = p->K0 * ti.es;
-    // Streamed pre-pass: the pre-pass kernel re-tiles only what the first wave of tiles reads -
-    // the LHS rows of the first group of m-tiles and the RHS rows of as many n-tiles as the CTA
-    // pairs can have in flight over that group, plus two - and the main kernel's workers the rest.
-    int64_t a_first = p->M, b_first = p->N;
+    // Streamed LHS pre-pass: the pre-pass kernel re-tiles the RHS and the LHS rows of the first
+    // group of m-tiles; the main kernel's workers re-tile the LHS rows of the later groups.
+    int64_t a_first = p->M;
     if (want_streamed) {
       const int m_tiles = int((p->M * 16 + 2 * BM - 1) / (2 * BM));
       const int gm = std::min(m_tiles, debug_int("IREE_UK_B200_DEBUG_GROUP_M", 8));
-      a_first = std::min<int64_t>(p->M, int64_t(gm) * (2 * BM / 16));
-      if (!prepared_rhs)
-        b_first = std::min<int64_t>(p->N, int64_t((pair_clusters + gm - 1) / gm + 2) * (bn / 16));
-      constexpr int64_t kMaxJobs = 1ll << 31;
+      const int64_t first = std::min<int64_t>(p->M, int64_t(gm) * (2 * BM / 16));
       const int kj = G == 4 ? warp_job_k1<4>() : warp_job_k1<2>();
       const int64_t kch = (p->K + kj - 1) / kj;
-      const int64_t jobs_b = (p->N - b_first) * kch, jobs_a = (p->M - a_first) * kch;
-      if (jobs_a + jobs_b > 0 && jobs_a + jobs_b < kMaxJobs && p->M + p->N < kMaxJobs) {
+      const int64_t jobs = (p->M - first) * kch;
+      // Worth it once the rows the workers take over are a good part of the whole pre-pass
+      // (at least a quarter of all tile rows of both operands): measured +1 % on the 8-way
+      // shard of the headline problem, nothing on the unsharded one, whose pre-pass is mostly RHS.
+      const bool pays = (p->M - first) * 4 >= p->M + (prepared_rhs ? 0 : p->N) ||
+                        variant_forced_streamed;
+      if (jobs > 0 && jobs < (1ll << 31) && pays) {
         stream_form = streamed_granule_form;
+        a_first = first;
         P.src_a = lhs;
-        P.src_b = rhs;
         P.src_stride_a = p->lhs_stride0 * ti.es;
-        P.src_stride_b = p->rhs_stride0 * ti.es;
         P.K1 = p->K;
         P.rt_dst_a = ws_a;
-        P.rt_dst_b = ws_b;
         P.rt_pitch = pitch;
         P.rt_sync = reinterpret_cast<uint32_t*>(ws_a + a_bytes + (prepared_rhs ? 0 : b_bytes));
         P.rt_a_first = a_first;
-        P.rt_b_first = b_first;
-        P.rt_jobs_b = uint32_t(jobs_b);
-        P.rt_jobs = uint32_t(jobs_a + jobs_b);
+        P.rt_jobs = uint32_t(jobs);
         P.rt_kchunks = int32_t(kch);
-      } else {
-        a_first = p->M;
-        b_first = p->N;
-        if (want_streamed && pair)  // occupancy of the plain form decides the tile width
-          pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0][0];
+      } else if (pair) {  // occupancy of the plain form decides the grid
+        pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0][0];
       }
     }
     const int rc = launch_retile(lhs, p->lhs_stride0 * ti.es, ws_a, a_first, rhs,
-                                 p->rhs_stride0 * ti.es, ws_b, prepared_rhs ? 0 : b_first, pitch,
+                                 p->rhs_stride0 * ti.es, ws_b, prepared_rhs ? 0 : p->N, pitch,
                                  p->K, G, stream, stream_form ? P.rt_sync : nullptr,
-                                 stream_form ? int(1 + p->M + p->N) : 0);
+                                 stream_form ? int(1 + p->M) : 0);
     if (rc) return rc;
     const int64_t plane_bytes = a_bytes + b_bytes;  // [A hi | B hi][A lo | B lo]
     if (ti.triple) {

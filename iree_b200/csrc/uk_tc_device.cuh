@@ -61,14 +61,13 @@ struct TcParams {
   const char* src_b;
   int64_t src_stride_a, src_stride_b;  // bytes between tile rows
   int64_t K1;
-  // streamed pre-pass (two-CTA kernel): what the kernel's own worker warps re-tile, from
-  // src_a / src_b above into the scratch the tensor maps describe
+  // streamed LHS pre-pass (two-CTA kernel): what the kernel's own worker warps re-tile, from
+  // src_a above into the scratch that map_a describes
   char* rt_dst_a;
-  char* rt_dst_b;
   int64_t rt_pitch;        // row pitch of the scratch, bytes
-  uint32_t* rt_sync;       // [0]: job cursor; [1 + r]: jobs done for LHS tile row r; [1 + M1 + r]: RHS
-  int64_t rt_a_first, rt_b_first;  // first tile row of each operand that the workers re-tile
-  uint32_t rt_jobs, rt_jobs_b;     // jobs in all, and how many of them (the first) are RHS jobs
+  uint32_t* rt_sync;       // [0]: job cursor; [1 + r]: jobs done for LHS tile row r
+  int64_t rt_a_first;      // first LHS tile row that the workers re-tile
+  uint32_t rt_jobs;        // jobs in all
   int32_t rt_kchunks;      // jobs per tile row
   int32_t triple;        // f32 operands as hi/lo tf32 planes, three MMAs per K slice
   int32_t out16;         // 0: 32-bit output; 1: f16 output, 2: bf16 output (rounded once, RNE)

@@ -489,19 +489,22 @@ __global__ void __launch_bounds__(kSwThreads, 1) mmt4d_tc_sw_kernel(const __grid
 //   tmem_empty[b] leader's only, 8 arrivals: the four epilogue warps of each CTA
 // No TMA load uses cluster multicast.
 //
-// Streamed pre-pass (G != 0). The re-tile of the operands into K-major scratch is pure data
-// movement that the tensor-core main loop does not need all at once: a tile needs its own LHS
-// rows and RHS rows only. In this form the pre-pass kernel re-tiles just the rows the first
-// wave of tiles reads; eight more warps per CTA ("workers") re-tile all other rows while the
-// main loop runs, in the order in which the tile schedule will need them (the remaining RHS
-// rows first - the first group of LHS rows walks all of them - then the LHS rows of the later
-// groups). Each worker warp claims jobs (8 KB: one tile row, warp_job_k1<G>() k1 steps, re-tiled
-// in registers) from a cursor in global memory and counts finished jobs per tile row; the TMA producer of a tile first checks,
-// with a bounded acquire wait, that the counters of the rows it is about to load have reached the
-// number of jobs per row, then orders its TMA loads after what it observed with a proxy fence.
-// Workers never wait for anything and any CTA's workers can take any job, so the re-tile makes
-// progress whichever CTAs of the launch happen to be resident: nothing in this kernel waits on
-// a CTA that may not be running.
+// Streamed LHS pre-pass (G != 0). The re-tile of an operand into K-major scratch is pure data
+// movement that the tensor-core main loop does not need all at once: a tile needs only its own
+// LHS rows. The tile schedule walks the LHS in groups of m-tiles, so in this form the pre-pass
+// kernel re-tiles the RHS and just the first group of LHS rows; eight more warps per CTA
+// ("workers") re-tile the later groups while the main loop runs on the earlier ones. That takes
+// most of the LHS re-tile - the part of a call that does not shrink when the RHS is sharded
+// across GPUs - off the critical path. Each worker warp claims jobs (8 KB: one tile row,
+// warp_job_k1<G>() k1 steps, re-tiled in registers) from a cursor in global memory and counts
+// finished jobs per tile row; the TMA producer of a tile first checks, with a bounded acquire
+// wait, that the counters of the eight LHS tile rows it is about to load have reached the number
+// of jobs per row, then orders its TMA loads after what it observed with a proxy fence. Workers
+// never wait for anything and any CTA's workers can take any job, so the re-tile makes progress
+// whichever CTAs of the launch happen to be resident: nothing in this kernel waits on a CTA that
+// may not be running. (Streaming the RHS the same way was measured too: its re-tile is five
+// times the LHS's at the headline size, and run beside the main loop it slowed that loop by
+// almost what the pre-pass had cost.)
 constexpr int kWorkerWarps = 8;
 constexpr int kWorkerThreads = kWorkerWarps * 32;
 constexpr int kWorkerFirstWarp = kThreads / 32;            // warps 6..13
@@ -573,18 +576,15 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
         if (j >= P.rt_jobs) break;
         // the next job's number travels while this job is being done
         if (lane == 0) claimed = atomicAdd(P.rt_sync, 1u);
-        const bool is_b = j < P.rt_jobs_b;
-        const uint32_t jj = is_b ? j : j - P.rt_jobs_b;
-        const uint32_t r = jj / kch;
-        const int chunk = int(jj - r * kch);
-        const int64_t row = int64_t(is_b ? P.rt_b_first : P.rt_a_first) + r;
-        const char* src_row = (is_b ? P.src_b + row * P.src_stride_b : P.src_a + row * P.src_stride_a);
-        retile_warp_job<G>(src_row, is_b ? P.rt_dst_b : P.rt_dst_a, P.rt_pitch, row, P.K1,
+        const uint32_t r = j / kch;
+        const int chunk = int(j - r * kch);
+        const int64_t row = P.rt_a_first + r;
+        retile_warp_job<G>(P.src_a + row * P.src_stride_a, P.rt_dst_a, P.rt_pitch, row, P.K1,
                            int64_t(chunk) * KJ, lane);
         // every lane's stores are ordered before the count that announces them
         __threadfence();
         __syncwarp();
-        if (lane == 0) atomicAdd(P.rt_sync + 1 + (is_b ? P.M1 + row : row), 1u);
+        if (lane == 0) atomicAdd(P.rt_sync + 1 + row, 1u);
       }
     }
   } else if (warp == 0) {
@@ -608,17 +608,13 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
           cb[i] = nt * sb_st.tstep[i] + r * sb_st.rstep[i];
         }
         if (G != 0) {
-          // Streamed pre-pass: lanes 0-7 vouch for this CTA's eight LHS tile rows, the next
-          // bn / 32 lanes for its RHS tile rows. Rows below rt_*_first were re-tiled by the
-          // pre-pass kernel; the others are ready once their counter has reached the jobs per row.
+          // Streamed pre-pass: lanes 0-7 vouch for this CTA's eight LHS tile rows. Rows below
+          // rt_a_first were re-tiled by the pre-pass kernel; the others are ready once their
+          // counter has reached the jobs per row.
           const uint32_t* ctr = nullptr;
-          const int b_tile_rows = P.bn >> 5;
           if (lane < 8) {
             const int64_t row = int64_t(mt) * (2 * BM / 16) + int64_t(r) * (BM / 16) + lane;
             if (row >= P.rt_a_first && row < P.M1) ctr = P.rt_sync + 1 + row;
-          } else if (lane < 8 + b_tile_rows) {
-            const int64_t row = int64_t(nt) * (P.bn >> 4) + int64_t(r) * b_tile_rows + (lane - 8);
-            if (row >= P.rt_b_first && row < P.N1) ctr = P.rt_sync + 1 + P.M1 + row;
           }
           bool ready = true;
           if (ctr) {

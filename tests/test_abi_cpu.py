@@ -147,8 +147,8 @@ def test_mmt4d_info_and_workspace_size():
     assert uk.mmt4d_workspace_size(big) == 2 * 64 * 128 + 4 * 32 * 128
     p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
     # row-major copies of both operands, 128-byte row pitch; behind them the job cursor and
-    # one ready counter per LHS / RHS tile row of the streamed pre-pass
-    sync = (4 * (1 + 512 + 1792) + 1023) // 1024 * 1024
+    # one ready counter per LHS tile row of the streamed pre-pass
+    sync = (4 * (1 + 512) + 1023) // 1024 * 1024
     assert uk.mmt4d_workspace_size(p) == (512 + 1792) * 16 * 4096 * 2 * 2 + sync
     assert uk.mmt4d_workspace_size(_mmt4d(M0=9, N0=6, K0=3)) == 0
 
@@ -247,7 +247,7 @@ def test_scratch_sizes_are_consistent():
     counters of the streamed pre-pass); f32 in its tensor-core mode needs two planes of each;
     triples without a tensor-core path need none."""
     p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
-    sync = (4 * (1 + 512 + 1792) + 1023) // 1024 * 1024
+    sync = (4 * (1 + 512) + 1023) // 1024 * 1024
     whole = uk.mmt4d_workspace_size(p)
     assert whole == (512 + 1792) * 16 * 8192 * 2 + sync   # the headline problem: 576 MiB
     assert uk.mmt4d_prepared_rhs_size(p) + uk.mmt4d_prepared_workspace_size(p) == whole

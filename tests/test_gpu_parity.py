@@ -486,9 +486,9 @@ FORMS = {"one_cta": 6, "two_cta": 5, "two_cta_streamed": 7}
 @pytest.mark.parametrize("t,K0,mode", [(abi.MMT4D_S8S8S32, 2, "exact"), (abi.MMT4D_BF16BF16F32, 2, "exact"),
                                        (abi.MMT4D_F16F16F32, 1, "exact")], ids=["s8", "bf16", "f16"])
 @pytest.mark.parametrize("shape", [(1, 1, 1), (17, 9, 65), (40, 33, 130), (100, 40, 257),
-                                   # more LHS / RHS tile rows than the pre-pass of the streamed
-                                   # form covers: its workers re-tile the rest
-                                   (200, 40, 130), (40, 500, 33)],
+                                   # more LHS tile rows than the pre-pass of the streamed form
+                                   # covers (its workers re-tile rows 128 and up), ragged K
+                                   (200, 40, 130), (300, 20, 33), (40, 500, 33)],
                          ids=lambda s: "%dx%dx%d" % s)
 @pytest.mark.parametrize("accumulate", [0, 1])
 def test_mmt4d_every_kernel_form_on_small_problems(form, t, K0, mode, shape, accumulate):
