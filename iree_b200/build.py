@@ -69,6 +69,42 @@ def build(verbose=False, ptxas_info=False):
     return LIB_PATH
 
 
+PLUGIN_PATH = os.path.join(_HERE, "libiree_uk_b200_plugin.so")
+PLUGIN_SRC = os.path.join(_HERE, "..", "plugin", "iree_uk_b200_plugin.c")
+
+
+def reference_include_dir():
+    """``runtime/src`` of an IREE checkout (for the standalone executable-plugin header): the
+    IREE_REFERENCE_SRC environment variable, or a checkout named ``reference`` beside this
+    repository; None when neither exists."""
+    cands = [os.environ.get("IREE_REFERENCE_SRC"),
+             os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference", "runtime", "src")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "iree", "hal", "local", "executable_plugin.h")):
+            return c
+    return None
+
+
+def build_plugin(verbose=False):
+    """Compiles the IREE executable plugin (plugin/iree_uk_b200_plugin.c) against the plugin
+    header of an IREE checkout and links it to the library beside it. Returns its path, or None
+    when no checkout is available (an already built plugin is then left as it is)."""
+    inc = reference_include_dir()
+    if inc is None:
+        return PLUGIN_PATH if os.path.exists(PLUGIN_PATH) else None
+    deps = [PLUGIN_SRC, LIB_PATH] + glob.glob(os.path.join(_HERE, "..", "include", "*.h"))
+    if _newer(PLUGIN_PATH, deps):
+        cmd = ["gcc", "-std=c11", "-O2", "-Wall", "-Wextra", "-fPIC", "-shared",
+               "-fvisibility=hidden", "-I" + inc, "-I" + os.path.join(_HERE, "..", "include"),
+               PLUGIN_SRC, "-o", PLUGIN_PATH, "-L" + _HERE, "-liree_uk_b200",
+               "-Wl,-rpath,$ORIGIN"]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
+    return PLUGIN_PATH
+
+
 if __name__ == "__main__":
     build(verbose=True, ptxas_info="--ptxas" in sys.argv)
     print(LIB_PATH)
+    print(build_plugin(verbose=True))

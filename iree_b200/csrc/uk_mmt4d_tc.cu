@@ -400,6 +400,8 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   P.bn = bn;
   P.m_tiles = int((p->M + tile_m - 1) / tile_m);
   P.n_tiles = int((ncols + bn - 1) / bn);
+  P.num_work = P.tail_first = P.m_tiles * P.n_tiles;
+  P.tail_split = 1;
   P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
   P.out = static_cast<char*>(p->out_buffer) + p->out_offset * 4;
   P.out_stride0 = p->out_stride0;
@@ -717,6 +719,39 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   P.bn = bn;
   P.m_tiles = int((p->M * 16 + tile_m - 1) / tile_m);
   P.n_tiles = int((p->N * 16 + bn - 1) / bn);
+  P.num_work = P.tail_first = P.m_tiles * P.n_tiles;
+  P.tail_split = 1;
+  if (pair && !ti.triple) {
+    // Tail of the schedule: the tiles of the last, partial round over the CTA pairs are cut
+    // along N into 2 or 4 narrow tiles when that shortens the round (tile time ~ width + 96
+    // columns' worth, as in pick_bn_pair).
+    const int tiles = P.num_work, rem = tiles % pair_clusters;
+    if (tiles > pair_clusters && rem != 0) {
+      int best = 1;
+      int64_t best_cost = int64_t(bn + 96);
+      for (int split : {2, 4}) {
+        if ((bn / split) % 16 != 0 || bn % split != 0) continue;
+        const int64_t rounds = (int64_t(rem) * split + pair_clusters - 1) / pair_clusters;
+        const int64_t cost = rounds * (bn / split + 96);
+        if (cost < best_cost) { best_cost = cost; best = split; }
+      }
+      best = debug_int("IREE_UK_B200_DEBUG_TAIL_SPLIT", best);
+      if (best > 1) {
+        const int b_rows_narrow = bn / best / 2;
+        const int64_t pitch = round_up(kelems * ti.es, 128);
+        const uint64_t db[3] = {uint64_t(kelems), uint64_t(p->N * 16), 1};
+        const uint64_t sb[2] = {uint64_t(pitch), uint64_t(pitch) * uint64_t(p->N * 16)};
+        const uint32_t bb[3] = {uint32_t(kblk_elems), uint32_t(b_rows_narrow), 1};
+        char* ws_b = prepared_rhs ? const_cast<char*>(static_cast<const char*>(prepared_rhs))
+                                  : static_cast<char*>(ws) + round_up(p->M * 16 * pitch, 1024);
+        if (!encode_map(&P.map_b_narrow, ti.tm_type, ws_b, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+          return IREE_UK_B200_CUDA_ERROR;
+        P.tail_first = tiles - rem;
+        P.tail_split = best;
+        P.num_work = P.tail_first + rem * best;
+      }
+    }
+  }
   P.group_m = std::min(P.m_tiles, debug_int("IREE_UK_B200_DEBUG_GROUP_M", pair ? 8 : 16));
   P.out = static_cast<char*>(p->out_buffer) + p->out_offset * ti.out_es;
   P.out_stride0 = p->out_stride0;
@@ -766,7 +801,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   cudaError_t e;
   if (tev) KernelTiming::record(tev[1], stream);
   if (pair) {
-    const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
+    const int grid = 2 * std::min(P.num_work, pair_clusters);
     e = launch_main(pair_kernel(ti.is_int, stream_form), grid, 2, smem, stream, P,
                     pair_threads(stream_form));
   } else {
@@ -1133,6 +1168,8 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
   P.bn = bn;
   P.m_tiles = int((M + tile_m - 1) / tile_m);
   P.n_tiles = int((N + bn - 1) / bn);
+  P.num_work = P.tail_first = P.m_tiles * P.n_tiles;
+  P.tail_split = 1;
   P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
   P.out = out;
   P.out_stride0 = out_stride0;

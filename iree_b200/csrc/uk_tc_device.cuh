@@ -35,6 +35,10 @@ struct OperandStage {
 struct TcParams {
   CUtensorMap map_a;
   CUtensorMap map_b;
+  CUtensorMap map_b_narrow;  // two-CTA kernel: the RHS with the box of a narrow tail tile
+  int32_t num_work;          // work items (tiles, the tail ones counted tail_split times)
+  int32_t tail_first;        // first narrow item = first tile of the tail (num_work when none)
+  int32_t tail_split;        // narrow tiles per tail tile
   OperandStage sa, sb;
   uint32_t desc_hi_a, desc_hi_b;    // bits 32..63 of the shared-memory descriptors
   uint32_t desc_lbo_a, desc_lbo_b;  // leading byte offset >> 4
@@ -335,6 +339,33 @@ __device__ __forceinline__ void tile_coords(const TcParams& P, int tile, int* mt
   const int gm = min(P.group_m, P.m_tiles - g * P.group_m);
   *nt = r / gm;
   *mt = g * P.group_m + (r - *nt * gm);
+}
+
+// Work items of the two-CTA kernel. Items [0, tail_first) are whole tiles in schedule order.
+// When the tile count is not a multiple of the number of CTA pairs, the tiles of the last,
+// partial round are cut along N into tail_split narrower tiles each (items tail_first and up),
+// so that the round keeps every pair busy for a fraction of a tile's time instead of a few
+// pairs for a whole one.
+struct WorkItem {
+  int mt, nt;    // tile coordinates
+  int col0;      // first output column, in elements
+  int width;     // accumulator columns of this item (bn, or bn / tail_split)
+  bool narrow;
+};
+__device__ __forceinline__ WorkItem work_item(const TcParams& P, int w) {
+  WorkItem it;
+  int tile = w, part = 0;
+  it.width = P.bn;
+  it.narrow = w >= P.tail_first;
+  if (it.narrow) {
+    const int r = w - P.tail_first;
+    tile = P.tail_first + r / P.tail_split;
+    part = r - (tile - P.tail_first) * P.tail_split;
+    it.width = P.bn / P.tail_split;
+  }
+  tile_coords(P, tile, &it.mt, &it.nt);
+  it.col0 = it.nt * P.bn + part * it.width;
+  return it;
 }
 
 enum : uint32_t {

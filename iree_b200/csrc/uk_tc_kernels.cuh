@@ -534,7 +534,6 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
   const uint32_t stage_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t stage_bytes = uint32_t(P.stage_bytes_a + P.stage_bytes_b);  // per CTA
   const int S = P.num_stages;
-  const int num_tiles = P.m_tiles * P.n_tiles;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -598,14 +597,24 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
       const OperandStage sa_st = P.sa, sb_st = P.sb;
       const int num_kb = P.num_kb;
       const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        int mt, nt;
-        tile_coords(P, tile, &mt, &nt);
+      for (int w = pair; w < P.num_work && ok; w += num_pairs) {
+        const WorkItem it = work_item(P, w);
+        const int mt = it.mt, nt = it.nt;
         int ca[3], cb[3];
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
           ca[i] = mt * sa_st.tstep[i] + r * sa_st.rstep[i];
           cb[i] = nt * sb_st.tstep[i] + r * sb_st.rstep[i];
+        }
+        // A narrow tail tile: K-major RHS rows [col0, col0 + width), half of them per CTA, through
+        // the tensor map whose box has that many rows; the stage keeps its layout (the boxes
+        // just hold fewer rows), only the bytes to expect change.
+        const CUtensorMap* map_b = &P.map_b;
+        uint32_t tx_bytes = 2u * stage_bytes;
+        if (it.narrow) {
+          cb[1] = it.col0 + r * (it.width >> 1);
+          map_b = &P.map_b_narrow;
+          tx_bytes = 2u * (a_bytes + uint32_t(sb_st.nbox) * uint32_t(it.width >> 1) * 128u);
         }
         if (G != 0) {
           // Streamed pre-pass: lanes 0-7 vouch for this CTA's eight LHS tile rows. Rows below
@@ -645,9 +654,9 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
           const bool starve = P.starve != 0;  // test hook: nothing ever arrives
           if (!starve && elect_one()) {
-            if (leader) mbar_expect_tx(own_bar, 2u * stage_bytes);
+            if (leader) mbar_expect_tx(own_bar, tx_bytes);
             issue_operand_loads<true>(&P.map_a, sa_st, sa, bar, ca);
-            issue_operand_loads<true>(&P.map_b, sb_st, sa + a_bytes, bar, cb);
+            issue_operand_loads<true>(map_b, sb_st, sa + a_bytes, bar, cb);
           }
           __syncwarp();
 #pragma unroll
@@ -691,7 +700,10 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
       const MmaIssue mi = make_mma_issue(P);
       const uint32_t a_bytes = uint32_t(P.stage_bytes_a);
       const int num_kb = P.num_kb;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      MmaIssue mi_narrow = mi;  // the same MMAs with the N of a narrow tail tile
+      mi_narrow.idesc = (mi.idesc & ~(0x3Fu << 17)) | (uint32_t((P.bn / max(P.tail_split, 1)) >> 3) << 17);
+      for (int w = pair; w < P.num_work && ok; w += num_pairs) {
+        const bool narrow = w >= P.tail_first;
         if (!mbar_wait_warp(smem_u32(&tmem_empty_bar[buf]), buf_phase ^ 1u, abortp, wait_limit)) {
           if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
           raise_abort_pair(&abort_flag, rank);
@@ -712,7 +724,7 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
             if (IS_INT && mi.dual)
               issue_stage_mmas_dual<true>(mi, d_tmem, d_tmem + uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             else
-              issue_stage_mmas<IS_INT, true>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+              issue_stage_mmas<IS_INT, true>(narrow ? mi_narrow : mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             tc_commit_pair(smem_u32(&empty_bar[stage]), 3);  // both CTAs may refill the stage
             if (kb == num_kb - 1) tc_commit_pair(smem_u32(&tmem_full_bar[buf]), 3);  // accumulators done
           }
@@ -729,10 +741,10 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
     const uint32_t epi_stage = stage_base + uint32_t(S) * stage_bytes + uint32_t(q) * kEpiStageBytes;
     int buf = 0;
     uint32_t buf_phase = 0;
-    const int chunks = P.bn >> 4;
-    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-      int mt, nt;
-      tile_coords(P, tile, &mt, &nt);
+    for (int w = pair; w < P.num_work; w += num_pairs) {
+      const WorkItem it = work_item(P, w);
+      const int mt = it.mt, nt = it.nt;
+      const int chunks = it.width >> 4;
       if (!__all_sync(0xFFFFFFFFu, mbar_wait(smem_u32(&tmem_full_bar[buf]), buf_phase, abortp, wait_limit))) {
         if (lane == 0) atomicOr(P.status, kStatusEpilogueTimeout);
         raise_abort_pair(&abort_flag, rank);
@@ -745,7 +757,7 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
         epilogue_rows_dual(P, t_hi, t_hi + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
       } else {
         const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
-        epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks, epi_stage, lane);
+        epilogue_rows(P, taddr0, row, int64_t(it.col0 >> 4), chunks, epi_stage, lane);
       }
       tc_fence_before();
       __syncwarp();

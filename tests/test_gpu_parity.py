@@ -508,6 +508,23 @@ def test_mmt4d_every_kernel_form_on_small_problems(form, t, K0, mode, shape, acc
     G.check_device_status()
 
 
+@pytest.mark.parametrize("shape", [(385, 97, 3), (353, 127, 2), (465, 127, 2), (337, 49, 5)],
+                         ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("t,K0", [(abi.MMT4D_S8S8S32, 2), (abi.MMT4D_BF16BF16F32, 2)], ids=["s8", "bf16"])
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_narrow_tail_tiles(shape, t, K0, accumulate):
+    """Tile counts that leave a partial last round over the 74 CTA pairs of a B200: the
+    two-CTA kernel cuts the tiles of that round into 2 or 4 narrower ones (accumulator widths
+    256, 224, 192 and 160 columns are all covered by these shapes). Ragged M and N edges;
+    small-integer values, so the reference's bytes are expected exactly."""
+    M, N, K = shape
+    case = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, accumulate, seed=37, mode="exact", loose=False)
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    assert np.array_equal(got, G.oracle_mmt4d(case)), case.label()
+    G.check_device_status()
+
+
 def test_undersized_workspace_is_refused_not_served_by_a_slower_kernel():
     import torch
     from iree_b200 import ukernel as uk
