@@ -150,6 +150,14 @@ bool testing_starve_producers();
 // True when the environment variable is set to a non-empty value other than "0".
 bool env_flag(const char* name);
 
+// Tuning overrides read from the environment. They exist only in a build made with
+// -DIREE_UK_B200_EXPERIMENTS (parameter sweeps); the shipped library always takes `fallback`.
+#ifdef IREE_UK_B200_EXPERIMENTS
+int debug_int(const char* name, int fallback);
+#else
+constexpr int debug_int(const char*, int fallback) { return fallback; }
+#endif
+
 }  // namespace uk
 
 #endif  // IREE_UK_B200_CSRC_UK_COMMON_H_

@@ -39,16 +39,6 @@ namespace {
 // host side: tensor maps, descriptors, launch
 // ---------------------------------------------------------------------------------------
 
-// Tuning overrides read from the environment. They exist only in a build made with
-// -DIREE_UK_B200_EXPERIMENTS (parameter sweeps); the shipped library always takes `fallback`.
-#ifdef IREE_UK_B200_EXPERIMENTS
-int debug_int(const char* name, int fallback) {
-  const char* v = std::getenv(name);
-  return v ? std::atoi(v) : fallback;
-}
-#else
-constexpr int debug_int(const char*, int fallback) { return fallback; }
-#endif
 
 // Wait policy of a launch: every device-side wait gives up after about a second; with the
 // starve test hook set, the producers fill nothing and the limit drops to a few tens of

@@ -505,8 +505,14 @@ int launch_fixed(RelayoutArgs a, cudaStream_t stream) {
 // accumulator tiles. (T0, T1) are extents along matrix rows / columns.
 using Pack16x1   = FixedShape<16, 1, 1, 256, false, false>;  // f32 [M][K] -> [M1][K1][16][1]
 using Pack16x2   = FixedShape<16, 2, 1, 256, true, false>;   // bf16/i8 [M][K] -> [M1][K1][16][2]
-using PackT1x16  = FixedShape<1, 16, 64, 4, true, true>;     // [K][N] -> [N1][K1][16][1], 0x300
-using PackT2x16  = FixedShape<2, 16, 32, 8, false, true>;    // [K][N] -> [N1][K1][16][2], 0x300
+// RHS-style packs read a block of matrix rows whose segments go to different tile rows. Blocks
+// of few, long row segments (8 rows x 2 KB) keep their rate when the memory system is slow (a
+// GPU warmed up by a long GEMM: 0.98-1.03 of a same-size copy, where 64 rows x 256 bytes fell to
+// 0.79); the many-short-rows shapes remain for matrices the long ones do not divide.
+using PackT1x16  = FixedShape<1, 16, 8, 32, true, true>;     // [K][N] -> [N1][K1][16][1], 0x300
+using PackT1x16Small = FixedShape<1, 16, 64, 4, true, true>;
+using PackT2x16  = FixedShape<2, 16, 4, 64, false, true>;    // [K][N] -> [N1][K1][16][2], 0x300
+using PackT2x16Small = FixedShape<2, 16, 32, 8, false, true>;
 using Tile16x16  = FixedShape<16, 16, 1, 16, true, false>;   // accumulator tiles
 
 template <int ES, bool IS_PACK>
@@ -518,7 +524,9 @@ int launch_staged(RelayoutArgs& a, const char* mat_base, const char* tiled_base,
   UK_TRY_FIXED(Pack16x1)
   UK_TRY_FIXED(Pack16x2)
   UK_TRY_FIXED(PackT1x16)
+  UK_TRY_FIXED(PackT1x16Small)
   UK_TRY_FIXED(PackT2x16)
+  UK_TRY_FIXED(PackT2x16Small)
   UK_TRY_FIXED(Tile16x16)
 #undef UK_TRY_FIXED
   const size_t smem = plan_staged(&a, ES, mat_base, tiled_base);

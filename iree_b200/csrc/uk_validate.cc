@@ -13,6 +13,13 @@ bool env_flag(const char* name) {
   return v && v[0] && std::strcmp(v, "0") != 0;
 }
 
+#ifdef IREE_UK_B200_EXPERIMENTS
+int debug_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+#endif
+
 bool mmt4d_types(uint32_t flags, Mmt4dTypes* t) {
   switch (flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) {
     case IREE_UK_FLAG_MMT4D_TYPE_F32F32F32: *t = {Elem::F32, Elem::F32, Elem::F32}; return true;

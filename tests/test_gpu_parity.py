@@ -227,6 +227,25 @@ def test_pack_aligned_vector_paths(tile):
                     assert np.array_equal(got, G.oracle_pack(case)), vars(case)
 
 
+@pytest.mark.parametrize("tile,outer", [
+    ((abi.PACK_F32F32, 16, 1), (16, 32)), ((abi.PACK_F32F32, 16, 1), (64, 12)),
+    ((abi.PACK_F16F16, 16, 1), (8, 64)),
+    ((abi.PACK_BF16BF16, 16, 2), (8, 64)), ((abi.PACK_BF16BF16, 16, 2), (32, 24)),
+    ((abi.PACK_I8I8, 16, 2), (12, 128)), ((abi.PACK_I8I8, 16, 2), (64, 8)),
+], ids=lambda v: "x".join(str(x) for x in v))
+@pytest.mark.parametrize("pad", ["none", "one_incomplete_tile"])
+def test_pack_rhs_style_constant_shape_kernels(tile, outer, pad):
+    """The RHS pack of a matmul ([K][N] -> [N1][K1][N0][K0], both transposes,
+    tools/e2e_matmul_benchmark.c:238-254) on matrices that the constant-shape kernels divide:
+    the long-row blocks and the many-short-rows blocks, whole blocks (bulk row copies) and
+    blocks that hold padding."""
+    case = cases.PackCase(tile[0], tile[1], tile[2], outer, 1, 1, pad, seed=77, loose=False)
+    got, path = G.run_pack_case(case)
+    assert path == abi.PATH_FAST_COPY
+    assert np.array_equal(got, G.oracle_pack(case)), vars(case)
+    G.check_device_status()
+
+
 @pytest.mark.parametrize("tile", cases.UNPACK_TILES, ids=lambda t: "t%x_%dx%d" % t)
 def test_unpack_aligned_vector_paths(tile):
     seed = 200
