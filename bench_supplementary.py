@@ -267,6 +267,16 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         r["graph_replay"]["gbs"] = gemv_bytes / r["graph_replay"]["ms_per_call"] / 1e6
         res[k] = r
 
+    # decode-shaped GEMV on a narrowed tile: bf16 1x16x2, one token against the headline weights
+    if want("mmt4d_bf16_gemv_1x28672x8192"):
+        k, r = _mmt4d_case("mmt4d_bf16_gemv_1x28672x8192", abi.MMT4D_BF16BF16F32, 1, 1792, 4096,
+                           1, 16, 2, peaks, None, torch.bfloat16, copies=1, graph_calls=20)
+        nbytes_gemv = 1792 * 4096 * 64 + 4096 * 4 + 1792 * 64
+        r["gbs"] = nbytes_gemv / r["ms"] / 1e6
+        r["frac_hbm"] = r["gbs"] / hbm
+        r["graph_replay"]["gbs"] = nbytes_gemv / r["graph_replay"]["ms_per_call"] / 1e6
+        res[k] = r
+
     if custom_matmul is not None:
         mm, mn, mk = custom_matmul
         res["matmul_rowmajor_bf16_custom_%dx%dx%d" % (mm, mn, mk)] = _matmul_rowmajor_case(

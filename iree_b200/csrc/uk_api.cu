@@ -47,7 +47,7 @@ bool testing_starve_producers() { return g_starve.load(std::memory_order_relaxed
 
 namespace {
 
-enum class Mmt4dPath { None, Generic, Tc, TcRetile, TcSw, Gemv, ZeroFill };
+enum class Mmt4dPath { None, Generic, Tc, TcRetile, TcSw, Gemv, Narrow, ZeroFill };
 
 // Kernel selection, the analogue of ukernel/mmt4d.c:105-138 (early-out, then an
 // architecture-specific tile function, else the generic one).
@@ -66,6 +66,8 @@ int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path)
     // s16u4s32: the tensor-core path once there are rows to fill a tile, else the GEMV.
     if (have_ws && p->M >= 32 && mmt4d_tc_s16u4_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
     if (mmt4d_gemv_s16u4_eligible(p)) { *path = Mmt4dPath::Gemv; return 0; }
+    // narrowed M0 with N0 = 16: weight streaming, with or without scratch
+    if (mmt4d_narrow_eligible(p)) { *path = Mmt4dPath::Narrow; return 0; }
     if (have_ws && mmt4d_tc_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
     // Without scratch, a 16-bit K0 = 1 operand ([tile][K1][16]) can still be read by TMA as an
     // MN-major tensor-core operand; K0 = 2 operands cannot and fall to the generic kernel.
@@ -86,6 +88,7 @@ int path_code(Mmt4dPath p) {
     case Mmt4dPath::TcSw: return IREE_UK_B200_PATH_TCGEN05;
     case Mmt4dPath::TcRetile: return IREE_UK_B200_PATH_TCGEN05_RETILE;
     case Mmt4dPath::Gemv: return IREE_UK_B200_PATH_GEMV;
+    case Mmt4dPath::Narrow: return IREE_UK_B200_PATH_GEMV;
     default: return IREE_UK_B200_PATH_ZERO_FILL;
   }
 }
@@ -100,6 +103,7 @@ int run_mmt4d(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, bool h
     case Mmt4dPath::None: return IREE_UK_B200_OK;
     case Mmt4dPath::ZeroFill: return launch_mmt4d_zero_fill(p, stream);
     case Mmt4dPath::Gemv: return launch_mmt4d_gemv_s16u4(p, stream);
+    case Mmt4dPath::Narrow: return launch_mmt4d_narrow(p, stream);
     case Mmt4dPath::TcRetile: return launch_mmt4d_tc(p, ws, ws_bytes, kTcVariantDefault, stream);
     case Mmt4dPath::Tc: return launch_mmt4d_tc(p, nullptr, 0, kTcVariantDirect, stream);
     case Mmt4dPath::TcSw: return launch_mmt4d_tc_sw(p, stream);
@@ -185,6 +189,12 @@ uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t fl
   if (tc_type && M0 == 16 && N0 == 16 && (g == 1 || g == 2 || g == 4 || g == 8 || g == 16))
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 && M0 == 1 && N0 == 32 && K0 == 8)
+    return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
+  // narrowed M0: the weight-streaming kernel
+  const bool narrow_type = (type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 && K0 == 2) ||
+                           (type == IREE_UK_FLAG_MMT4D_TYPE_F16F16F32 && K0 == 1) ||
+                           (type == IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32 && K0 == 2);
+  if (narrow_type && N0 == 16 && (M0 == 1 || M0 == 2 || M0 == 4 || M0 == 8))
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   return 0;
 }

@@ -48,6 +48,9 @@ int launch_mmt4d_generic(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
 int launch_mmt4d_zero_fill(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
 int launch_mmt4d_gemv_s16u4(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
 bool mmt4d_gemv_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
+// Narrowed M0 (1, 2, 4, 8) x N0 = 16 tiles of s8s8s32 / f16f16f32 / bf16bf16f32: weight streaming.
+bool mmt4d_narrow_eligible(const iree_uk_mmt4d_params_t* p);
+int launch_mmt4d_narrow(const iree_uk_mmt4d_params_t* p, cudaStream_t stream);
 
 // Output of a tensor-core mmt4d written as a row-major rows x cols matrix (the unpack folded
 // into the epilogue); p->out_buffer / out_offset / out_stride0 then describe that matrix.

@@ -7,6 +7,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <type_traits>
 
 #include "uk_common.h"
 
@@ -324,6 +325,124 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Narrowed M0 (1, 2, 4 or 8 rows) with N0 = 16: the tiles the reference's encoder picks when M
+// is small (decode, GEMV-like shapes; compiler/.../CPUEncodingExternalModels.cpp narrows M0 to
+// the next power of two) and for which it ships ISA tile functions
+// (arch/x86_64/mmt4d_x86_64_tiles.inl): s8s8s32 K0 = 2, f16f16f32 K0 = 1, bf16bf16f32 K0 = 2.
+// With so few LHS rows the call is a weight stream: every RHS byte is read once per LHS tile
+// row and used for M0 multiply-adds, so HBM bounds it and tensor cores cannot help.
+// One block per (LHS tile row, RHS tile row); its 8 warps interleave along K, each lane reads
+// 16-byte vectors of the RHS row - a vector holds one k1 step of 4 (bf16) or 8 (s8, f16)
+// neighbouring n0 rows, and a lane always meets the same rows - with four loads in flight, takes
+// the matching LHS values through L1 (the LHS tile row is a few KB), and keeps M0 x rows sums.
+// f32 sums are formed in another order than the reference's (k interleaved over lanes and
+// warps); integers are exact.
+// ---------------------------------------------------------------------------------------
+enum class NarrowType : int { S8, F16, BF16 };
+
+template <NarrowType T, int M0>
+__global__ void __launch_bounds__(256) mmt4d_narrow_kernel(GenericArgs a) {
+  constexpr int ROWS = T == NarrowType::BF16 ? 4 : 8;   // n0 rows per 16-byte vector
+  constexpr int VPT = 16 / ROWS;                        // vectors per RHS tile
+  constexpr int KSUB = 32 / VPT;                        // k1 steps per warp-wide load
+  constexpr int TILE_B = VPT * 16;                      // RHS tile bytes
+  constexpr int XB = T == NarrowType::BF16 ? 4 : 2;     // LHS bytes per (k1, m0): K0 elements
+  constexpr int U = 4;                                  // loads in flight per lane
+  using Acc = typename std::conditional<T == NarrowType::S8, int32_t, float>::type;
+  __shared__ Acc partial[8][M0][16];
+  const int64_t m1 = blockIdx.x / a.N, n1 = blockIdx.x - m1 * a.N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int v = lane % VPT, ksub = lane / VPT;
+  const char* rhs = a.rhs + n1 * a.rhs_stride_b + v * 16;
+  const char* lhs = a.lhs + m1 * a.lhs_stride_b;
+  Acc acc[M0][ROWS];
+#pragma unroll
+  for (int m = 0; m < M0; ++m)
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) acc[m][r] = Acc(0);
+
+  for (int64_t kb = int64_t(warp) * (U * KSUB); kb < a.K; kb += 8 * U * KSUB) {
+    uint4 w[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t k1 = kb + u * KSUB + ksub;
+      w[u] = k1 < a.K ? __ldg(reinterpret_cast<const uint4*>(rhs + k1 * TILE_B))
+                      : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t k1 = kb + u * KSUB + ksub;
+      if (k1 >= a.K) continue;
+      const uint32_t ww[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+      const char* xp = lhs + k1 * (M0 * XB);
+#pragma unroll
+      for (int m = 0; m < M0; ++m) {
+        if (T == NarrowType::BF16) {
+          const uint32_t x = __ldg(reinterpret_cast<const uint32_t*>(xp + m * 4));
+          const float x0 = __uint_as_float(x << 16), x1 = __uint_as_float(x & 0xFFFF0000u);
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            acc[m][r] = fmaf(__uint_as_float(ww[r] << 16), x0, acc[m][r]);
+            acc[m][r] = fmaf(__uint_as_float(ww[r] & 0xFFFF0000u), x1, acc[m][r]);
+          }
+        } else if (T == NarrowType::F16) {
+          const float x = __half2float(__ushort_as_half(__ldg(reinterpret_cast<const uint16_t*>(xp + m * 2))));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ww[j]));
+            acc[m][2 * j] = fmaf(f.x, x, acc[m][2 * j]);
+            acc[m][2 * j + 1] = fmaf(f.y, x, acc[m][2 * j + 1]);
+          }
+        } else {
+          // two s8 of the LHS as two s16; a weight word holds rows 2j (low half) and 2j + 1
+          const uint32_t xb = __ldg(reinterpret_cast<const uint16_t*>(xp + m * 2));
+          const int32_t x0 = int8_t(xb & 0xFF), x1 = int8_t(xb >> 8);
+          const uint32_t xs = (uint32_t(x0) & 0xFFFFu) | (uint32_t(x1) << 16);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int32_t lo, hi;
+            asm("dp2a.lo.s32.s32 %0, %1, %2, %3;" : "=r"(lo) : "r"(xs), "r"(ww[j]), "r"(int32_t(acc[m][2 * j])));
+            asm("dp2a.hi.s32.s32 %0, %1, %2, %3;" : "=r"(hi) : "r"(xs), "r"(ww[j]), "r"(int32_t(acc[m][2 * j + 1])));
+            acc[m][2 * j] = Acc(lo);
+            acc[m][2 * j + 1] = Acc(hi);
+          }
+        }
+      }
+    }
+  }
+  // lanes that differ only in their k1 position hold partial sums of the same rows
+#pragma unroll
+  for (int m = 0; m < M0; ++m)
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      Acc x = acc[m][r];
+#pragma unroll
+      for (int d = VPT; d < 32; d <<= 1) x += __shfl_xor_sync(0xFFFFFFFFu, x, d);
+      acc[m][r] = x;
+    }
+  if (lane < VPT) {
+#pragma unroll
+    for (int m = 0; m < M0; ++m)
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) partial[warp][m][v * ROWS + r] = acc[m][r];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < M0 * 16; e += blockDim.x) {
+    const int m = e >> 4, n0 = e & 15;
+    Acc sum = Acc(0);
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) sum += partial[w8][m][n0];
+    Acc* op = reinterpret_cast<Acc*>(a.out) + m1 * a.out_stride0 + n1 * (M0 * 16) + e;
+    if (T == NarrowType::S8) {
+      uint32_t* uo = reinterpret_cast<uint32_t*>(op);
+      *uo = a.accumulate ? *uo + uint32_t(sum) : uint32_t(sum);  // wraps like the reference's int32
+    } else {
+      *op = a.accumulate ? *op + sum : sum;
+    }
+  }
+}
+
 bool fill_args(const iree_uk_mmt4d_params_t* p, GenericArgs* a) {
   Mmt4dTypes t;
   if (!mmt4d_types(p->flags, &t)) return false;
@@ -393,6 +512,51 @@ int launch_mmt4d_zero_fill(const iree_uk_mmt4d_params_t* p, cudaStream_t stream)
   else
     mmt4d_zero_fill_kernel<uint16_t><<<int(blocks), 256, 0, stream>>>(a.out, a.out_stride0, a.M, row_elems);
   return cuda_status(cudaGetLastError());
+}
+
+bool mmt4d_narrow_eligible(const iree_uk_mmt4d_params_t* p) {
+  const uint32_t type = p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK;
+  int k0 = 0, es = 0;
+  switch (type) {
+    case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: k0 = 2; es = 1; break;
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32: k0 = 1; es = 2; break;
+    case IREE_UK_FLAG_MMT4D_TYPE_BF16BF16F32: k0 = 2; es = 2; break;
+    default: return false;
+  }
+  if (p->N0 != 16 || p->K0 != k0 || p->K < 1) return false;
+  if (p->M0 != 1 && p->M0 != 2 && p->M0 != 4 && p->M0 != 8) return false;
+  if (p->M * p->N > 0x7FFFFFFF) return false;
+  // 16-byte loads of the RHS rows, K0-element loads of the LHS
+  const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * es);
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset * es);
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * 4);
+  return (rhs % 16 == 0) && ((p->rhs_stride0 * es) % 16 == 0) && (lhs % (k0 * es) == 0) &&
+         ((p->lhs_stride0 * es) % (k0 * es) == 0) && (out % 4 == 0);
+}
+
+namespace {
+template <NarrowType T>
+int launch_narrow_m0(const GenericArgs& a, int blocks, cudaStream_t stream) {
+  switch (a.M0) {
+    case 1: mmt4d_narrow_kernel<T, 1><<<blocks, 256, 0, stream>>>(a); break;
+    case 2: mmt4d_narrow_kernel<T, 2><<<blocks, 256, 0, stream>>>(a); break;
+    case 4: mmt4d_narrow_kernel<T, 4><<<blocks, 256, 0, stream>>>(a); break;
+    default: mmt4d_narrow_kernel<T, 8><<<blocks, 256, 0, stream>>>(a); break;
+  }
+  return cuda_status(cudaGetLastError());
+}
+}  // namespace
+
+int launch_mmt4d_narrow(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
+  GenericArgs a;
+  if (!fill_args(p, &a)) return IREE_UK_B200_INVALID_ARGUMENT;
+  const int64_t blocks = a.M * a.N;
+  if (blocks <= 0) return IREE_UK_B200_OK;
+  switch (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) {
+    case IREE_UK_FLAG_MMT4D_TYPE_S8S8S32: return launch_narrow_m0<NarrowType::S8>(a, int(blocks), stream);
+    case IREE_UK_FLAG_MMT4D_TYPE_F16F16F32: return launch_narrow_m0<NarrowType::F16>(a, int(blocks), stream);
+    default: return launch_narrow_m0<NarrowType::BF16>(a, int(blocks), stream);
+  }
 }
 
 bool mmt4d_gemv_s16u4_eligible(const iree_uk_mmt4d_params_t* p) {

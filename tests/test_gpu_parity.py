@@ -170,6 +170,35 @@ def test_mmt4d_s16u4_tensor_core_path(shape, accumulate):
     assert np.array_equal(got2, got)
 
 
+NARROW_TYPES = [(abi.MMT4D_S8S8S32, 2), (abi.MMT4D_F16F16F32, 1), (abi.MMT4D_BF16BF16F32, 2)]
+
+
+@pytest.mark.parametrize("t,K0", NARROW_TYPES, ids=["s8", "f16", "bf16"])
+@pytest.mark.parametrize("M0", [1, 2, 4, 8])
+@pytest.mark.parametrize("shape", [(1, 1, 1), (1, 7, 33), (3, 5, 64), (1, 40, 1000), (2, 3, 129)],
+                         ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_narrowed_m0_weight_streaming(t, K0, M0, shape, accumulate):
+    """Narrowed M0 x 16 tiles (arch/x86_64/mmt4d_x86_64_tiles.inl:30-60 has ISA functions for
+    them): the weight-streaming kernel, with and without scratch. Small-integer values: exact."""
+    M, N, K = shape
+    case = cases.Mmt4dCase(t, M0, 16, K0, M, N, K, accumulate, seed=43, mode="exact", loose=False)
+    want = G.oracle_mmt4d(case)
+    for ws in (True, False):
+        got, path = G.run_mmt4d_case(case, use_workspace=ws)
+        assert path == abi.PATH_GEMV
+        assert np.array_equal(got, want), case.label()
+
+
+@pytest.mark.parametrize("t,K0", NARROW_TYPES[1:], ids=["f16", "bf16"])
+def test_mmt4d_narrowed_m0_normal_values(t, K0):
+    case = cases.Mmt4dCase(t, 4, 16, K0, 1, 96, 2048, 1, seed=47, mode="normal", loose=False)
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_GEMV
+    want = G.oracle_mmt4d(case)
+    assert cases.rel_frobenius(got.view(np.float32), want.view(np.float32)) <= 1e-3
+
+
 def test_mmt4d_int_wraparound():
     """int32 sums wrap modulo 2^32 like the reference's (extreme s8 values, long K, and an
     initial accumulator near INT32_MAX)."""
