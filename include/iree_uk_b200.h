@@ -99,6 +99,9 @@ typedef int64_t iree_uk_index_t;
 #define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F16F16F16 0x0400
 #define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16F32 0x0500
 #define IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16BF16 0x0600
+/* Not a reference flag (the reference uses bits 0-15 only): answer what the reference's own
+ * x86-64 build answers for params->cpu_data instead of this library's tile choice. */
+#define IREE_UK_B200_FLAG_QUERY_TILE_SIZES_REFERENCE_X86_64 0x10000
 
 /*===----------------------------------------------------------------------===*/
 /* Parameter structs — field-for-field the reference's                         */
@@ -544,7 +547,12 @@ IREE_UK_B200_EXPORT int iree_uk_b200_unpack_path(const iree_uk_unpack_params_t* 
  * x86-64 encoder picks (compiler/src/iree/compiler/Codegen/ExternalInterfaces/
  * CPUEncodingExternalModels.cpp:479-585) — and, for f32 (no tensor-core kernel here), the
  * 16x16x1 the reference answers on AVX-512 (ukernel/arch/x86_64/
- * query_tile_sizes_x86_64_entry_point.c:10-25). */
+ * query_tile_sizes_x86_64_entry_point.c:10-25).
+ * With IREE_UK_B200_FLAG_QUERY_TILE_SIZES_REFERENCE_X86_64 set in params->flags the call answers
+ * exactly what the reference's x86-64 build answers for params->cpu_data (then required, not
+ * ignored): f32 16x1x16 / 8x1x8 / 8x1x4 and i8 16x2x16 / 8x2x8 / 8x2x4 by AVX-512 / AVX2 / neither
+ * (query_tile_sizes_x86_64_entry_point.c:10-64), and the generic 8x4x8 for the other operations
+ * (query_tile_sizes.c:35-41) - for callers that keep a CPU pipeline's packed layouts. */
 IREE_UK_B200_EXPORT int iree_uk_b200_query_tile_sizes_2d(
     const iree_uk_query_tile_sizes_2d_params_t* params,
     iree_uk_query_tile_sizes_2d_out_params_t* out_params);

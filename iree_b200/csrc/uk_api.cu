@@ -2,6 +2,7 @@
 #include <cstdio>
 #include <cstring>
 #include <atomic>
+#include <initializer_list>
 #include <mutex>
 #include <vector>
 
@@ -592,6 +593,37 @@ int iree_uk_b200_query_tile_sizes_2d(const iree_uk_query_tile_sizes_2d_params_t*
                                      iree_uk_query_tile_sizes_2d_out_params_t* out_params) {
   if (!params || !out_params) return IREE_UK_B200_INVALID_ARGUMENT;
   int64_t m = 16, n = 16, k = 1;
+  const bool reference = (params->flags & IREE_UK_B200_FLAG_QUERY_TILE_SIZES_REFERENCE_X86_64) != 0;
+  if (params->flags & ~(IREE_UK_FLAG_QUERY_TILE_SIZES_OPERAND_ROLE_MASK |
+                        IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MASK |
+                        IREE_UK_B200_FLAG_QUERY_TILE_SIZES_REFERENCE_X86_64))
+    return IREE_UK_B200_INVALID_ARGUMENT;
+  if (reference) {
+    // The reference's x86-64 answers (arch/x86_64/query_tile_sizes_x86_64_entry_point.c:10-64,
+    // feature predicates arch/x86_64/common_x86_64.h:26-53, bit positions
+    // schemas/cpu_feature_bits.inl:85-112); other operations get query_tile_sizes.c:35-41.
+    if (!params->cpu_data) return IREE_UK_B200_INVALID_ARGUMENT;
+    const uint64_t d = params->cpu_data[0];
+    auto all = [&](std::initializer_list<int> bits) {
+      for (int b : bits) if (!((d >> b) & 1)) return false;
+      return true;
+    };
+    const bool avx2 = all({15, 11, 14});                       // AVX2, FMA, F16C
+    const bool avx512 = avx2 && all({20, 24, 23, 22, 21});     // F, BW, DQ, VL, CD
+    const bool vnni = avx512 && all({28});
+    switch (params->flags & IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MASK) {
+      case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F32F32F32:
+        k = 1; m = avx512 ? 16 : 8; n = avx512 ? 16 : (avx2 ? 8 : 4); break;
+      case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_I8I8I32:
+        k = 2; m = vnni ? 16 : 8; n = vnni ? 16 : (avx2 ? 8 : 4); break;
+      case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F16F16F32:
+      case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F16F16F16:
+      case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16F32:
+      case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_BF16BF16BF16:
+        m = 8; k = 4; n = 8; break;
+      default: return IREE_UK_B200_INVALID_ARGUMENT;
+    }
+  } else
   switch (params->flags & IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MASK) {
     case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_F32F32F32: k = 1; break;
     case IREE_UK_FLAG_QUERY_TILE_SIZES_OPERATION_MATMUL_I8I8I32: k = 2; break;

@@ -233,9 +233,15 @@ def unpack_path(params):
     return r
 
 
-def query_tile_sizes_2d(flags, size0=0, size1=0):
-    """``iree_uk_query_tile_sizes_2d``: (tile_size0, tile_size1)."""
-    p = abi.QueryTileSizes2dParams(flags=flags, size0=size0, size1=size1, cpu_data=None)
+QUERY_REFERENCE_X86_64 = 0x10000
+
+
+def query_tile_sizes_2d(flags, size0=0, size1=0, cpu_data0=None):
+    """``iree_uk_query_tile_sizes_2d``: (tile_size0, tile_size1). With ``QUERY_REFERENCE_X86_64``
+    in ``flags`` and ``cpu_data0`` (the first cpu_data word) the reference's x86-64 answer."""
+    words = (C.c_uint64 * 8)(cpu_data0 or 0) if cpu_data0 is not None else None
+    p = abi.QueryTileSizes2dParams(flags=flags, size0=size0, size1=size1,
+                                   cpu_data=C.cast(words, C.c_void_p) if words is not None else None)
     o = abi.QueryTileSizes2dOut()
     _check(lib.iree_uk_b200_query_tile_sizes_2d(C.addressof(p), C.addressof(o)),
            "query_tile_sizes_2d")

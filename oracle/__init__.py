@@ -162,6 +162,19 @@ def unpack(p, impl="oracle", features="host"):
                          C.addressof(cd))
 
 
+def query_tile_sizes_2d_ref(flags, cpu_data0):
+    """The compiled reference's iree_uk_query_tile_sizes_2d for one cpu_data[0] word:
+    (tile_size0, tile_size1)."""
+    r = ref()
+    cd = (C.c_uint64 * 8)(cpu_data0)
+    p = abi.QueryTileSizes2dParams(flags=flags, size0=0, size1=0, cpu_data=C.cast(cd, C.c_void_p))
+    o = abi.QueryTileSizes2dOut()
+    r.iree_uk_query_tile_sizes_2d.restype = None
+    r.iree_uk_query_tile_sizes_2d.argtypes = [C.c_void_p, C.c_void_p]
+    r.iree_uk_query_tile_sizes_2d(C.addressof(p), C.addressof(o))
+    return int(o.tile_size0), int(o.tile_size1)
+
+
 def _chunks(total, parts):
     parts = max(1, min(parts, total))
     base, rem = divmod(total, parts)

@@ -216,6 +216,30 @@ def test_query_tile_sizes():
         uk.query_tile_sizes_2d(0x0204)
 
 
+def test_query_tile_sizes_reference_answers_under_the_compat_flag():
+    """With the compat flag the call answers what the reference's x86-64 build answers for a
+    cpu_data word; checked against the compiled reference itself where it is present, for every
+    operation, role and feature level."""
+    import oracle
+    bit = lambda *bs: sum(1 << b for b in bs)
+    avx2 = bit(15, 11, 14)
+    avx512 = avx2 | bit(20, 21, 22, 23, 24)
+    levels = [0, avx2, avx512, avx512 | bit(28), avx512 | bit(28, 31)]
+    expect_f32 = {0: (8, 1, 4), avx2: (8, 1, 8)}
+    for d in levels:
+        for op in range(1, 7):
+            for role in (1, 2, 3):
+                flags = (op << 8) | role
+                got = uk.query_tile_sizes_2d(flags | uk.QUERY_REFERENCE_X86_64, cpu_data0=d)
+                if oracle.ref_available():
+                    assert got == oracle.query_tile_sizes_2d_ref(flags, d), (hex(d), op, role)
+    assert uk.query_tile_sizes_2d(0x0103 | uk.QUERY_REFERENCE_X86_64, cpu_data0=0) == (8, 4)
+    assert uk.query_tile_sizes_2d(0x0203 | uk.QUERY_REFERENCE_X86_64, cpu_data0=avx512 | bit(28)) == (16, 16)
+    assert uk.query_tile_sizes_2d(0x0501 | uk.QUERY_REFERENCE_X86_64, cpu_data0=avx512) == (8, 4)
+    with pytest.raises(uk.UkernelError):   # the compat answer needs cpu_data
+        uk.query_tile_sizes_2d(0x0101 | uk.QUERY_REFERENCE_X86_64)
+
+
 def test_shard_params_partition_n():
     full = _mmt4d(abi.MMT4D_BF16BF16F32, M=8, N=30, K=16)
     covered = []
