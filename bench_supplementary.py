@@ -304,7 +304,14 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         res["matmul_rowmajor_bf16_8192x28672x8192"] = _matmul_rowmajor_case(
             8192, 28672, 8192, bf16_peak)
 
-    # pack f32 8192x8192 -> [512][8192][16][1]; TRANSPOSE_INNER variant; RHS-style 0x301
+    # pack f32 8192x8192 -> [512][8192][16][1]; TRANSPOSE_INNER variant; RHS-style 0x301.
+    # The bandwidth-bound group starts after a two-second pause: seconds of GEMM work just before
+    # leave the memory system slower for a second or two (a same-size device copy measures
+    # 5.4 instead of 5.9 TB/s), and these figures are about the kernels, not about what ran before.
+    if only is None:
+        import time
+        torch.cuda.synchronize()
+        time.sleep(2.0)
     n = 8192
     src = torch.randn(n * n, device="cuda")
     dst = torch.empty(n * n, device="cuda")
