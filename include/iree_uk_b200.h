@@ -465,6 +465,18 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_host(const iree_uk_mmt4d_params_t* pa
                                                 void* device_arena, size_t arena_bytes,
                                                 void* cu_stream);
 
+/* As iree_uk_b200_mmt4d_host, for a caller that has already brought the LHS to the device:
+ * params->lhs_buffer / lhs_offset / lhs_stride0 are ignored and the LHS tile rows are read from
+ * `device_lhs`, `device_lhs_stride0` elements apart (device memory of the current device, 16-byte
+ * aligned rows for the tensor-core kernels, ready once the work already enqueued on `cu_stream`
+ * has run); RHS and output stay host buffers. This is the per-GPU step of an N-sharded
+ * host-buffer mmt4d in which the LHS crosses PCIe once - each GPU uploads 1/G of its tile rows -
+ * and is then all-gathered over NVLink, instead of being uploaded in full to every GPU. No
+ * counterpart in the reference, whose callers never shard. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_host_resident_lhs(
+    const iree_uk_mmt4d_params_t* params, const void* device_lhs,
+    iree_uk_index_t device_lhs_stride0, void* device_arena, size_t arena_bytes, void* cu_stream);
+
 /* Replaces iree_uk_mmt4d_info (ukernel/mmt4d.h:25-27, mmt4d.c:143-149): bit 0 is set when
  * a tensor-core (tcgen05) kernel exists for this (types, M0, N0, K0). */
 IREE_UK_B200_EXPORT uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0,

@@ -30,6 +30,7 @@ SIGNATURES = {
     "iree_uk_b200_mmt4d_static_scratch": (C.c_int, [_P, _P]),
     "iree_uk_b200_mmt4d_host_arena_size": (_sz, [_P]),
     "iree_uk_b200_mmt4d_host": (C.c_int, [_P, _P, _sz, _P]),
+    "iree_uk_b200_mmt4d_host_resident_lhs": (C.c_int, [_P, _P, _I, _P, _sz, _P]),
     "iree_uk_b200_mmt4d_ws_peers": (C.c_int, [_P, _P, C.c_int, _P, _sz, _P]),
     "iree_uk_b200_mmt4d_ws_multicast": (C.c_int, [_P, _P, _P, _sz, _P]),
     "iree_uk_b200_mmt4d_ws_unpacked": (C.c_int, [_P, _I, _I, _P, _sz, _P]),

@@ -153,8 +153,32 @@ size_t iree_uk_b200_mmt4d_host_arena_size(const iree_uk_mmt4d_params_t* params) 
   return size_t(a.total);
 }
 
+namespace {
+int mmt4d_host_impl(const iree_uk_mmt4d_params_t* params, const void* device_lhs,
+                    iree_uk_index_t device_lhs_stride0, void* device_arena, size_t arena_bytes,
+                    void* cu_stream);
+}  // namespace
+
 int iree_uk_b200_mmt4d_host(const iree_uk_mmt4d_params_t* params, void* device_arena,
                             size_t arena_bytes, void* cu_stream) {
+  return mmt4d_host_impl(params, nullptr, 0, device_arena, arena_bytes, cu_stream);
+}
+
+int iree_uk_b200_mmt4d_host_resident_lhs(const iree_uk_mmt4d_params_t* params,
+                                         const void* device_lhs,
+                                         iree_uk_index_t device_lhs_stride0, void* device_arena,
+                                         size_t arena_bytes, void* cu_stream) {
+  if (!device_lhs || device_lhs_stride0 < 0) return IREE_UK_B200_INVALID_ARGUMENT;
+  return mmt4d_host_impl(params, device_lhs, device_lhs_stride0, device_arena, arena_bytes,
+                         cu_stream);
+}
+
+}  // extern "C"
+
+namespace {
+int mmt4d_host_impl(const iree_uk_mmt4d_params_t* params, const void* device_lhs,
+                    iree_uk_index_t device_lhs_stride0, void* device_arena, size_t arena_bytes,
+                    void* cu_stream) {
   const int rc = validate_mmt4d(params);
   if (rc) return rc;
   const iree_uk_mmt4d_params_t& p = *params;
@@ -191,9 +215,17 @@ int iree_uk_b200_mmt4d_host(const iree_uk_mmt4d_params_t* params, void* device_a
 
   Chunk ch[kMaxChunks], lb_[kLhsBlocks];
   const int nch = make_chunks(p.N, ch);
-  const int nlb = make_lhs_blocks(p.M, lb_);
+  // With the LHS already on the device there is nothing to upload block by block: one block.
+  int nlb = make_lhs_blocks(p.M, lb_);
+  if (device_lhs) {
+    nlb = 1;
+    lb_[0].begin = 0;
+    lb_[0].count = p.M;
+  }
+  const char* d_lhs_rows = device_lhs ? static_cast<const char*>(device_lhs) : d_lhs;
+  const int64_t d_lhs_row_bytes = device_lhs ? device_lhs_stride0 * lb / 8 : a.lhs_row_bytes;
   auto upload_lhs_block = [&](int i) -> bool {
-    if (lhs_w > 0 &&
+    if (!device_lhs && lhs_w > 0 &&
         cudaMemcpy2DAsync(d_lhs + lb_[i].begin * a.lhs_row_bytes, size_t(a.lhs_row_bytes),
                           h_lhs + lb_[i].begin * h_lhs_pitch, size_t(h_lhs_pitch), size_t(lhs_w),
                           size_t(lb_[i].count), cudaMemcpyHostToDevice, pipe->h2d) != cudaSuccess)
@@ -216,7 +248,7 @@ int iree_uk_b200_mmt4d_host(const iree_uk_mmt4d_params_t* params, void* device_a
         return IREE_UK_B200_CUDA_ERROR;
     }
     iree_uk_mmt4d_params_t q = p;
-    q.lhs_buffer = d_lhs + mb * a.lhs_row_bytes; q.lhs_offset = 0; q.lhs_stride0 = a.lhs_row_bytes * 8 / lb;
+    q.lhs_buffer = d_lhs_rows + mb * d_lhs_row_bytes; q.lhs_offset = 0; q.lhs_stride0 = d_lhs_row_bytes * 8 / lb;
     q.rhs_buffer = d_rhs + c.begin * a.rhs_row_bytes; q.rhs_offset = 0; q.rhs_stride0 = a.rhs_row_bytes * 8 / rb;
     q.out_buffer = d_slab; q.out_offset = 0; q.out_stride0 = c.count * int64_t(p.M0) * p.N0;
     q.M = mc;
@@ -265,5 +297,4 @@ int iree_uk_b200_mmt4d_host(const iree_uk_mmt4d_params_t* params, void* device_a
 #undef UK_CUDA
   return IREE_UK_B200_OK;
 }
-
-}  // extern "C"
+}  // namespace

@@ -39,6 +39,42 @@ def gather_output(slab, M, N, tile_elems, group=None, stream=None):
     return full
 
 
+class HostShardedMmt4d:
+    """The N-sharded mmt4d on HOST buffers: every rank holds the same LHS and its own RHS tile
+    rows in (pinned) host memory and wants its own output slab in host memory.
+
+    Uploading the whole LHS to every GPU sends it over PCIe ``world`` times, and the ranks of one
+    machine share the host side of those links. Here the LHS crosses PCIe once: rank r uploads
+    tile rows [r*M/world, (r+1)*M/world) into its place in a device buffer of the whole LHS, an
+    all-gather over NVLink (NCCL, in place) completes that buffer on every GPU, and
+    ``iree_uk_b200_mmt4d_host_resident_lhs`` runs the rest (RHS chunks in, kernels, output slabs
+    out, pipelined). M must be divisible by the world size. ``params`` is this rank's
+    ``Mmt4dParams`` with host pointers (as for ``ukernel.mmt4d_host``); ``host_lhs`` a pinned
+    CPU tensor holding the whole LHS with tight tile rows."""
+
+    def __init__(self, params, host_lhs, group=None):
+        import torch
+        import torch.distributed as dist
+        self.dist, self.group, self.torch = dist, group, torch
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if params.M % self.world:
+            raise ValueError("HostShardedMmt4d needs M divisible by the world size")
+        self.params, self.host_lhs = params, host_lhs
+        self.lhs_dev = torch.empty_like(host_lhs, device="cuda")
+        self.row_elems = host_lhs.numel() // params.M
+        per = (params.M // self.world) * self.row_elems
+        self.my_dev = self.lhs_dev.view(-1)[self.rank * per:(self.rank + 1) * per]
+        self.my_host = host_lhs.view(-1)[self.rank * per:(self.rank + 1) * per]
+        self.arena = torch.empty(uk.mmt4d_host_arena_size(params), dtype=torch.uint8, device="cuda")
+        self.h2d_bytes_lhs = per * host_lhs.element_size()
+
+    def run(self, stream=None):
+        """Enqueues one call; the host output is complete once ``stream`` has been synchronised."""
+        self.my_dev.copy_(self.my_host, non_blocking=True)
+        self.dist.all_gather_into_tensor(self.lhs_dev.view(-1), self.my_dev, group=self.group)
+        uk.mmt4d_host_resident_lhs(self.params, self.lhs_dev, self.row_elems, self.arena, stream)
+
+
 class PeerOutputs:
     """The other ranks' copies of a replicated output buffer, addressable from this GPU.
 

@@ -63,6 +63,14 @@ def mmt4d_host(params, arena, stream=None):
                                        _stream_handle(stream)), "mmt4d_host")
 
 
+def mmt4d_host_resident_lhs(params, device_lhs, device_lhs_stride0, arena, stream=None):
+    """``mmt4d_host`` with the LHS already on the device (``device_lhs``: a CUDA tensor of tile
+    rows ``device_lhs_stride0`` elements apart); RHS and output are host buffers in ``params``."""
+    _check(lib.iree_uk_b200_mmt4d_host_resident_lhs(
+        C.addressof(params), device_lhs.data_ptr(), device_lhs_stride0, arena.data_ptr(),
+        arena.numel() * arena.element_size(), _stream_handle(stream)), "mmt4d_host_resident_lhs")
+
+
 def mmt4d_peers(params, peer_out_ptrs, workspace, stream=None):
     """mmt4d whose output tiles are also stored, by the same kernel, to the buffers at
     ``peer_out_ptrs`` (device addresses valid on this GPU, usually other GPUs' memory opened

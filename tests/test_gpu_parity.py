@@ -366,6 +366,38 @@ def test_mmt4d_host_buffers(spec):
     assert np.array_equal(out.numpy(), want)
 
 
+@pytest.mark.parametrize("spec", [
+    (abi.MMT4D_S8S8S32, 16, 16, 2, 24, 40, 64, 1, "exact"),
+    (abi.MMT4D_BF16BF16F32, 16, 16, 2, 9, 17, 33, 0, "exact"),
+    (abi.MMT4D_S8S8S32, 9, 6, 3, 5, 7, 13, 1, "exact"),
+], ids=lambda s: "t%x_%dx%dx%d_%dx%dx%d" % s[:7])
+def test_mmt4d_host_buffers_with_device_resident_lhs(spec):
+    """The host-pointer entry point with the LHS already on the device (the per-GPU step of the
+    sharded host-buffer call): RHS and output stay host buffers with loose strides and offsets,
+    the LHS is a device copy with its own row pitch; whole host output equal to the reference's."""
+    import torch
+    from iree_b200 import ukernel as uk
+    t, M0, N0, K0, M, N, K, acc, mode = spec
+    case = cases.Mmt4dCase(t, M0, N0, K0, M, N, K, acc, seed=43, mode=mode, loose=True)
+    want = G.oracle_mmt4d(case)
+    es = cases.KIND_BITS[case.kinds[0]] // 8
+    row = K * M0 * K0
+    pitch = (row * es + 15) // 16 * 16 // es + 16 // es     # a looser, 16-byte aligned row pitch
+    host = np.zeros(M * pitch * es, dtype=np.uint8)
+    src = case.lhs[case.lhs_offset * es:]
+    for i in range(M):
+        host[i * pitch * es:i * pitch * es + row * es] = src[i * case.lhs_stride0 * es:
+                                                             i * case.lhs_stride0 * es + row * es]
+    d_lhs = torch.from_numpy(host).cuda()
+    rhs = torch.from_numpy(case.rhs.copy()).pin_memory()
+    out = torch.from_numpy(case.out_init.copy()).pin_memory()
+    p = case.params(0, rhs.data_ptr(), out.data_ptr())
+    arena = torch.empty(max(uk.mmt4d_host_arena_size(p), 256), dtype=torch.uint8, device="cuda")
+    uk.mmt4d_host_resident_lhs(p, d_lhs, pitch, arena)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.numpy(), want)
+
+
 @pytest.mark.parametrize("t", [abi.MMT4D_F16F16F32, abi.MMT4D_BF16BF16F32], ids=["f16", "bf16"])
 @pytest.mark.parametrize("shape", [(1, 1, 1), (8, 16, 64), (9, 17, 65), (24, 40, 31), (16, 32, 200)],
                          ids=lambda s: "%dx%dx%d" % s)
