@@ -305,6 +305,9 @@ def per_config_rooflines(supp, peaks):
            "mmt4d_s16u4s32_prefill_8192x14336x4096",
            "split_s16 + unpack_u4 + mmt4d_tc2_kernel<int> (two i8 products per term)", 2 * burst,
            scale=2.0)
+    tensor("mmt4d_s16s16s32_4096x4096x4096_as_8bit_tensor_work", "mmt4d_s16s16s32_4096x4096x4096",
+           "retile_split_s16 + mmt4d_tc2_kernel<int> (four i8 products per term)", 2 * burst,
+           scale=4.0)
     memory("mmt4d_s16u4s32_gemv_1x14336x4096_per_call", "mmt4d_s16u4s32_gemv_1x14336x4096",
            "mmt4d_gemv_s16u4_kernel")
     memory("mmt4d_s16u4s32_gemv_1x14336x4096_graph_replay", "mmt4d_s16u4s32_gemv_1x14336x4096",

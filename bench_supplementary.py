@@ -257,6 +257,12 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
                            448, 512, 1, 32, 8, peaks, None)
         r["frac_of_2x_bf16_burst_counting_both_byte_products"] = 2 * r["tops"] / (2 * bf16_peak)
         res[k] = r
+    # s16s16s32 16x16x2: four 8-bit tensor-core products per s16 x s16 term
+    if want("mmt4d_s16s16s32_4096x4096x4096"):
+        k, r = _mmt4d_case("mmt4d_s16s16s32_4096x4096x4096", abi.MMT4D_S16S16S32, 256, 256, 2048,
+                           16, 16, 2, peaks, None)
+        r["frac_of_2x_bf16_burst_counting_all_four_byte_products"] = 4 * r["tops"] / (2 * bf16_peak)
+        res[k] = r
     # decode GEMV s16u4s32: bytes are the algorithmic figure (weights + vector + output)
     if want("mmt4d_s16u4s32_gemv_1x14336x4096"):
         k, r = _mmt4d_case("mmt4d_s16u4s32_gemv_1x14336x4096", abi.MMT4D_S16U4S32, 1, 448, 512,

@@ -62,6 +62,8 @@ bool mmt4d_tc_operands_eligible(const iree_uk_mmt4d_params_t* p);
 bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p);
 // s16u4s32 1x32x8 with enough rows to fill tensor-core tiles (two byte planes x u8 weights).
 bool mmt4d_tc_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
+// s16s16s32 16x16x2 (two byte planes of both operands, four 8-bit products per term).
+bool mmt4d_tc_s16s16_eligible(const iree_uk_mmt4d_params_t* p);
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 // `peer_out_buffers`: optional device pointers (usually on other GPUs) that stand for
 // p->out_buffer in further copies of the output; every tile is stored to all of them too.

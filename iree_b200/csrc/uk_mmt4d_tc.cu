@@ -253,6 +253,18 @@ bool mmt4d_tc_s16u4_eligible(const iree_uk_mmt4d_params_t* p) {
   return true;
 }
 
+bool mmt4d_tc_s16s16_eligible(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) != IREE_UK_FLAG_MMT4D_TYPE_S16S16S32) return false;
+  if (p->M0 != 16 || p->N0 != 16 || p->K0 != 2 || p->K < 1 || p->M < 1 || p->N < 1) return false;
+  const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * 2);
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset * 2);
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * 4);
+  if ((lhs | rhs | out) & 15) return false;
+  if ((p->lhs_stride0 * 2) % 16 || (p->rhs_stride0 * 2) % 16 || (p->out_stride0 * 4) % 16) return false;
+  if ((p->M + 7) / 8 * ((p->N + 3) / 4) > 0x3FFFFFFF) return false;
+  return true;
+}
+
 namespace {
 
 struct S16U4Layout {
@@ -422,6 +434,122 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   return cuda_status(cudaGetLastError());
 }
 
+// ---- s16s16s32 (M0 = N0 = 16, K0 = 2) on the tensor cores -----------------------------------
+// x = 256 * hi + lo with hi the signed high byte and lo the unsigned low byte of an s16, so
+// sum(a * b) = 65536 * sum(ha * hb) + 256 * (sum(ha * lb) + sum(la * hb)) + sum(la * lb): four
+// 8-bit tensor-core products per term into three s32 accumulators, recombined modulo 2^32 by the
+// epilogue - which is the reference's own wrapping int32 arithmetic (mmt4d_tile_generic.c).
+struct S16S16Layout {
+  int64_t pitch, plane_a, plane_b;
+};
+S16S16Layout s16s16_layout(const iree_uk_mmt4d_params_t* p) {
+  S16S16Layout l;
+  l.pitch = round_up(p->K * 2, 128);
+  l.plane_a = round_up(p->M * 16 * l.pitch, 1024);
+  l.plane_b = round_up(p->N * 16 * l.pitch, 1024);
+  return l;
+}
+
+int launch_mmt4d_tc_s16s16(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes,
+                           cudaStream_t stream) {
+  if (!mmt4d_tc_s16s16_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
+  uint32_t* status = device_status_word();
+  if (!status) return IREE_UK_B200_CUDA_ERROR;
+  const S16S16Layout l = s16s16_layout(p);
+  if (!ws || ws_bytes < size_t(2 * (l.plane_a + l.plane_b))) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+  const DeviceInfo* di = device_info();
+  if (!di) return IREE_UK_B200_CUDA_ERROR;
+  KernelTiming* timing = kernel_timing();
+  cudaEvent_t* tev = timing ? timing->next_slot() : nullptr;
+  if (tev) KernelTiming::record(tev[0], stream);
+
+  char* a_hi = static_cast<char*>(ws);
+  char* b_hi = a_hi + 2 * l.plane_a;
+  {
+    const int64_t kchunks = (p->K + 255) / 256;
+    const SplitOperand a = {static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * 2,
+                            p->lhs_stride0 * 2, a_hi, l.plane_a, p->M * kchunks};
+    const SplitOperand b = {static_cast<const char*>(p->rhs_buffer) + p->rhs_offset * 2,
+                            p->rhs_stride0 * 2, b_hi, l.plane_b, p->N * kchunks};
+    if (a.blocks + b.blocks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
+    retile_split_s16_kernel<<<int(a.blocks + b.blocks), 256, 0, stream>>>(a, b, l.pitch, p->K,
+                                                                        int(kchunks));
+    if (cudaGetLastError() != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  }
+
+  TcParams P;
+  std::memset(&P, 0, sizeof P);
+  const int64_t kbytes = p->K * 2, rows = p->M * 16, ncols = p->N * 16;
+  // 128 accumulator columns x 3 accumulators leave room for one buffer only; narrower problems
+  // (64 columns or fewer) keep two.
+  const int bn = int(std::min<int64_t>(128, round_up(ncols, 16)));
+  const int pair_clusters = di->pair_clusters[1][0];
+  const bool pair = bn == 128 && rows >= 256 && pair_clusters >= 1 &&
+                    ((rows + 255) / 256) * ((ncols + 127) / 128) >= 74;
+  const int tile_m = pair ? 2 * BM : BM;
+  const int b_rows = pair ? bn / 2 : bn;
+  const uint64_t da[3] = {uint64_t(kbytes), uint64_t(rows), 2};
+  const uint64_t db[3] = {uint64_t(kbytes), uint64_t(ncols), 2};
+  const uint64_t sa[2] = {uint64_t(l.pitch), uint64_t(l.plane_a)};
+  const uint64_t sb[2] = {uint64_t(l.pitch), uint64_t(l.plane_b)};
+  const uint32_t ba[3] = {128, BM, 1};
+  const uint32_t bb[3] = {128, uint32_t(b_rows), 1};
+  if (!encode_map(&P.map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_hi, da, sa, ba, CU_TENSOR_MAP_SWIZZLE_128B) ||
+      !encode_map(&P.map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, b_hi, db, sb, bb, CU_TENSOR_MAP_SWIZZLE_128B))
+    return IREE_UK_B200_CUDA_ERROR;
+  // box 0: high plane, box 1: low plane
+  P.sa = {2, BM * 128, {128, 0, 0}, {0, tile_m, 0}, {0, 0, 1}, {0, pair ? BM : 0, 0}};
+  P.sb = {2, b_rows * 128, {128, 0, 0}, {0, bn, 0}, {0, 0, 1}, {0, pair ? b_rows : 0, 0}};
+  P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
+  P.desc_lbo_a = P.desc_lbo_b = 1;
+  P.kadv_a = P.kadv_b = 2;
+  P.kbox_units_a = uint32_t(BM * 128) >> 4;      // from the high to the low plane tile
+  P.kbox_units_b = uint32_t(b_rows * 128) >> 4;
+  // accumulate s32; the operands' sign bits are set per product by the issuing thread
+  P.idesc = (2u << 4) | (uint32_t(bn >> 3) << 17) | (uint32_t(tile_m >> 4) << 24);
+  P.quad = 1;
+  P.acc_bufs = 2 * 3 * bn <= 512 ? 2 : 1;
+  P.kboxes = 1;
+  P.mma_per_box = 4;
+  P.stage_bytes_a = 2 * BM * 128;
+  P.stage_bytes_b = 2 * b_rows * 128;
+  P.num_kb = int((kbytes + 127) / 128);
+  P.bn = bn;
+  P.m_tiles = int((rows + tile_m - 1) / tile_m);
+  P.n_tiles = int((ncols + bn - 1) / bn);
+  P.num_work = P.tail_first = P.m_tiles * P.n_tiles;
+  P.tail_split = 1;
+  P.group_m = std::min(P.m_tiles, pair ? 8 : 16);
+  P.out = static_cast<char*>(p->out_buffer) + p->out_offset * 4;
+  P.out_stride0 = p->out_stride0;
+  P.M1 = p->M;
+  P.N1 = p->N;
+  P.accumulate = (p->flags & IREE_UK_FLAG_MMT4D_ACCUMULATE) ? 1 : 0;
+  P.out_is_int = 1;
+  P.status = status;
+  set_wait_policy(&P);
+  const int stage_bytes = P.stage_bytes_a + P.stage_bytes_b;
+  P.num_stages = std::max(2, std::min(kMaxStages, 200 * 1024 / stage_bytes));
+  const size_t smem = size_t(P.num_stages) * stage_bytes + 1024;
+  if (smem > size_t(di->max_smem)) return IREE_UK_B200_CUDA_ERROR;
+  if (tev) KernelTiming::record(tev[1], stream);
+  cudaError_t e;
+  if (pair) {
+    const int grid = 2 * std::min(P.m_tiles * P.n_tiles, pair_clusters);
+    e = launch_main(pair_kernel(true, 0), grid, 2, smem, stream, P);
+  } else {
+    const int grid = std::min(P.m_tiles * P.n_tiles, di->sms);
+    e = launch_main(mmt4d_tc_kernel<true>, grid, 1, smem, stream, P);
+  }
+  if (e != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+  if (tev) {
+    KernelTiming::record(tev[2], stream);
+    timing->calls.fetch_add(1, std::memory_order_relaxed);
+  }
+  return cuda_status(cudaGetLastError());
+}
+
 }  // namespace
 
 // Operand side of the tensor-core path's conditions: a tensor-core triple, 16x16 tiles, a K0
@@ -465,6 +593,11 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
     if (p->M0 != 1 || p->N0 != 32 || p->K0 != 8 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
     const S16U4Layout l = s16u4_layout(p);
     return size_t(2 * l.plane_bytes + l.w_bytes);
+  }
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32) {
+    if (p->M0 != 16 || p->N0 != 16 || p->K0 != 2 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
+    const S16S16Layout l = s16s16_layout(p);
+    return size_t(2 * (l.plane_a + l.plane_b));
   }
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti)) return 0;
@@ -527,10 +660,11 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   if (num_peers < 0 || num_peers > IREE_UK_B200_MAX_PEERS || (num_peers && !peer_out_buffers))
     return IREE_UK_B200_INVALID_ARGUMENT;
   // Peer copies exist for the plain tiled epilogue only.
-  if ((num_peers || multicast_out) && (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
-    return IREE_UK_B200_UNSUPPORTED;
-  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
-    return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
+  const uint32_t type = p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK;
+  const bool planes = type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 || type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32;
+  if ((num_peers || multicast_out || prepared_rhs || rm) && planes) return IREE_UK_B200_UNSUPPORTED;
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32) return launch_mmt4d_tc_s16s16(p, ws, ws_bytes, stream);
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || !(rm ? mmt4d_tc_operands_eligible(p) : mmt4d_tc_eligible(p)))
     return IREE_UK_B200_UNSUPPORTED;

@@ -47,6 +47,8 @@ struct TcParams {
   uint32_t idesc;
   uint32_t idesc2;      // dual-LHS mode: instruction descriptor of the second (low-byte) MMA
   int32_t dual;         // s16u4s32: two LHS planes (signed high / unsigned low bytes) per stage
+  int32_t quad;         // s16s16s32: two byte planes of both operands, four MMAs per K slice
+  int32_t acc_bufs;     // accumulator buffers in TMEM: 2 (epilogue overlaps the next tile), or 1
   int32_t kboxes;       // K boxes per stage (1 or 2)
   int32_t mma_per_box;  // tcgen05.mma per K box
   int32_t stage_bytes_a, stage_bytes_b;
@@ -711,6 +713,42 @@ __device__ __forceinline__ void epilogue_rows_dual(const TcParams& P, uint32_t t
   }
 }
 
+// Epilogue of the four-product mode (s16s16s32, 16x16 tiles): three accumulators of `bn` columns
+// (high x high, the two cross products, low x low); value = (hh << 16) + (cross << 8) + ll
+// (+ old), all modulo 2^32 like the reference's int32 arithmetic.
+__device__ __forceinline__ void epilogue_rows_quad(const TcParams& P, uint32_t taddr_hh, int64_t row,
+                                                   int64_t n1_0, int chunks) {
+  const int64_t m1 = row >> 4;
+  const int m0 = int(row & 15);
+  const uint32_t bn = uint32_t(P.bn);
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t r[16], x[16];
+    tmem_ld16(taddr_hh + uint32_t(c * 16), r);
+    tmem_ld16(taddr_hh + bn + uint32_t(c * 16), x);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r[j] = (r[j] << 16) + (x[j] << 8);
+    tmem_ld16(taddr_hh + 2u * bn + uint32_t(c * 16), x);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r[j] += x[j];
+    const int64_t n1 = n1_0 + c;
+    if (m1 < P.M1 && n1 < P.N1) {
+      uint4* d4 = reinterpret_cast<uint4*>(P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4);
+      if (P.accumulate) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 old = d4[v];
+          r[4 * v + 0] += old.x; r[4 * v + 1] += old.y; r[4 * v + 2] += old.z; r[4 * v + 3] += old.w;
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        d4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+    }
+  }
+}
+
 // One stage's TMA loads for one operand. `c` holds the coordinates of box 0 for this k-block.
 template <bool PAIR>
 __device__ __forceinline__ void issue_operand_loads(const CUtensorMap* map, const OperandStage& st,
@@ -727,7 +765,7 @@ __device__ __forceinline__ void issue_operand_loads(const CUtensorMap* map, cons
 // lives in registers of the single issuing thread.
 struct MmaIssue {
   uint32_t lo_a, lo_b, hi_a, hi_b, kadv_a, kadv_b, kbox_a, kbox_b, idesc, idesc2;
-  int kboxes, mma_per_box, dual, triple;
+  int kboxes, mma_per_box, dual, triple, quad;
 };
 __device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
   MmaIssue m;
@@ -736,7 +774,7 @@ __device__ __forceinline__ MmaIssue make_mma_issue(const TcParams& P) {
   m.kadv_a = P.kadv_a; m.kadv_b = P.kadv_b;
   m.kbox_a = P.kbox_units_a; m.kbox_b = P.kbox_units_b;
   m.idesc = P.idesc; m.kboxes = P.kboxes; m.mma_per_box = P.mma_per_box;
-  m.idesc2 = P.idesc2; m.dual = P.dual; m.triple = P.triple;
+  m.idesc2 = P.idesc2; m.dual = P.dual; m.triple = P.triple; m.quad = P.quad;
   return m;
 }
 // Dual-LHS stage (s16u4s32): shared memory holds [high-byte plane | low-byte plane | RHS]; each K
@@ -758,6 +796,39 @@ __device__ __forceinline__ void issue_stage_mmas_dual(const MmaIssue& m, uint32_
     } else {
       tc_mma<true>(d_hi, da_hi, db, m.idesc, acc);
       tc_mma<true>(d_lo, da_lo, db, m.idesc2, acc);
+    }
+    acc = 1u;
+    au += m.kadv_a;
+    bu += m.kadv_b;
+  }
+}
+
+// Four-product stage (s16s16s32): shared memory holds [high | low] byte planes of both operands
+// (x = 256 * hi + lo with hi the signed high byte and lo the unsigned low byte). Each K slice
+// feeds hi*hi into d, hi*lo and lo*hi into d + bn, lo*lo into d + 2 bn; m.idesc carries neither
+// operand's sign bit (bit 7: A signed, bit 10: B signed).
+template <bool PAIR>
+__device__ __forceinline__ void issue_stage_mmas_quad(const MmaIssue& m, uint32_t d, uint32_t bn,
+                                                      uint32_t a_units, uint32_t b_units,
+                                                      bool first_kblock) {
+  uint32_t acc = first_kblock ? 0u : 1u;
+  uint32_t au = a_units, bu = b_units;
+  const uint32_t a_signed = 1u << 7, b_signed = 1u << 10;
+  for (int j = 0; j < m.mma_per_box; ++j) {
+    const uint64_t a_hi = (uint64_t(m.hi_a) << 32) | uint64_t((au & 0x3FFFu) | m.lo_a);
+    const uint64_t a_lo = (uint64_t(m.hi_a) << 32) | uint64_t(((au + m.kbox_a) & 0x3FFFu) | m.lo_a);
+    const uint64_t b_hi = (uint64_t(m.hi_b) << 32) | uint64_t((bu & 0x3FFFu) | m.lo_b);
+    const uint64_t b_lo = (uint64_t(m.hi_b) << 32) | uint64_t(((bu + m.kbox_b) & 0x3FFFu) | m.lo_b);
+    if (PAIR) {
+      tc_mma_pair<true>(d, a_hi, b_hi, m.idesc | a_signed | b_signed, acc);
+      tc_mma_pair<true>(d + bn, a_hi, b_lo, m.idesc | a_signed, acc);
+      tc_mma_pair<true>(d + bn, a_lo, b_hi, m.idesc | b_signed, 1u);
+      tc_mma_pair<true>(d + 2u * bn, a_lo, b_lo, m.idesc, acc);
+    } else {
+      tc_mma<true>(d, a_hi, b_hi, m.idesc | a_signed | b_signed, acc);
+      tc_mma<true>(d + bn, a_hi, b_lo, m.idesc | a_signed, acc);
+      tc_mma<true>(d + bn, a_lo, b_hi, m.idesc | b_signed, 1u);
+      tc_mma<true>(d + 2u * bn, a_lo, b_lo, m.idesc, acc);
     }
     acc = 1u;
     au += m.kadv_a;

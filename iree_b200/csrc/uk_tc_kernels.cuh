@@ -59,6 +59,9 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
   const long long wait_limit = P.wait_cycles;
+  // accumulators of one tile: bn columns, two (dual-LHS mode) or three (four-product mode) of them
+  const int acc_cols = P.bn * (P.quad ? 3 : (P.dual ? 2 : 1));
+  const int nbuf = P.acc_bufs == 1 ? 1 : 2;
   pdl_wait();
 
   if (warp == 0) {
@@ -130,7 +133,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn * (mi.dual ? 2 : 1));
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * acc_cols);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp, wait_limit)) {
             if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
@@ -141,7 +144,9 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           tc_fence_after();
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
           if (elect_one()) {
-            if (IS_INT && mi.dual)
+            if (IS_INT && mi.quad)
+              issue_stage_mmas_quad<false>(mi, d_tmem, uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            else if (IS_INT && mi.dual)
               issue_stage_mmas_dual<false>(mi, d_tmem, d_tmem + uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             else
               issue_stage_mmas<IS_INT, false>(mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
@@ -152,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+        if (++buf == nbuf) { buf = 0; buf_phase ^= 1u; }
       }
     }
   } else {
@@ -174,17 +179,17 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
       }
       tc_fence_after();
       const int64_t row = int64_t(mt) * BM + m_local;
-      if (P.dual) {
-        const uint32_t t_hi = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * 2 * P.bn);
-        epilogue_rows_dual(P, t_hi, t_hi + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
-      } else {
-        const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
+      const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * acc_cols);
+      if (P.quad)
+        epilogue_rows_quad(P, taddr0, row, int64_t(nt) * chunks, chunks);
+      else if (P.dual)
+        epilogue_rows_dual(P, taddr0, taddr0 + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
+      else
         epilogue_rows(P, taddr0, row, int64_t(nt) * chunks, chunks, epi_stage, lane);
-      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&tmem_empty_bar[buf]));
-      if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+      if (++buf == nbuf) { buf = 0; buf_phase ^= 1u; }
     }
   }
 
@@ -559,6 +564,9 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
   const uint32_t tmem_base = tmem_slot;
   volatile int* abortp = &abort_flag;
   const long long wait_limit = P.wait_cycles;
+  // accumulators of one tile: bn columns, two (dual-LHS mode) or three (four-product mode) of them
+  const int acc_cols = P.bn * (P.quad ? 3 : (P.dual ? 2 : 1));
+  const int nbuf = P.acc_bufs == 1 ? 1 : 2;
   pdl_wait();
 
   if (G != 0 && warp >= kWorkerFirstWarp) {
@@ -710,7 +718,7 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + uint32_t(buf * P.bn * (mi.dual ? 2 : 1));
+        const uint32_t d_tmem = tmem_base + uint32_t(buf * acc_cols);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait_warp(smem_u32(&full_bar[stage]), phase, abortp, wait_limit)) {
             if (lane == 0) atomicOr(P.status, kStatusMmaTimeout);
@@ -721,7 +729,9 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
           tc_fence_after();
           const uint32_t sa = stage_base + uint32_t(stage) * stage_bytes;
           if (elect_one()) {
-            if (IS_INT && mi.dual)
+            if (IS_INT && mi.quad)
+              issue_stage_mmas_quad<true>(mi, d_tmem, uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
+            else if (IS_INT && mi.dual)
               issue_stage_mmas_dual<true>(mi, d_tmem, d_tmem + uint32_t(P.bn), sa >> 4, (sa + a_bytes) >> 4, kb == 0);
             else
               issue_stage_mmas<IS_INT, true>(narrow ? mi_narrow : mi, d_tmem, sa >> 4, (sa + a_bytes) >> 4, kb == 0);
@@ -732,7 +742,7 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
           if (++stage == S) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+        if (++buf == nbuf) { buf = 0; buf_phase ^= 1u; }
       }
     }
   } else {
@@ -752,17 +762,17 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
       }
       tc_fence_after();
       const int64_t row = int64_t(mt) * 256 + int64_t(rank) * 128 + q * 32 + lane;
-      if (P.dual) {
-        const uint32_t t_hi = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * 2 * P.bn);
-        epilogue_rows_dual(P, t_hi, t_hi + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
-      } else {
-        const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * P.bn);
+      const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * acc_cols);
+      if (P.quad)
+        epilogue_rows_quad(P, taddr0, row, int64_t(it.col0 >> 4), chunks);
+      else if (P.dual)
+        epilogue_rows_dual(P, taddr0, taddr0 + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
+      else
         epilogue_rows(P, taddr0, row, int64_t(it.col0 >> 4), chunks, epi_stage, lane);
-      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty_bar[buf]), 0));
-      if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+      if (++buf == nbuf) { buf = 0; buf_phase ^= 1u; }
     }
   }
 

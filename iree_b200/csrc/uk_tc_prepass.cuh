@@ -270,6 +270,64 @@ __global__ void __launch_bounds__(256) split_s16_kernel(const char* __restrict__
   }
 }
 
+// s16s16s32 pre-pass: a [tile][K1][16][2] s16 operand becomes two K-major byte planes
+// [tile * 16 + r][K1 * 2] (high bytes, low bytes). A block moves 256 k1 steps of one tile row
+// (16 KB) through shared memory, 68 bytes per k1 like the plain re-tile; a thread then reads the
+// 8 words (8 k1 steps x 2 s16) of one row and stores 16 bytes to each plane. Lanes cover 8 rows
+// x 4 k1 groups, which keeps the shared-memory reads on 32 different banks.
+struct SplitOperand {
+  const char* src;       // first panel
+  int64_t src_stride_b;  // bytes between panels (tile rows)
+  char* hi;              // high-byte plane; the low-byte plane follows at +plane_bytes
+  int64_t plane_bytes;
+  int64_t blocks;        // tile rows x k chunks
+};
+__global__ void __launch_bounds__(256) retile_split_s16_kernel(SplitOperand opa, SplitOperand opb,
+                                                               int64_t pitch_b, int64_t K1,
+                                                               int kchunks) {
+  pdl_launch_dependents();
+  constexpr int KC = 256, PITCH = 68;
+  __shared__ __align__(16) unsigned char sm[KC * PITCH];
+  const bool is_a = int64_t(blockIdx.x) < opa.blocks;
+  const SplitOperand& op = is_a ? opa : opb;
+  const int64_t block = is_a ? int64_t(blockIdx.x) : int64_t(blockIdx.x) - opa.blocks;
+  const int64_t tile = block / kchunks;
+  const int chunk = int(block - tile * kchunks);
+  const int64_t k_base = int64_t(chunk) * KC;
+  const int kn = int(min(int64_t(KC), K1 - k_base));
+  const uint4* sp = reinterpret_cast<const uint4*>(op.src + tile * op.src_stride_b + k_base * 64);
+  const int tid = int(threadIdx.x);
+#pragma unroll 4
+  for (int v = tid; v < kn * 4; v += 256) {
+    const uint4 x = __ldg(sp + v);
+    uint32_t* d = reinterpret_cast<uint32_t*>(sm + (v >> 2) * PITCH + (v & 3) * 16);
+    d[0] = x.x; d[1] = x.y; d[2] = x.z; d[3] = x.w;
+  }
+  // k1 steps past the end of a ragged last chunk read as zero
+  for (int v = kn * 16 + tid; v < ((kn + 7) & ~7) * 16; v += 256)
+    *reinterpret_cast<uint32_t*>(sm + (v >> 4) * PITCH + (v & 15) * 4) = 0u;
+  __syncthreads();
+  const int groups = (kn + 7) >> 3;  // 16-byte vectors per row and plane
+  const int groups4 = (groups + 3) & ~3;
+  // task t: row = (t & 7) | ((t >> 5) & 1) << 3, group = ((t >> 3) & 3) | (t >> 6) << 2
+  for (int t = tid; t < 16 * groups4; t += 256) {
+    const int r = (t & 7) | (((t >> 5) & 1) << 3);
+    const int g = ((t >> 3) & 3) | ((t >> 6) << 2);
+    if (g >= groups) continue;
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      w[j] = *reinterpret_cast<const uint32_t*>(sm + (g * 8 + j) * PITCH + r * 4);
+    const uint4 lo = make_uint4(__byte_perm(w[0], w[1], 0x6420), __byte_perm(w[2], w[3], 0x6420),
+                                __byte_perm(w[4], w[5], 0x6420), __byte_perm(w[6], w[7], 0x6420));
+    const uint4 hi = make_uint4(__byte_perm(w[0], w[1], 0x7531), __byte_perm(w[2], w[3], 0x7531),
+                                __byte_perm(w[4], w[5], 0x7531), __byte_perm(w[6], w[7], 0x7531));
+    char* dp = op.hi + (tile * 16 + r) * pitch_b + (k_base + g * 8) * 2;
+    *reinterpret_cast<uint4*>(dp) = hi;
+    *reinterpret_cast<uint4*>(dp + op.plane_bytes) = lo;
+  }
+}
+
 // RHS [N1][K1][32][8 x u4] (tile = 128 bytes, low nibble = even k0) -> row-major u8
 // [N1*32][K1*8]. A block widens 64 k1 steps of one tile row through shared memory: contiguous
 // 16-byte loads, 16-byte stores of 512-byte row segments.

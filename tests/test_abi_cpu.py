@@ -145,6 +145,13 @@ def test_mmt4d_info_and_workspace_size():
     assert uk.mmt4d_path(big) == abi.PATH_TCGEN05_RETILE
     assert uk.mmt4d_path(big, with_workspace=False) == abi.PATH_GEMV
     assert uk.mmt4d_workspace_size(big) == 2 * 64 * 128 + 4 * 32 * 128
+    # s16s16s32 16x16x2: a high and a low byte plane of both operands, 128-byte row pitch
+    s16 = _mmt4d(abi.MMT4D_S16S16S32, M=8, N=4, K=100, M0=16, N0=16, K0=2)
+    assert uk.mmt4d_info(16, 16, 2, abi.MMT4D_S16S16S32) == 1
+    assert uk.mmt4d_info(8, 8, 2, abi.MMT4D_S16S16S32) == 0
+    assert uk.mmt4d_path(s16) == abi.PATH_TCGEN05_RETILE
+    assert uk.mmt4d_path(s16, with_workspace=False) == abi.PATH_GENERIC
+    assert uk.mmt4d_workspace_size(s16) == 2 * (8 + 4) * 16 * 256
     p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
     # row-major copies of both operands, 128-byte row pitch; behind them the job cursor and
     # one ready counter per LHS tile row of the streamed pre-pass

@@ -170,6 +170,27 @@ def test_mmt4d_s16u4_tensor_core_path(shape, accumulate):
     assert np.array_equal(got2, got)
 
 
+@pytest.mark.parametrize("shape", [(1, 1, 1), (8, 16, 64), (9, 17, 65), (3, 5, 7), (24, 40, 31),
+                                   (1, 1, 1000), (16, 3, 260),
+                                   # enough 256 x 128 tiles for the two-CTA form, ragged edges
+                                   (160, 64, 9), (170, 67, 5)], ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_mmt4d_s16s16_tensor_core_path(shape, accumulate):
+    """s16s16s32 16x16x2 (arch/x86_64/mmt4d_x86_64_avx512_base.c:312 has the ISA function): byte
+    planes of both operands, four 8-bit tensor-core products per term, recombined modulo 2^32.
+    Full-range s16 values, so the sums wrap like the reference's int32 arithmetic; bit-exact.
+    Without scratch the generic kernel serves the same problem and agrees."""
+    M, N, K = shape
+    case = cases.Mmt4dCase(abi.MMT4D_S16S16S32, 16, 16, 2, M, N, K, accumulate, seed=M + K,
+                           mode="normal", loose=False)
+    got, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    assert np.array_equal(got, G.oracle_mmt4d(case)), shape
+    got2, path2 = G.run_mmt4d_case(case, use_workspace=False)
+    assert path2 == abi.PATH_GENERIC
+    assert np.array_equal(got2, got)
+
+
 NARROW_TYPES = [(abi.MMT4D_S8S8S32, 2), (abi.MMT4D_F16F16F32, 1), (abi.MMT4D_BF16BF16F32, 2)]
 
 
