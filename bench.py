@@ -305,6 +305,10 @@ def per_config_rooflines(supp, peaks):
            "mmt4d_s16u4s32_prefill_8192x14336x4096",
            "split_s16 + unpack_u4 + mmt4d_tc2_kernel<int> (two i8 products per term)", 2 * burst,
            scale=2.0)
+    tensor("mmt4d_bf16_headline_plain_call_pooled_scratch", "mmt4d_bf16_headline_plain_call_pooled_scratch",
+           "iree_uk_b200_mmt4d_pooled: retile_kernel<4> + mmt4d_tc2_kernel<float>", burst, spec=2250.0)
+    tensor("mmt4d_bf16_headline_plain_call_scratch_free", "mmt4d_bf16_headline_plain_call_scratch_free",
+           "iree_uk_b200_mmt4d: mmt4d_tc_sw_kernel", burst, spec=2250.0)
     tensor("mmt4d_s16s16s32_4096x4096x4096_as_8bit_tensor_work", "mmt4d_s16s16s32_4096x4096x4096",
            "retile_split_s16 + mmt4d_tc2_kernel<int> (four i8 products per term)", 2 * burst,
            scale=4.0)

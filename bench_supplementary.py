@@ -81,7 +81,7 @@ def _rand_bytes(n):
 
 
 def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None, copies=1,
-                graph_calls=0, use_ws=True):
+                graph_calls=0, use_ws=True, pooled=False):
     """``copies`` > 1: the call is timed as a sweep over that many independent buffer sets
     (see _time_rotating); otherwise one call per event pair, with ``flush`` read in between."""
     lb, rb, _ = abi.MMT4D_BITS[flags & 0xFF]
@@ -100,7 +100,10 @@ def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None
         ws = torch.empty(nws, dtype=torch.uint8, device="cuda") if nws else None
         path = uk.mmt4d_path(p, ws is not None)
         keep.append((lhs, rhs, out, ws, p))
-        fns.append(lambda p=p, ws=ws: uk.mmt4d(p, workspace=ws))
+        if pooled:  # the plain signature, scratch from the library's stream-ordered pool
+            fns.append(lambda p=p: uk.mmt4d_pooled(p))
+        else:
+            fns.append(lambda p=p, ws=ws: uk.mmt4d(p, workspace=ws))
     if copies > 1:
         med, best = _time_rotating(fns)
     else:
@@ -257,6 +260,15 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
                            448, 512, 1, 32, 8, peaks, None)
         r["frac_of_2x_bf16_burst_counting_both_byte_products"] = 2 * r["tops"] / (2 * bf16_peak)
         res[k] = r
+    # the headline problem through the plain three-pointer signature: scratch-free kernel, and
+    # the pre-pass kernels on scratch from the library's memory pool
+    for name, kw in [("mmt4d_bf16_headline_plain_call_scratch_free", {"use_ws": False}),
+                     ("mmt4d_bf16_headline_plain_call_pooled_scratch", {"use_ws": False, "pooled": True})]:
+        if want(name):
+            k, r = _mmt4d_case(name, abi.MMT4D_BF16BF16F32, 512, 1792, 4096, 16, 16, 2, peaks,
+                               None, torch.bfloat16, **kw)
+            r["frac_of_bf16_burst"] = r["tops"] / bf16_peak
+            res[k] = r
     # s16s16s32 16x16x2: four 8-bit tensor-core products per s16 x s16 term
     if want("mmt4d_s16s16s32_4096x4096x4096"):
         k, r = _mmt4d_case("mmt4d_s16s16s32_4096x4096x4096", abi.MMT4D_S16S16S32, 256, 256, 2048,

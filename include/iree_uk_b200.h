@@ -398,6 +398,23 @@ IREE_UK_B200_EXPORT int iree_uk_b200_peer_close(void* device_ptr);
 IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_static_scratch(
     const iree_uk_mmt4d_params_t* params, void* cu_stream);
 
+/* mmt4d with scratch taken from a stream-ordered memory pool that the library owns (one per
+ * device, created on first use; no reference counterpart). For a caller of the reference's
+ * plain three-pointer signature that may allocate but has no buffer planned for scratch: the
+ * call takes iree_uk_b200_mmt4d_workspace_size bytes from the pool with
+ * cudaMallocFromPoolAsync on `cu_stream`, runs exactly what iree_uk_b200_mmt4d_ws would run
+ * on them, and returns them with cudaFreeAsync on the same stream. The pool keeps what it has
+ * been given (release threshold: unlimited), so after the first call of a given size no
+ * device memory is obtained from the driver; iree_uk_b200_scratch_pool_trim hands memory back.
+ * Problems that use no scratch are served exactly as by iree_uk_b200_mmt4d. Nothing in the
+ * library calls this on its own: a caller that cannot allocate uses
+ * iree_uk_b200_mmt4d_static_scratch or iree_uk_b200_mmt4d. */
+IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_pooled(const iree_uk_mmt4d_params_t* params,
+                                                  void* cu_stream);
+/* Releases the current device's scratch pool down to `keep_bytes` of unused memory
+ * (cudaMemPoolTrimTo); memory of calls still in flight is not touched. */
+IREE_UK_B200_EXPORT int iree_uk_b200_scratch_pool_trim(size_t keep_bytes);
+
 /* Flat-argument twin of iree_uk_mmt4d (ukernel/mmt4d.h:14-22, mmt4d.c:151-177) with the
  * workspace and the stream appended; `cpu_data` is kept in the list so a call site can be
  * substituted one for one. */

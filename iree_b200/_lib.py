@@ -28,6 +28,8 @@ SIGNATURES = {
     "iree_uk_b200_mmt4d_workspace_size": (_sz, [_P]),
     "iree_uk_b200_mmt4d_ws": (C.c_int, [_P, _P, _sz, _P]),
     "iree_uk_b200_mmt4d_static_scratch": (C.c_int, [_P, _P]),
+    "iree_uk_b200_mmt4d_pooled": (C.c_int, [_P, _P]),
+    "iree_uk_b200_scratch_pool_trim": (C.c_int, [C.c_size_t]),
     "iree_uk_b200_mmt4d_host_arena_size": (_sz, [_P]),
     "iree_uk_b200_mmt4d_host": (C.c_int, [_P, _P, _sz, _P]),
     "iree_uk_b200_mmt4d_host_resident_lhs": (C.c_int, [_P, _P, _I, _P, _sz, _P]),

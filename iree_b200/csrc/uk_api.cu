@@ -161,6 +161,67 @@ int iree_uk_b200_mmt4d_ws(const iree_uk_mmt4d_params_t* params, void* workspace,
   return run_mmt4d(params, workspace, workspace_bytes, true, cu_stream);
 }
 
+namespace {
+// The current device's scratch pool, created on first use; nullptr on failure.
+cudaMemPool_t scratch_pool() {
+  constexpr int kMaxDevices = 64;
+  static cudaMemPool_t pools[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!pools[dev]) {
+    cudaMemPoolProps props = {};
+    props.allocType = cudaMemAllocationTypePinned;
+    props.handleTypes = cudaMemHandleTypeNone;
+    props.location.type = cudaMemLocationTypeDevice;
+    props.location.id = dev;
+    cudaMemPool_t pool = nullptr;
+    if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    uint64_t keep = ~uint64_t(0);
+    if (cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) {
+      cudaGetLastError();
+      cudaMemPoolDestroy(pool);
+      return nullptr;
+    }
+    pools[dev] = pool;
+  }
+  return pools[dev];
+}
+}  // namespace
+
+int iree_uk_b200_mmt4d_pooled(const iree_uk_mmt4d_params_t* params, void* cu_stream) {
+  Mmt4dPath path;
+  const int rc = select_mmt4d(params, true, &path);
+  if (rc) return rc;
+  if (path != Mmt4dPath::TcRetile) return run_mmt4d(params, nullptr, 0, false, cu_stream);
+  const size_t bytes = mmt4d_tc_workspace_size(params);
+  cudaMemPool_t pool = scratch_pool();
+  if (!pool) return IREE_UK_B200_CUDA_ERROR;
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  void* ws = nullptr;
+  if (cudaMallocFromPoolAsync(&ws, bytes, pool, stream) != cudaSuccess) {
+    cudaGetLastError();
+    return IREE_UK_B200_CUDA_ERROR;
+  }
+  const int run = run_mmt4d(params, ws, bytes, true, cu_stream);
+  // Stream-ordered: the memory returns to the pool after the kernels enqueued above.
+  if (cudaFreeAsync(ws, stream) != cudaSuccess) {
+    cudaGetLastError();
+    return run ? run : IREE_UK_B200_CUDA_ERROR;
+  }
+  return run;
+}
+
+int iree_uk_b200_scratch_pool_trim(size_t keep_bytes) {
+  cudaMemPool_t pool = scratch_pool();
+  if (!pool) return IREE_UK_B200_CUDA_ERROR;
+  return cuda_status(cudaMemPoolTrimTo(pool, keep_bytes));
+}
+
 int iree_uk_b200_mmt4d_flat(const void* lhs_buffer, iree_uk_index_t lhs_offset,
                             iree_uk_index_t lhs_stride0, const void* rhs_buffer,
                             iree_uk_index_t rhs_offset, iree_uk_index_t rhs_stride0,

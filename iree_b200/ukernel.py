@@ -204,6 +204,19 @@ def mmt4d_static_scratch(params, stream=None):
            "mmt4d_static_scratch")
 
 
+def mmt4d_pooled(params, stream=None):
+    """mmt4d with scratch from the library's stream-ordered memory pool (taken and returned on
+    ``stream``): the kernels of ``mmt4d(..., workspace=...)`` behind the reference's plain
+    signature, for callers that may allocate."""
+    _check(lib.iree_uk_b200_mmt4d_pooled(C.addressof(params), _stream_handle(stream)),
+           "mmt4d_pooled")
+
+
+def scratch_pool_trim(keep_bytes=0):
+    """Hands the unused memory of the current device's scratch pool back, down to ``keep_bytes``."""
+    _check(lib.iree_uk_b200_scratch_pool_trim(keep_bytes), "scratch_pool_trim")
+
+
 def mmt4d_path(params, with_workspace=True):
     """Which kernel serves the call (``abi.PATH_*``); raises on rejected parameters."""
     r = lib.iree_uk_b200_mmt4d_path(C.addressof(params), 1 if with_workspace else 0)

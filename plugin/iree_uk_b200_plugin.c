@@ -26,8 +26,10 @@
  * which stream, and may give it scratch memory. Both arrive as plugin parameters at load
  * ("stream", "workspace", "workspace_bytes": decimal or 0x-prefixed integers) or later through
  * iree_uk_b200_plugin_configure. Without a workspace the mmt4d thunk uses the library's
- * static-scratch entry point, and falls back to the scratch-free kernels when a problem does
- * not fit that array: an import call has no allocator to turn to.
+ * static-scratch entry point; when a problem does not fit that array it falls back to the
+ * scratch-free kernels (an import call has no allocator to turn to) unless the runtime that
+ * loaded the plugin allowed stream-ordered allocation with the parameter "scratch_pool" = 1,
+ * in which case the scratch comes from the library's own memory pool on the call's stream.
  *
  * A thunk returns 0 on success and the library's status code otherwise.
  */
@@ -53,6 +55,7 @@ typedef struct plugin_state_t {
   void* stream;            /* CUstream every call is enqueued on */
   void* workspace;         /* device scratch for mmt4d, or NULL */
   size_t workspace_bytes;
+  int scratch_pool;        /* nonzero: problems beyond the static scratch may use the library's pool */
   int last_status;         /* library status of the last failing call, 0 when none failed */
 } plugin_state_t;
 
@@ -67,7 +70,8 @@ static int mmt4d_thunk(void* params_ptr, void* context, void* reserved) {
     rc = iree_uk_b200_mmt4d_ws(p, st->workspace, st->workspace_bytes, st->stream);
   } else {
     rc = iree_uk_b200_mmt4d_static_scratch(p, st->stream);
-    if (rc == IREE_UK_B200_WORKSPACE_TOO_SMALL) rc = iree_uk_b200_mmt4d(p, st->stream);
+    if (rc == IREE_UK_B200_WORKSPACE_TOO_SMALL)
+      rc = st->scratch_pool ? iree_uk_b200_mmt4d_pooled(p, st->stream) : iree_uk_b200_mmt4d(p, st->stream);
   }
   if (rc) st->last_status = rc;
   return rc;
@@ -136,12 +140,14 @@ static iree_hal_executable_plugin_status_t plugin_load(
   st->stream = NULL;
   st->workspace = NULL;
   st->workspace_bytes = 0;
+  st->scratch_pool = 0;
   st->last_status = 0;
   for (size_t i = 0; i < param_count; ++i) {
     uint64_t v = 0;
     const int known = view_equals(params[i].key, "stream") ? 1
                       : view_equals(params[i].key, "workspace") ? 2
-                      : view_equals(params[i].key, "workspace_bytes") ? 3 : 0;
+                      : view_equals(params[i].key, "workspace_bytes") ? 3
+                      : view_equals(params[i].key, "scratch_pool") ? 4 : 0;
     if (!known) continue; /* parameters meant for other plugins */
     if (!parse_u64(params[i].value, &v)) {
       iree_hal_executable_plugin_allocator_free(environment->host_allocator, st);
@@ -151,6 +157,7 @@ static iree_hal_executable_plugin_status_t plugin_load(
     if (known == 1) st->stream = (void*)(uintptr_t)v;
     if (known == 2) st->workspace = (void*)(uintptr_t)v;
     if (known == 3) st->workspace_bytes = (size_t)v;
+    if (known == 4) st->scratch_pool = v != 0;
   }
   *out_self = st;
   return iree_hal_executable_plugin_ok_status();

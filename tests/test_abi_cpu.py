@@ -44,6 +44,7 @@ def test_workspace_entry_point_reports_bad_arguments_without_launching():
     too small for the kernel that would use it is refused instead of being ignored."""
     assert lib.iree_uk_b200_mmt4d_ws(None, 0x40000, 1 << 20, None) == abi.INVALID_ARGUMENT
     assert lib.iree_uk_b200_mmt4d_ws(None, None, 0, None) == abi.INVALID_ARGUMENT
+    assert lib.iree_uk_b200_mmt4d_pooled(None, None) == abi.INVALID_ARGUMENT
     p = _mmt4d()
     need = uk.mmt4d_workspace_size(p)
     assert need > 256

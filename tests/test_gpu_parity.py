@@ -639,3 +639,33 @@ def test_undersized_workspace_is_refused_not_served_by_a_slower_kernel():
     assert e.value.status == abi.WORKSPACE_TOO_SMALL
     torch.cuda.synchronize()
     assert np.array_equal(out.cpu().numpy(), case.out_init)
+
+
+def test_mmt4d_pooled_scratch_matches_the_workspace_call():
+    """iree_uk_b200_mmt4d_pooled: the same kernels as the workspace call on memory of the
+    library's stream-ordered pool; calls back to back, after a trim, and on a second stream."""
+    import torch
+    from iree_b200 import ukernel as uk
+    case = cases.Mmt4dCase(abi.MMT4D_BF16BF16F32, 16, 16, 2, 24, 40, 300, 1, seed=9, mode="exact",
+                           loose=False)
+    want, path = G.run_mmt4d_case(case)
+    assert path == abi.PATH_TCGEN05_RETILE
+    side = torch.cuda.Stream()
+    for round_ in range(4):
+        lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
+        p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+        if round_ == 3:
+            side.wait_stream(torch.cuda.current_stream())
+            uk.mmt4d_pooled(p, stream=side)
+        else:
+            uk.mmt4d_pooled(p)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want)
+        if round_ == 1:
+            uk.scratch_pool_trim(0)
+    # a problem without scratch goes the usual way
+    small = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 9, 6, 3, 5, 7, 13, 0, seed=2, loose=False)
+    lhs, rhs, out = G.to_device(small.lhs), G.to_device(small.rhs), G.to_device(small.out_init)
+    uk.mmt4d_pooled(small.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr()))
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), G.oracle_mmt4d(small))

@@ -117,3 +117,30 @@ def test_imports_compute_what_the_reference_ukernels_compute(with_workspace):
     assert ld.last_status() == 0
     assert uk.device_status() == (0, 0)
     ld.unload()
+
+
+@pytest.mark.gpu
+def test_mmt4d_beyond_the_static_scratch_uses_the_pool_when_allowed():
+    """A problem whose scratch need exceeds the 32 MiB array: with "scratch_pool" = 1 the import
+    runs the pre-pass kernels on memory of the library's stream-ordered pool; without it the
+    scratch-free kernel. Both give the reference's result."""
+    import torch
+    from oracle import cases
+    from iree_b200 import ukernel as uk
+    import gpu_util as G
+    case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, 40, 72, 10000, 1, seed=5, mode="exact",
+                           loose=False)
+    want = G.oracle_mmt4d(case)
+    for allow in ("0", "1"):
+        ld = P.Loader(params=[("scratch_pool", allow)])
+        _, _, fns, ctxs = ld.resolve(["iree_uk_mmt4d"])
+        assert ld.configure(torch.cuda.current_stream().cuda_stream, None, 0) == 0
+        lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
+        p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+        assert uk.mmt4d_workspace_size(p) > uk.STATIC_SCRATCH_BYTES
+        assert P.IMPORT_FN(fns[0])(C.addressof(p), ctxs[0], None) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want)
+        assert ld.last_status() == 0
+        ld.unload()
+    assert uk.device_status() == (0, 0)
