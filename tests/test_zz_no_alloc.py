@@ -82,6 +82,18 @@ def test_static_scratch_runs_s16u4_with_many_rows_on_the_tensor_cores():
     assert bool((out == 7).all())
 
 
+def test_static_scratch_runs_s16s16_on_the_tensor_cores():
+    """s16s16s32 16x16x2 uses scratch (byte planes of both operands) with iree_uk_b200_mmt4d_ws,
+    so it does here too: same bytes as that call and as the reference, twice in a row."""
+    case = cases.Mmt4dCase(abi.MMT4D_S16S16S32, 16, 16, 2, 24, 40, 130, 1, seed=26, mode="normal",
+                           loose=False)
+    for _ in range(2):
+        got, want = _run_both(case)
+        assert np.array_equal(got, want)
+        assert np.array_equal(got, G.oracle_mmt4d(case))
+    G.check_device_status()
+
+
 def test_static_scratch_refuses_oversized_problem():
     M, N, K = 256, 256, 4096  # needs 64 MiB of re-tiled operands
     lhs = torch.zeros(M * K * 16, dtype=torch.float16, device="cuda")
