@@ -477,7 +477,8 @@ iree_uk_b200_mmt4d_host_arena_size(const iree_uk_mmt4d_params_t* params);
  * iree_uk_b200_mmt4d_host_arena_size bytes, in use until the work has completed). The call
  * returns once everything is enqueued; out_buffer is complete when work enqueued on `cu_stream`
  * after this call runs (or after synchronising it). Host buffers should be page-locked, or the
- * copies will not overlap. Uses three internal streams per device, created on first use. */
+ * copies will not overlap. Uses three internal streams per device, created on first use; calls
+ * for one device from several host threads take turns enqueueing and run one after another. */
 IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_host(const iree_uk_mmt4d_params_t* params,
                                                 void* device_arena, size_t arena_bytes,
                                                 void* cu_stream);

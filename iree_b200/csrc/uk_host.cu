@@ -27,6 +27,7 @@ constexpr int kMaxJobs = kMaxChunks + kLhsBlocks;
 
 struct HostPipe {
   bool ready = false;
+  std::mutex enqueue;  // one call at a time builds its chain of copies, kernels and events
   cudaStream_t h2d = nullptr, compute = nullptr, d2h = nullptr;
   cudaEvent_t start = nullptr, lhs_done = nullptr, done = nullptr;
   cudaEvent_t in_done[kMaxChunks] = {}, lhs_block_done[kLhsBlocks] = {}, out_ready[kMaxJobs] = {};
@@ -190,6 +191,9 @@ int mmt4d_host_impl(const iree_uk_mmt4d_params_t* params, const void* device_lhs
   if (reinterpret_cast<uintptr_t>(device_arena) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
   HostPipe* pipe = host_pipe();
   if (!pipe) return IREE_UK_B200_CUDA_ERROR;
+  // The three streams and their events belong to the device, so calls from several host
+  // threads take turns enqueueing (the work itself is ordered by the streams).
+  std::lock_guard<std::mutex> enqueue_lock(pipe->enqueue);
   cudaStream_t user = static_cast<cudaStream_t>(cu_stream);
 
   Mmt4dTypes t;
