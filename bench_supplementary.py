@@ -388,8 +388,8 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
 
 def main():
     """``python bench_supplementary.py [--only SUBSTR] [--mmt4d bf16,M1,N1,K1 [--no-ws]]
-    [--matmul M,N,K] [--iters N] [--warmup N]``: prints one JSON object. Small, single-kernel runs of this
-    command are what the profiles under ``profiles/`` were captured from."""
+    [--matmul M,N,K] [--iters N] [--warmup N]``: prints one JSON object. With ``--only`` and one
+    iteration it is a small single-kernel run, suitable for a profiler capture."""
     import argparse
     import json
     import os
