@@ -312,6 +312,11 @@ def per_config_rooflines(supp, peaks):
     tensor("mmt4d_s16s16s32_4096x4096x4096_as_8bit_tensor_work", "mmt4d_s16s16s32_4096x4096x4096",
            "retile_split_s16 + mmt4d_tc2_kernel<int> (four i8 products per term)", 2 * burst,
            scale=4.0)
+    tensor("mmt4d_s16s8s32_4096x4096x4096_as_8bit_tensor_work", "mmt4d_s16s8s32_4096x4096x4096",
+           "retile_split_s16 + retile_kernel<2> + mmt4d_tc2_kernel<int> (two i8 products per term)",
+           2 * burst, scale=2.0)
+    tensor("mmt4d_s8s4s32_4096x4096x4096", "mmt4d_s8s4s32_4096x4096x4096",
+           "widen_s4_kernel + retile_kernel<2> + mmt4d_tc2_kernel<int>", 2 * burst)
     memory("mmt4d_s16u4s32_gemv_1x14336x4096_per_call", "mmt4d_s16u4s32_gemv_1x14336x4096",
            "mmt4d_gemv_s16u4_kernel")
     memory("mmt4d_s16u4s32_gemv_1x14336x4096_graph_replay", "mmt4d_s16u4s32_gemv_1x14336x4096",

@@ -72,6 +72,9 @@ int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path)
     if (have_ws && mmt4d_tc_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
     // s16s16s32 16x16x2: byte planes on the tensor cores (scratch only; generic kernel without)
     if (have_ws && mmt4d_tc_s16s16_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
+    if (have_ws && mmt4d_tc_s16s8_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
+    // s8s4s32 16x16xK0: nibbles widened by the pre-pass, then the s8s8s32 kernels (scratch only)
+    if (have_ws && mmt4d_tc_s8s4_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
     // Without scratch, a 16-bit K0 = 1 operand ([tile][K1][16]) can still be read by TMA as an
     // MN-major tensor-core operand; K0 = 2 operands cannot and fall to the generic kernel.
     if (!have_ws && mmt4d_tc_direct_eligible(p)) { *path = Mmt4dPath::Tc; return 0; }
@@ -254,7 +257,11 @@ uint32_t iree_uk_b200_mmt4d_info(int32_t M0, int32_t N0, int32_t K0, uint32_t fl
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 && M0 == 1 && N0 == 32 && K0 == 8)
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
-  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32 && M0 == 16 && N0 == 16 && K0 == 2)
+  if ((type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32 || type == IREE_UK_FLAG_MMT4D_TYPE_S16S8S32) &&
+      M0 == 16 && N0 == 16 && K0 == 2)
+    return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S8S4S32 && M0 == 16 && N0 == 16 &&
+      (K0 == 2 || K0 == 4 || K0 == 8 || K0 == 16))
     return IREE_UK_FLAG_MMT4D_INFO_HAVE_ARCHITECTURE_SPECIFIC_TILE_FUNCTION;
   // narrowed M0: the weight-streaming kernel
   const bool narrow_type = (type == IREE_UK_FLAG_MMT4D_TYPE_S8S8S32 && K0 == 2) ||

@@ -64,6 +64,12 @@ bool mmt4d_tc_eligible(const iree_uk_mmt4d_params_t* p);
 bool mmt4d_tc_s16u4_eligible(const iree_uk_mmt4d_params_t* p);
 // s16s16s32 16x16x2 (two byte planes of both operands, four 8-bit products per term).
 bool mmt4d_tc_s16s16_eligible(const iree_uk_mmt4d_params_t* p);
+// s16s8s32 16x16x2 (two byte planes of the LHS against the s8 RHS, two products per term).
+bool mmt4d_tc_s16s8_eligible(const iree_uk_mmt4d_params_t* p);
+// s8s4s32 16x16xK0 (K0 = 2, 4, 8, 16): nibbles widened to bytes by the pre-pass, then s8s8s32.
+bool mmt4d_tc_s8s4_eligible(const iree_uk_mmt4d_params_t* p);
+int launch_mmt4d_tc_s8s4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
+                         cudaStream_t stream);
 size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p);
 // `peer_out_buffers`: optional device pointers (usually on other GPUs) that stand for
 // p->out_buffer in further copies of the output; every tile is stored to all of them too.

@@ -265,6 +265,33 @@ bool mmt4d_tc_s16s16_eligible(const iree_uk_mmt4d_params_t* p) {
   return true;
 }
 
+bool mmt4d_tc_s16s8_eligible(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) != IREE_UK_FLAG_MMT4D_TYPE_S16S8S32) return false;
+  if (p->M0 != 16 || p->N0 != 16 || p->K0 != 2 || p->K < 1 || p->M < 1 || p->N < 1) return false;
+  const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset * 2);
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset);
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * 4);
+  if ((lhs | rhs | out) & 15) return false;
+  if ((p->lhs_stride0 * 2) % 16 || p->rhs_stride0 % 16 || (p->out_stride0 * 4) % 16) return false;
+  if ((p->M + 7) / 8 * ((p->N + 3) / 4) > 0x3FFFFFFF) return false;
+  return true;
+}
+
+bool mmt4d_tc_s8s4_eligible(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) != IREE_UK_FLAG_MMT4D_TYPE_S8S4S32) return false;
+  if (p->M0 != 16 || p->N0 != 16 || p->K < 1 || p->M < 1 || p->N < 1) return false;
+  if (p->K0 != 2 && p->K0 != 4 && p->K0 != 8 && p->K0 != 16) return false;
+  if (p->rhs_offset & 1) return false;  // the RHS starts on a byte
+  const uintptr_t lhs = reinterpret_cast<uintptr_t>(p->lhs_buffer) + uintptr_t(p->lhs_offset);
+  const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset / 2);
+  const uintptr_t out = reinterpret_cast<uintptr_t>(p->out_buffer) + uintptr_t(p->out_offset * 4);
+  if ((lhs | rhs | out) & 15) return false;
+  if (p->lhs_stride0 % 16 || (p->rhs_stride0 & 1) || (p->rhs_stride0 / 2) % 16 || (p->out_stride0 * 4) % 16)
+    return false;
+  if ((p->M + 7) / 8 * ((p->N + 3) / 4) > 0x3FFFFFFF) return false;
+  return true;
+}
+
 namespace {
 
 struct S16U4Layout {
@@ -450,13 +477,17 @@ S16S16Layout s16s16_layout(const iree_uk_mmt4d_params_t* p) {
   return l;
 }
 
+// Also serves s16s8s32 16x16x2 (`rhs_s8`): the RHS is then a single plane of signed bytes, every
+// term takes two products (high x b, low x b) into two accumulators, double buffered.
 int launch_mmt4d_tc_s16s16(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes,
                            cudaStream_t stream) {
-  if (!mmt4d_tc_s16s16_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
+  const bool rhs_s8 = (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16S8S32;
+  if (!(rhs_s8 ? mmt4d_tc_s16s8_eligible(p) : mmt4d_tc_s16s16_eligible(p))) return IREE_UK_B200_UNSUPPORTED;
   uint32_t* status = device_status_word();
   if (!status) return IREE_UK_B200_CUDA_ERROR;
   const S16S16Layout l = s16s16_layout(p);
-  if (!ws || ws_bytes < size_t(2 * (l.plane_a + l.plane_b))) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  const int b_planes = rhs_s8 ? 1 : 2;
+  if (!ws || ws_bytes < size_t(2 * l.plane_a + b_planes * l.plane_b)) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
   if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
   const DeviceInfo* di = device_info();
   if (!di) return IREE_UK_B200_CUDA_ERROR;
@@ -471,11 +502,17 @@ int launch_mmt4d_tc_s16s16(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_
     const SplitOperand a = {static_cast<const char*>(p->lhs_buffer) + p->lhs_offset * 2,
                             p->lhs_stride0 * 2, a_hi, l.plane_a, p->M * kchunks};
     const SplitOperand b = {static_cast<const char*>(p->rhs_buffer) + p->rhs_offset * 2,
-                            p->rhs_stride0 * 2, b_hi, l.plane_b, p->N * kchunks};
+                            p->rhs_stride0 * 2, b_hi, l.plane_b, rhs_s8 ? 0 : p->N * kchunks};
     if (a.blocks + b.blocks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
     retile_split_s16_kernel<<<int(a.blocks + b.blocks), 256, 0, stream>>>(a, b, l.pitch, p->K,
                                                                         int(kchunks));
     if (cudaGetLastError() != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
+    if (rhs_s8) {  // the s8 RHS [N1][K1][16][2]: a plain re-tile with 2-byte granules
+      const int rc = launch_retile(nullptr, 0, nullptr, 0,
+                                   static_cast<const char*>(p->rhs_buffer) + p->rhs_offset,
+                                   p->rhs_stride0, b_hi, p->N, l.pitch, p->K, 2, stream);
+      if (rc) return rc;
+    }
   }
 
   TcParams P;
@@ -490,7 +527,7 @@ int launch_mmt4d_tc_s16s16(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_
   const int tile_m = pair ? 2 * BM : BM;
   const int b_rows = pair ? bn / 2 : bn;
   const uint64_t da[3] = {uint64_t(kbytes), uint64_t(rows), 2};
-  const uint64_t db[3] = {uint64_t(kbytes), uint64_t(ncols), 2};
+  const uint64_t db[3] = {uint64_t(kbytes), uint64_t(ncols), uint64_t(b_planes)};
   const uint64_t sa[2] = {uint64_t(l.pitch), uint64_t(l.plane_a)};
   const uint64_t sb[2] = {uint64_t(l.pitch), uint64_t(l.plane_b)};
   const uint32_t ba[3] = {128, BM, 1};
@@ -500,20 +537,29 @@ int launch_mmt4d_tc_s16s16(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_
     return IREE_UK_B200_CUDA_ERROR;
   // box 0: high plane, box 1: low plane
   P.sa = {2, BM * 128, {128, 0, 0}, {0, tile_m, 0}, {0, 0, 1}, {0, pair ? BM : 0, 0}};
-  P.sb = {2, b_rows * 128, {128, 0, 0}, {0, bn, 0}, {0, 0, 1}, {0, pair ? b_rows : 0, 0}};
+  P.sb = {b_planes, b_rows * 128, {128, 0, 0}, {0, bn, 0}, {0, 0, 1}, {0, pair ? b_rows : 0, 0}};
   P.desc_hi_a = P.desc_hi_b = desc_hi(1024, 2);
   P.desc_lbo_a = P.desc_lbo_b = 1;
   P.kadv_a = P.kadv_b = 2;
   P.kbox_units_a = uint32_t(BM * 128) >> 4;      // from the high to the low plane tile
-  P.kbox_units_b = uint32_t(b_rows * 128) >> 4;
-  // accumulate s32; the operands' sign bits are set per product by the issuing thread
-  P.idesc = (2u << 4) | (uint32_t(bn >> 3) << 17) | (uint32_t(tile_m >> 4) << 24);
-  P.quad = 1;
-  P.acc_bufs = 2 * 3 * bn <= 512 ? 2 : 1;
+  P.kbox_units_b = rhs_s8 ? 0u : uint32_t(b_rows * 128) >> 4;
+  // accumulate s32; in the four-product mode the operands' sign bits are set per product by the
+  // issuing thread, in the two-product mode the RHS is signed and the LHS planes differ
+  const uint32_t common = (2u << 4) | (uint32_t(bn >> 3) << 17) | (uint32_t(tile_m >> 4) << 24);
+  if (rhs_s8) {
+    P.idesc = common | (1u << 7) | (1u << 10);
+    P.idesc2 = common | (1u << 10);
+    P.dual = 2;
+    P.acc_bufs = 2;
+  } else {
+    P.idesc = common;
+    P.quad = 1;
+    P.acc_bufs = 2 * 3 * bn <= 512 ? 2 : 1;
+  }
   P.kboxes = 1;
   P.mma_per_box = 4;
   P.stage_bytes_a = 2 * BM * 128;
-  P.stage_bytes_b = 2 * b_rows * 128;
+  P.stage_bytes_b = b_planes * b_rows * 128;
   P.num_kb = int((kbytes + 127) / 128);
   P.bn = bn;
   P.m_tiles = int((rows + tile_m - 1) / tile_m);
@@ -594,10 +640,19 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
     const S16U4Layout l = s16u4_layout(p);
     return size_t(2 * l.plane_bytes + l.w_bytes);
   }
-  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32 ||
+      (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16S8S32) {
     if (p->M0 != 16 || p->N0 != 16 || p->K0 != 2 || p->K < 1 || p->M < 1 || p->N < 1) return 0;
     const S16S16Layout l = s16s16_layout(p);
-    return size_t(2 * (l.plane_a + l.plane_b));
+    const bool rhs_s8 = (p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16S8S32;
+    return size_t(2 * l.plane_a + (rhs_s8 ? 1 : 2) * l.plane_b);
+  }
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S8S4S32) {
+    // sized like the s8s8s32 problem of the same shape: the RHS is widened to bytes
+    if (p->K0 != 2 && p->K0 != 4 && p->K0 != 8 && p->K0 != 16) return 0;
+    iree_uk_mmt4d_params_t q = *p;
+    q.flags = (p->flags & ~uint32_t(IREE_UK_FLAG_MMT4D_TYPE_MASK)) | IREE_UK_FLAG_MMT4D_TYPE_S8S8S32;
+    return mmt4d_tc_workspace_size(&q);
   }
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti)) return 0;
@@ -665,6 +720,14 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   if ((num_peers || multicast_out || prepared_rhs || rm) && planes) return IREE_UK_B200_UNSUPPORTED;
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32) return launch_mmt4d_tc_s16s16(p, ws, ws_bytes, stream);
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16S8S32) {
+    if (num_peers || multicast_out || prepared_rhs || rm) return IREE_UK_B200_UNSUPPORTED;
+    return launch_mmt4d_tc_s16s16(p, ws, ws_bytes, stream);
+  }
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S8S4S32) {
+    if (num_peers || multicast_out || prepared_rhs || rm) return IREE_UK_B200_UNSUPPORTED;
+    return launch_mmt4d_tc_s8s4(p, ws, ws_bytes, variant, stream);
+  }
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || !(rm ? mmt4d_tc_operands_eligible(p) : mmt4d_tc_eligible(p)))
     return IREE_UK_B200_UNSUPPORTED;
@@ -944,6 +1007,32 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
 }  // namespace uk
 
 namespace uk {
+
+// s8s4s32 with 16x16xK0 tiles: the RHS nibbles are sign-extended to bytes and re-tiled in one
+// pre-pass (widen_s4_kernel), which leaves exactly what a prepared s8s8s32 RHS is; the call
+// then runs as s8s8s32 with that prepared RHS (one 8-bit tensor-core product per term, the LHS
+// re-tile streamed as usual). Workspace: [LHS scratch + sync block][widened RHS].
+int launch_mmt4d_tc_s8s4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, int variant,
+                         cudaStream_t stream) {
+  if (!mmt4d_tc_s8s4_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
+  iree_uk_mmt4d_params_t q = *p;
+  q.flags = (p->flags & ~uint32_t(IREE_UK_FLAG_MMT4D_TYPE_MASK)) | IREE_UK_FLAG_MMT4D_TYPE_S8S8S32;
+  const size_t lhs_part = mmt4d_tc_prepared_workspace_size(&q), rhs_part = mmt4d_tc_prepared_rhs_size(&q);
+  if (!lhs_part || !rhs_part) return IREE_UK_B200_UNSUPPORTED;
+  if (!ws || ws_bytes < lhs_part + rhs_part) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+  char* widened = static_cast<char*>(ws) + lhs_part;
+  const int64_t pitch = round_up(p->K * p->K0, 128);
+  const int rc = launch_widen_s4(static_cast<const char*>(p->rhs_buffer) + p->rhs_offset / 2,
+                                 p->rhs_stride0 / 2, widened, p->N, pitch, p->K, p->K0, stream);
+  if (rc) return rc;
+  // the s8s8s32 call never reads its RHS operand itself: it is described by the prepared copy
+  q.rhs_buffer = widened;
+  q.rhs_offset = 0;
+  q.rhs_stride0 = p->K * 16 * p->K0;
+  return launch_mmt4d_tc(&q, ws, lhs_part, variant, stream, nullptr, 0, nullptr, widened);
+}
+
 namespace {
 
 using SwKernel = void (*)(const TcParams);

@@ -46,7 +46,8 @@ struct TcParams {
   uint32_t kbox_units_a, kbox_units_b;  // 16-byte units between the K boxes of one stage
   uint32_t idesc;
   uint32_t idesc2;      // dual-LHS mode: instruction descriptor of the second (low-byte) MMA
-  int32_t dual;         // s16u4s32: two LHS planes (signed high / unsigned low bytes) per stage
+  int32_t dual;         // two LHS planes (signed high / unsigned low bytes) per stage:
+                        // 1 = s16u4s32 (row-major output, M0 = 1), 2 = s16s8s32 (16x16 output tiles)
   int32_t quad;         // s16s16s32: two byte planes of both operands, four MMAs per K slice
   int32_t acc_bufs;     // accumulator buffers in TMEM: 2 (epilogue overlaps the next tile), or 1
   int32_t kboxes;       // K boxes per stage (1 or 2)
@@ -699,6 +700,36 @@ __device__ __forceinline__ void epilogue_rows_dual(const TcParams& P, uint32_t t
     const int64_t col = col0 + c * 16;
     if (row < P.M1 && col < ncols) {
       uint4* d4 = reinterpret_cast<uint4*>(P.out + (row * P.out_stride0 + col) * 4);
+      if (P.accumulate) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 old = d4[v];
+          r[4 * v + 0] += old.x; r[4 * v + 1] += old.y; r[4 * v + 2] += old.z; r[4 * v + 3] += old.w;
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < 4; ++v)
+        d4[v] = make_uint4(r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+    }
+  }
+}
+
+// Epilogue of the dual-LHS mode with 16x16 output tiles (s16s8s32): two accumulators of `bn`
+// columns (high byte plane, low byte plane); value = (hi << 8) + lo (+ old) modulo 2^32.
+__device__ __forceinline__ void epilogue_rows_dual_tiled(const TcParams& P, uint32_t taddr_hi,
+                                                         int64_t row, int64_t n1_0, int chunks) {
+  const int64_t m1 = row >> 4;
+  const int m0 = int(row & 15);
+  for (int c = 0; c < chunks; ++c) {
+    uint32_t h[16], r[16];
+    tmem_ld16(taddr_hi + uint32_t(c * 16), h);
+    tmem_ld16(taddr_hi + uint32_t(P.bn) + uint32_t(c * 16), r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) r[j] += h[j] << 8;
+    const int64_t n1 = n1_0 + c;
+    if (m1 < P.M1 && n1 < P.N1) {
+      uint4* d4 = reinterpret_cast<uint4*>(P.out + (m1 * P.out_stride0 + n1 * 256 + m0 * 16) * 4);
       if (P.accumulate) {
 #pragma unroll
         for (int v = 0; v < 4; ++v) {

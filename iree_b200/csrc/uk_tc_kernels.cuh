@@ -182,6 +182,8 @@ __global__ void __launch_bounds__(kThreads, 1) mmt4d_tc_kernel(const __grid_cons
       const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * acc_cols);
       if (P.quad)
         epilogue_rows_quad(P, taddr0, row, int64_t(nt) * chunks, chunks);
+      else if (P.dual == 2)
+        epilogue_rows_dual_tiled(P, taddr0, row, int64_t(nt) * chunks, chunks);
       else if (P.dual)
         epilogue_rows_dual(P, taddr0, taddr0 + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
       else
@@ -765,6 +767,8 @@ mmt4d_tc2_kernel(const __grid_constant__ TcParams P) {
       const uint32_t taddr0 = tmem_base + (uint32_t(q * 32) << 16) + uint32_t(buf * acc_cols);
       if (P.quad)
         epilogue_rows_quad(P, taddr0, row, int64_t(it.col0 >> 4), chunks);
+      else if (P.dual == 2)
+        epilogue_rows_dual_tiled(P, taddr0, row, int64_t(it.col0 >> 4), chunks);
       else if (P.dual)
         epilogue_rows_dual(P, taddr0, taddr0 + uint32_t(P.bn), row, int64_t(nt) * P.bn, chunks);
       else

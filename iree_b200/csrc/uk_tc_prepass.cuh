@@ -328,6 +328,70 @@ __global__ void __launch_bounds__(256) retile_split_s16_kernel(SplitOperand opa,
   }
 }
 
+// s8s4s32 pre-pass for the RHS: [N1][K1][16][K0 x s4] (K0 / 2 bytes per row and k1 step, low
+// nibble = even k0) -> K-major s8 rows [N1 * 16 + r][K1 * K0], every nibble sign-extended to a
+// byte: what the s8s8s32 kernels consume as a re-tiled RHS. GS = K0 / 2 source bytes per granule.
+// A block widens 1024 / K0 k1 steps of one tile row (8 KB in, 16 rows x 1 KB out) through
+// shared memory.
+template <int GS>
+__global__ void __launch_bounds__(256) widen_s4_kernel(const char* __restrict__ rhs,
+                                                       int64_t rhs_stride_b, char* __restrict__ dst,
+                                                       int64_t pitch_b, int64_t K1, int kchunks) {
+  pdl_launch_dependents();
+  constexpr int K0 = 2 * GS, KC = 1024 / K0, PITCH = 16 * GS + 4;
+  __shared__ __align__(16) unsigned char sm[KC * PITCH];
+  const int64_t n1 = blockIdx.x / kchunks;
+  const int chunk = int(blockIdx.x - n1 * kchunks);
+  const int64_t k_base = int64_t(chunk) * KC;
+  const int kn = int(min(int64_t(KC), K1 - k_base));
+  const uint4* src = reinterpret_cast<const uint4*>(rhs + n1 * rhs_stride_b + k_base * (16 * GS));
+  const int tid = int(threadIdx.x);
+  for (int v = tid; v < kn * GS; v += 256) {
+    const uint4 x = __ldg(src + v);
+    const int byte = v * 16;
+    const int k = byte / (16 * GS), within = byte - k * (16 * GS);
+    uint32_t* d = reinterpret_cast<uint32_t*>(sm + k * PITCH + within);
+    d[0] = x.x; d[1] = x.y; d[2] = x.z; d[3] = x.w;
+  }
+  __syncthreads();
+  // 16 rows x (kn * K0 / 16) vectors of 16 widened bytes = 8 source bytes each
+  const int vec_per_row = (kn * K0 + 15) / 16;
+  const int vec_per_row8 = (vec_per_row + 7) & ~7;
+  for (int v = tid; v < 16 * vec_per_row8; v += 256) {
+    const int r = (v >> 3) & 15, kv = ((v >> 7) << 3) | (v & 7);
+    if (kv >= vec_per_row) continue;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int sb = kv * 8 + j;       // source byte of this row within the chunk
+      const int k = sb / GS, within = sb - k * GS;
+      const int b = k < kn ? int(int8_t(sm[k * PITCH + r * GS + within])) : 0;
+      const uint32_t lo = uint32_t(int32_t(int8_t(uint8_t(b << 4))) >> 4) & 0xFFu;
+      const uint32_t hi = uint32_t(b >> 4) & 0xFFu;  // arithmetic shift of the signed byte
+      w[j >> 1] |= (lo | (hi << 8)) << (16 * (j & 1));
+    }
+    *reinterpret_cast<uint4*>(dst + (n1 * 16 + r) * pitch_b + k_base * K0 + int64_t(kv) * 16) =
+        make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+int launch_widen_s4(const char* rhs, int64_t rhs_stride_b, char* dst, int64_t tiles,
+                    int64_t pitch_b, int64_t K1, int K0, cudaStream_t stream) {
+  if (tiles <= 0 || K1 <= 0) return IREE_UK_B200_OK;
+  const int KC = 1024 / K0;
+  const int64_t kchunks = (K1 + KC - 1) / KC;
+  if (tiles * kchunks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
+  const int blocks = int(tiles * kchunks);
+  switch (K0) {
+    case 2: widen_s4_kernel<1><<<blocks, 256, 0, stream>>>(rhs, rhs_stride_b, dst, pitch_b, K1, int(kchunks)); break;
+    case 4: widen_s4_kernel<2><<<blocks, 256, 0, stream>>>(rhs, rhs_stride_b, dst, pitch_b, K1, int(kchunks)); break;
+    case 8: widen_s4_kernel<4><<<blocks, 256, 0, stream>>>(rhs, rhs_stride_b, dst, pitch_b, K1, int(kchunks)); break;
+    case 16: widen_s4_kernel<8><<<blocks, 256, 0, stream>>>(rhs, rhs_stride_b, dst, pitch_b, K1, int(kchunks)); break;
+    default: return IREE_UK_B200_UNSUPPORTED;
+  }
+  return cuda_status(cudaGetLastError());
+}
+
 // RHS [N1][K1][32][8 x u4] (tile = 128 bytes, low nibble = even k0) -> row-major u8
 // [N1*32][K1*8]. A block widens 64 k1 steps of one tile row through shared memory: contiguous
 // 16-byte loads, 16-byte stores of 512-byte row segments.

@@ -153,6 +153,17 @@ def test_mmt4d_info_and_workspace_size():
     assert uk.mmt4d_path(s16) == abi.PATH_TCGEN05_RETILE
     assert uk.mmt4d_path(s16, with_workspace=False) == abi.PATH_GENERIC
     assert uk.mmt4d_workspace_size(s16) == 2 * (8 + 4) * 16 * 256
+    # s16s8s32 16x16x2: two LHS planes, one RHS plane; s8s4s32: sized like s8s8s32 (widened RHS)
+    s16s8 = _mmt4d(abi.MMT4D_S16S8S32, M=8, N=4, K=100, M0=16, N0=16, K0=2)
+    assert uk.mmt4d_info(16, 16, 2, abi.MMT4D_S16S8S32) == 1
+    assert uk.mmt4d_path(s16s8) == abi.PATH_TCGEN05_RETILE
+    assert uk.mmt4d_workspace_size(s16s8) == (2 * 8 + 4) * 16 * 256
+    s8s4 = _mmt4d(abi.MMT4D_S8S4S32, M=8, N=4, K=100, M0=16, N0=16, K0=4)
+    assert uk.mmt4d_info(16, 16, 4, abi.MMT4D_S8S4S32) == 1 and uk.mmt4d_info(16, 16, 6, abi.MMT4D_S8S4S32) == 0
+    assert uk.mmt4d_path(s8s4) == abi.PATH_TCGEN05_RETILE
+    assert uk.mmt4d_path(s8s4, with_workspace=False) == abi.PATH_GENERIC
+    assert uk.mmt4d_workspace_size(s8s4) == uk.mmt4d_workspace_size(
+        _mmt4d(abi.MMT4D_S8S8S32, M=8, N=4, K=100, M0=16, N0=16, K0=4))
     p = _mmt4d(abi.MMT4D_BF16BF16F32, M=512, N=1792, K=4096)
     # row-major copies of both operands, 128-byte row pitch; behind them the job cursor and
     # one ready counter per LHS tile row of the streamed pre-pass

@@ -174,15 +174,22 @@ def test_mmt4d_s16u4_tensor_core_path(shape, accumulate):
                                    (1, 1, 1000), (16, 3, 260),
                                    # enough 256 x 128 tiles for the two-CTA form, ragged edges
                                    (160, 64, 9), (170, 67, 5)], ids=lambda s: "%dx%dx%d" % s)
+@pytest.mark.parametrize("t,K0", [(abi.MMT4D_S16S16S32, 2), (abi.MMT4D_S16S8S32, 2),
+                                  (abi.MMT4D_S8S4S32, 2), (abi.MMT4D_S8S4S32, 4),
+                                  (abi.MMT4D_S8S4S32, 8), (abi.MMT4D_S8S4S32, 16)],
+                         ids=["s16s16", "s16s8", "s8s4_k2", "s8s4_k4", "s8s4_k8", "s8s4_k16"])
 @pytest.mark.parametrize("accumulate", [0, 1])
-def test_mmt4d_s16s16_tensor_core_path(shape, accumulate):
-    """s16s16s32 16x16x2 (arch/x86_64/mmt4d_x86_64_avx512_base.c:312 has the ISA function): byte
-    planes of both operands, four 8-bit tensor-core products per term, recombined modulo 2^32.
-    Full-range s16 values, so the sums wrap like the reference's int32 arithmetic; bit-exact.
-    Without scratch the generic kernel serves the same problem and agrees."""
+def test_mmt4d_byte_plane_types_on_the_tensor_cores(t, K0, shape, accumulate):
+    """The integer triples wider or narrower than a byte, 16x16 tiles, as 8-bit tensor-core
+    products. s16s16s32 16x16x2 (arch/x86_64/mmt4d_x86_64_avx512_base.c:312 has the ISA function):
+    byte planes of both operands, four products per term into three accumulators, recombined
+    modulo 2^32. s16s8s32: byte planes of the LHS, two products per term. s8s4s32: the nibbles
+    sign-extended to bytes by the pre-pass (mmt4d_tile_generic.c:37-44), one product per term.
+    Full-range values, so the sums wrap like the reference's int32 arithmetic; bit-exact. Without
+    scratch the generic kernel serves the same problem and agrees."""
     M, N, K = shape
-    case = cases.Mmt4dCase(abi.MMT4D_S16S16S32, 16, 16, 2, M, N, K, accumulate, seed=M + K,
-                           mode="normal", loose=False)
+    case = cases.Mmt4dCase(t, 16, 16, K0, M, N, K, accumulate, seed=M + K, mode="normal",
+                           loose=False)
     got, path = G.run_mmt4d_case(case)
     assert path == abi.PATH_TCGEN05_RETILE
     assert np.array_equal(got, G.oracle_mmt4d(case)), shape
