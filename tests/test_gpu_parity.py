@@ -372,6 +372,8 @@ def test_interleave_slabs_kernel():
     (abi.MMT4D_BF16BF16F32, 16, 16, 2, 9, 17, 33, 0, "exact"),
     (abi.MMT4D_S16U4S32, 1, 32, 8, 40, 9, 16, 1, "normal"),
     (abi.MMT4D_S16S16S32, 16, 16, 2, 9, 17, 33, 1, "normal"),
+    (abi.MMT4D_S16S8S32, 16, 16, 2, 9, 17, 33, 0, "normal"),
+    (abi.MMT4D_S8S4S32, 16, 16, 4, 9, 17, 33, 1, "normal"),
     (abi.MMT4D_S8S8S32, 9, 6, 3, 5, 7, 13, 1, "exact"),
     (abi.MMT4D_F16F16F16, 3, 5, 8, 5, 3, 4, 0, "exact"),
     (abi.MMT4D_S8S8S32, 16, 16, 2, 3, 5, 0, 0, "exact"),
