@@ -69,10 +69,14 @@ class HostShardedMmt4d:
         self.h2d_bytes_lhs = per * host_lhs.element_size()
 
     def run(self, stream=None):
-        """Enqueues one call; the host output is complete once ``stream`` has been synchronised."""
-        self.my_dev.copy_(self.my_host, non_blocking=True)
-        self.dist.all_gather_into_tensor(self.lhs_dev.view(-1), self.my_dev, group=self.group)
-        uk.mmt4d_host_resident_lhs(self.params, self.lhs_dev, self.row_elems, self.arena, stream)
+        """Enqueues one call on ``stream`` (a torch stream; default: the current one); the host
+        output is complete once that stream has been synchronised."""
+        torch = self.torch
+        stream = stream if stream is not None else torch.cuda.current_stream()
+        with torch.cuda.stream(stream):  # the copy and the collective are ordered on `stream`
+            self.my_dev.copy_(self.my_host, non_blocking=True)
+            self.dist.all_gather_into_tensor(self.lhs_dev.view(-1), self.my_dev, group=self.group)
+            uk.mmt4d_host_resident_lhs(self.params, self.lhs_dev, self.row_elems, self.arena, stream)
 
 
 class PeerOutputs:

@@ -144,3 +144,67 @@ def test_multicast_replication_two_processes():
     port = s.getsockname()[1]
     s.close()
     mp.spawn(_multicast_worker, args=(2, port), nprocs=2, join=True)
+
+
+def _host_sharded_worker(rank, world, port):
+    """One rank of the sharded host-buffer call: its own RHS tile rows and output slab in pinned
+    host memory, 1/world of the LHS uploaded, the rest received by an NCCL all-gather. Every rank
+    reaches the final barrier whatever it found (verdicts are exchanged first)."""
+    import os
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    from iree_b200 import sharding, ukernel as uk
+    ok, why = True, ""
+    try:
+        M, N, K = 8, 6, 40
+        case = cases.Mmt4dCase(abi.MMT4D_S8S8S32, 16, 16, 2, M, N, K, 0, seed=33, mode="normal",
+                               loose=False)
+        want = G.oracle_mmt4d(case).view(np.int32).reshape(M, N, 256)
+        b, c = sharding.shard_bounds(N, rank, world)
+        h_lhs = torch.from_numpy(case.lhs.copy()).pin_memory()
+        rhs_rows = case.rhs.reshape(N, -1)[b:b + c].copy()
+        h_rhs = torch.from_numpy(rhs_rows).pin_memory()
+        h_out = torch.full((M * c * 256,), 7, dtype=torch.int32).pin_memory()
+        p = abi.Mmt4dParams()
+        p.M, p.N, p.K, p.M0, p.N0, p.K0, p.flags = M, c, K, 16, 16, 2, abi.MMT4D_S8S8S32
+        p.lhs_buffer, p.rhs_buffer, p.out_buffer = h_lhs.data_ptr(), h_rhs.data_ptr(), h_out.data_ptr()
+        p.lhs_stride0, p.rhs_stride0, p.out_stride0 = K * 32, K * 32, c * 256
+        call = sharding.HostShardedMmt4d(p, h_lhs)
+        for _ in range(2):  # twice: the second call reuses the arena and the gathered LHS buffer
+            h_out.fill_(7)
+            call.run()
+            torch.cuda.synchronize()
+            if not np.array_equal(h_out.numpy().reshape(M, c, 256), want[:, b:b + c]):
+                ok, why = False, "rank %d: slab differs from the reference result" % rank
+        if ok and uk.device_status() != (0, 0):
+            ok, why = False, "device status"
+    except Exception as e:
+        ok, why = False, repr(e)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    assert ok, why
+    assert int(flag.item()) == 1, "another rank failed"
+
+
+def test_host_buffers_sharded_over_two_processes():
+    """Two ranks on two GPUs: the LHS crosses PCIe once (half per rank, completed by an
+    all-gather), each rank's host output slab equals the reference's columns."""
+    import socket
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_host_sharded_worker, args=(2, port), nprocs=2, join=True)
