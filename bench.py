@@ -309,13 +309,13 @@ def per_config_rooflines(supp, peaks):
            "iree_uk_b200_mmt4d_pooled: retile_kernel<4> + mmt4d_tc2_kernel<float>", burst, spec=2250.0)
     tensor("mmt4d_bf16_headline_plain_call_scratch_free", "mmt4d_bf16_headline_plain_call_scratch_free",
            "iree_uk_b200_mmt4d: mmt4d_tc_sw_kernel", burst, spec=2250.0)
-    tensor("mmt4d_s16s16s32_4096x4096x4096_as_8bit_tensor_work", "mmt4d_s16s16s32_4096x4096x4096",
+    tensor("mmt4d_s16s16s32_8192x14336x4096_as_8bit_tensor_work", "mmt4d_s16s16s32_8192x14336x4096",
            "retile_split_s16 + mmt4d_tc2_kernel<int> (four i8 products per term)", 2 * burst,
            scale=4.0)
-    tensor("mmt4d_s16s8s32_4096x4096x4096_as_8bit_tensor_work", "mmt4d_s16s8s32_4096x4096x4096",
+    tensor("mmt4d_s16s8s32_8192x14336x4096_as_8bit_tensor_work", "mmt4d_s16s8s32_8192x14336x4096",
            "retile_split_s16 + retile_kernel<2> + mmt4d_tc2_kernel<int> (two i8 products per term)",
            2 * burst, scale=2.0)
-    tensor("mmt4d_s8s4s32_4096x4096x4096", "mmt4d_s8s4s32_4096x4096x4096",
+    tensor("mmt4d_s8s4s32_8192x14336x4096", "mmt4d_s8s4s32_8192x14336x4096",
            "widen_s4_kernel + retile_kernel<2> + mmt4d_tc2_kernel<int>", 2 * burst)
     memory("mmt4d_s16u4s32_gemv_1x14336x4096_per_call", "mmt4d_s16u4s32_gemv_1x14336x4096",
            "mmt4d_gemv_s16u4_kernel")

@@ -270,16 +270,16 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
             r["frac_of_bf16_burst"] = r["tops"] / bf16_peak
             res[k] = r
     # s16s16s32 16x16x2: four 8-bit tensor-core products per s16 x s16 term
-    if want("mmt4d_s16s16s32_4096x4096x4096"):
-        k, r = _mmt4d_case("mmt4d_s16s16s32_4096x4096x4096", abi.MMT4D_S16S16S32, 256, 256, 2048,
+    if want("mmt4d_s16s16s32_8192x14336x4096"):
+        k, r = _mmt4d_case("mmt4d_s16s16s32_8192x14336x4096", abi.MMT4D_S16S16S32, 512, 896, 2048,
                            16, 16, 2, peaks, None)
         r["frac_of_2x_bf16_burst_counting_all_four_byte_products"] = 4 * r["tops"] / (2 * bf16_peak)
         res[k] = r
     # s16s8s32 16x16x2 (two products per term) and s8s4s32 16x16x2 (nibbles widened by the pre-pass)
-    for name, flags, products in [("mmt4d_s16s8s32_4096x4096x4096", abi.MMT4D_S16S8S32, 2),
-                                  ("mmt4d_s8s4s32_4096x4096x4096", abi.MMT4D_S8S4S32, 1)]:
+    for name, flags, products in [("mmt4d_s16s8s32_8192x14336x4096", abi.MMT4D_S16S8S32, 2),
+                                  ("mmt4d_s8s4s32_8192x14336x4096", abi.MMT4D_S8S4S32, 1)]:
         if want(name):
-            k, r = _mmt4d_case(name, flags, 256, 256, 2048, 16, 16, 2, peaks, None)
+            k, r = _mmt4d_case(name, flags, 512, 896, 2048, 16, 16, 2, peaks, None)
             r["frac_of_2x_bf16_burst_counting_every_byte_product"] = products * r["tops"] / (2 * bf16_peak)
             res[k] = r
     # decode GEMV s16u4s32: bytes are the algorithmic figure (weights + vector + output)
