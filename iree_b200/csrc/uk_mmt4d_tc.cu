@@ -388,6 +388,7 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   TcParams P;
   std::memset(&P, 0, sizeof P);
   const int64_t kbytes = p->K * 8, ncols = p->N * 32;
+  // (256 columns with one accumulator buffer measured slower here: 0.712 against 0.693 ms)
   const int bn = int(std::min<int64_t>(128, ncols));
   const uint64_t da[3] = {uint64_t(kbytes), uint64_t(p->M), 2};
   const uint64_t db[3] = {uint64_t(kbytes), uint64_t(ncols), 1};
@@ -421,6 +422,7 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   P.idesc = common | (1u << 7);
   P.idesc2 = common;
   P.dual = 1;
+  P.acc_bufs = 2 * 2 * bn <= 512 ? 2 : 1;
   P.kboxes = 1;
   P.mma_per_box = 4;
   P.stage_bytes_a = 2 * BM * 128;
@@ -518,11 +520,19 @@ int launch_mmt4d_tc_s16s16(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_
   TcParams P;
   std::memset(&P, 0, sizeof P);
   const int64_t kbytes = p->K * 2, rows = p->M * 16, ncols = p->N * 16;
-  // 128 accumulator columns x 3 accumulators leave room for one buffer only; narrower problems
-  // (64 columns or fewer) keep two.
-  const int bn = int(std::min<int64_t>(128, round_up(ncols, 16)));
+  // Accumulator width. 128 columns by default: two accumulators then fit TMEM twice (the
+  // epilogue overlaps the next tile), three only once. Problems that fill the CTA pairs with
+  // wider tiles take them, with ONE accumulator buffer: 256 columns in the two-product mode
+  // (measured 0.719 against 0.765 ms at 8192 x 14336 x 4096: wider MMAs re-read the LHS planes
+  // from shared memory half as often, which outweighs the lost overlap), 160 in the four-product
+  // mode (3 x 160 = 480 of the 512 columns; 1.230 against 1.259 ms).
+  int bn = int(std::min<int64_t>(128, round_up(ncols, 16)));
+  {
+    const int wide = rhs_s8 ? 256 : 160;
+    if (rows >= 256 && ((rows + 255) / 256) * ((ncols + wide - 1) / wide) >= 74) bn = wide;
+  }
   const int pair_clusters = di->pair_clusters[1][0];
-  const bool pair = bn == 128 && rows >= 256 && pair_clusters >= 1 &&
+  const bool pair = bn >= 128 && rows >= 256 && pair_clusters >= 1 &&
                     ((rows + 255) / 256) * ((ncols + 127) / 128) >= 74;
   const int tile_m = pair ? 2 * BM : BM;
   const int b_rows = pair ? bn / 2 : bn;
@@ -550,7 +560,7 @@ int launch_mmt4d_tc_s16s16(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_
     P.idesc = common | (1u << 7) | (1u << 10);
     P.idesc2 = common | (1u << 10);
     P.dual = 2;
-    P.acc_bufs = 2;
+    P.acc_bufs = 2 * 2 * bn <= 512 ? 2 : 1;
   } else {
     P.idesc = common;
     P.quad = 1;

@@ -173,7 +173,10 @@ def test_mmt4d_s16u4_tensor_core_path(shape, accumulate):
 @pytest.mark.parametrize("shape", [(1, 1, 1), (8, 16, 64), (9, 17, 65), (3, 5, 7), (24, 40, 31),
                                    (1, 1, 1000), (16, 3, 260),
                                    # enough 256 x 128 tiles for the two-CTA form, ragged edges
-                                   (160, 64, 9), (170, 67, 5)], ids=lambda s: "%dx%dx%d" % s)
+                                   (160, 64, 9), (170, 67, 5),
+                                   # enough tiles for the wide single-buffered accumulators
+                                   # (256 / 160 columns), ragged in M and N
+                                   (325, 67, 3)], ids=lambda s: "%dx%dx%d" % s)
 @pytest.mark.parametrize("t,K0", [(abi.MMT4D_S16S16S32, 2), (abi.MMT4D_S16S8S32, 2),
                                   (abi.MMT4D_S8S4S32, 2), (abi.MMT4D_S8S4S32, 4),
                                   (abi.MMT4D_S8S4S32, 8), (abi.MMT4D_S8S4S32, 16)],
