@@ -174,20 +174,22 @@ __global__ void __launch_bounds__(256) mmt4d_zero_fill_kernel(char* out, int64_t
 // even k0]; the whole RHS row n1 is K*128 contiguous bytes. One block per (m, n1) pair
 // keeps 32 int32 sums; each lane takes 16 bytes (4 n0 rows of one k1) per step, four k1
 // per warp step, and the eight warps interleave along K in chunks. HBM-bound by construction:
-// every weight byte is read once. The s16 x u4 products are computed exactly as
-// byte dot products: s16 = signed high byte * 256 + unsigned low byte, nibbles widened to
-// bytes, four dp4a per 8 weights, recombined as hi*256 + lo at the end.
+// every weight byte is read once. The nibbles are widened to bytes in registers (even and odd
+// ones apart) and multiplied with the s16 activations by dp2a, four per 8 weights; the
+// activations of a chunk are paired for that once per k1 step and shared through a staging row
+// per warp, not re-arranged by each of the eight lanes that meet the same k1.
 // ---------------------------------------------------------------------------------------
 
-__device__ __forceinline__ uint32_t dp4a_uu(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+// a: two signed 16-bit values, b: four unsigned bytes of which the low (high) two are used:
+// d = c + a.lo * b.byte0 + a.hi * b.byte1 (b.byte2, b.byte3)
+__device__ __forceinline__ int32_t dp2a_lo(uint32_t a, uint32_t b, int32_t c) {
+  int32_t d;
+  asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
-// a: four unsigned bytes, b: four signed bytes
-__device__ __forceinline__ int32_t dp4a_us(uint32_t a, uint32_t b, int32_t c) {
+__device__ __forceinline__ int32_t dp2a_hi(uint32_t a, uint32_t b, int32_t c) {
   int32_t d;
-  asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
 }
 
@@ -210,6 +212,7 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
   __shared__ __align__(128) unsigned char wbuf[kGemvBulkWarps][kGemvChunkBytes];
   __shared__ __align__(8) uint64_t bar[kGemvBulkWarps];
   __shared__ int32_t partial[kGemvBulkWarps][32];
+  __shared__ uint4 xs[kGemvBulkWarps][kGemvChunkK1];  // per warp: the chunk's activations, paired
   const int64_t m = blockIdx.x / a.N, n1 = blockIdx.x - m * a.N;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kq = lane >> 3, ng = lane & 7;
@@ -222,8 +225,7 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
-  uint32_t acc_lo[4] = {0u, 0u, 0u, 0u};
-  int32_t acc_hi[4] = {0, 0, 0, 0};
+  int32_t acc[4] = {0, 0, 0, 0};
   const int64_t chunks = (a.K + kGemvChunkK1 - 1) / kGemvChunkK1;
   uint32_t parity = 0;
   bool ok = true;
@@ -239,13 +241,17 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
           "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
           :: "r"(my_buf), "l"(rhs + k0 * 128), "r"(bytes), "r"(my_bar) : "memory");
     }
-    // the activations of this chunk, while the weights are on their way
-    uint4 xv[kGemvChunkK1 / 4];
-#pragma unroll
-    for (int s = 0; s < kGemvChunkK1 / 4; ++s) {
-      const int k = s * 4 + kq;
-      xv[s] = k < steps ? __ldg(lhs + k0 + k) : make_uint4(0u, 0u, 0u, 0u);
+    // The activations of this chunk, while the weights are on their way: lane l takes k1 step l,
+    // pairs its eight s16 values the way dp2a consumes them against the even and the odd nibbles
+    // - (x0,x2) (x4,x6) (x1,x3) (x5,x7) - and leaves the four words in this warp's staging row.
+    {
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (lane < steps) x = __ldg(lhs + k0 + lane);
+      const uint4 pairs = make_uint4(__byte_perm(x.x, x.y, 0x5410), __byte_perm(x.z, x.w, 0x5410),
+                                     __byte_perm(x.x, x.y, 0x7632), __byte_perm(x.z, x.w, 0x7632));
+      xs[warp][lane] = pairs;
     }
+    __syncwarp();
     // bounded wait for the chunk
     {
       const long long deadline = clock64() + (1ll << 31);
@@ -288,24 +294,19 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
                      : "r"(my_buf + uint32_t(k) * 128u + uint32_t(ng) * 16u) : "memory");
-      const uint4 x = xv[s];
-      const uint32_t e01 = __byte_perm(x.x, x.y, 0x5140), e23 = __byte_perm(x.z, x.w, 0x5140);
-      const uint32_t o01 = __byte_perm(x.x, x.y, 0x7362), o23 = __byte_perm(x.z, x.w, 0x7362);
-      const uint32_t xe_lo = __byte_perm(e01, e23, 0x5410), xe_hi = __byte_perm(e01, e23, 0x7632);
-      const uint32_t xo_lo = __byte_perm(o01, o23, 0x5410), xo_hi = __byte_perm(o01, o23, 0x7632);
+      const uint4 x = xs[warp][k];  // the eight lanes of one k read the same row
       const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const uint32_t w_even = ws[r] & 0x0F0F0F0Fu, w_odd = (ws[r] >> 4) & 0x0F0F0F0Fu;
-        acc_lo[r] = dp4a_uu(w_even, xe_lo, dp4a_uu(w_odd, xo_lo, acc_lo[r]));
-        acc_hi[r] = dp4a_us(w_even, xe_hi, dp4a_us(w_odd, xo_hi, acc_hi[r]));
+        acc[r] = dp2a_lo(x.x, w_even, acc[r]);
+        acc[r] = dp2a_hi(x.y, w_even, acc[r]);
+        acc[r] = dp2a_lo(x.z, w_odd, acc[r]);
+        acc[r] = dp2a_hi(x.w, w_odd, acc[r]);
       }
     }
     __syncwarp();  // every lane is done with the buffer before lane 0 refills it
   }
-  int32_t acc[4];
-#pragma unroll
-  for (int r = 0; r < 4; ++r) acc[r] = int32_t(acc_lo[r] + (uint32_t(acc_hi[r]) << 8));
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 8);
