@@ -68,6 +68,20 @@ def _time_rotating(fns, iters=None, warmup=None):
     return times[len(times) // 2], times[0]
 
 
+SETTLE_SECONDS = 0.0  # set by run() when the whole list is measured
+
+
+def _settle():
+    """Every case of the whole list starts from an idle GPU: seconds of tensor-core work just
+    before leave the part power-capped and its memory system slower for a second or two (a
+    same-size device copy then measures 5.4 instead of 5.9 TB/s, a 7 us GEMV 9.7 us), and these
+    figures are about the kernels, not about what ran before them."""
+    if SETTLE_SECONDS > 0:
+        import time
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_SECONDS)
+
+
 def _mmt4d_params(flags, M, N, K, M0, N0, K0, lhs, rhs, out):
     p = abi.Mmt4dParams()
     p.lhs_buffer, p.rhs_buffer, p.out_buffer = lhs.data_ptr(), rhs.data_ptr(), out.data_ptr()
@@ -104,6 +118,7 @@ def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None
             fns.append(lambda p=p: uk.mmt4d_pooled(p))
         else:
             fns.append(lambda p=p, ws=ws: uk.mmt4d(p, workspace=ws))
+    _settle()
     if copies > 1:
         med, best = _time_rotating(fns)
     else:
@@ -113,6 +128,7 @@ def _mmt4d_case(name, flags, M, N, K, M0, N0, K0, peaks, flush, float_dtype=None
     if copies > 1:
         res["timing"] = "sweep over %d buffer sets (footprint > L2), one event pair" % copies
     if graph_calls:
+        _settle()
         res["graph_replay"] = _graph_replay(fns, graph_calls, ops)
     return name, res
 
@@ -212,6 +228,8 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
     """All supplementary configurations, or those whose name contains ``only``. ``custom`` =
     (type name, M1, N1, K1) adds one tensor-core mmt4d of that size (used for profiling)."""
     res = {}
+    global SETTLE_SECONDS
+    SETTLE_SECONDS = 1.0 if only is None else 0.0
 
     def want(name):
         return only is None or only in name
@@ -330,13 +348,9 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
             8192, 28672, 8192, bf16_peak)
 
     # pack f32 8192x8192 -> [512][8192][16][1]; TRANSPOSE_INNER variant; RHS-style 0x301.
-    # The bandwidth-bound group starts after a two-second pause: seconds of GEMM work just before
-    # leave the memory system slower for a second or two (a same-size device copy measures
-    # 5.4 instead of 5.9 TB/s), and these figures are about the kernels, not about what ran before.
-    if only is None:
-        import time
-        torch.cuda.synchronize()
-        time.sleep(2.0)
+    # The bandwidth-bound group, too, starts from an idle GPU (see _settle).
+    _settle()
+    _settle()
     n = 8192
     src = torch.randn(n * n, device="cuda")
     dst = torch.empty(n * n, device="cuda")
