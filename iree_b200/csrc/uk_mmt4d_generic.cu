@@ -332,7 +332,9 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
 // the next power of two) and for which it ships ISA tile functions
 // (arch/x86_64/mmt4d_x86_64_tiles.inl): s8s8s32 K0 = 2, f16f16f32 K0 = 1, bf16bf16f32 K0 = 2.
 // With so few LHS rows the call is a weight stream: every RHS byte is read once per LHS tile
-// row and used for M0 multiply-adds, so HBM bounds it and tensor cores cannot help.
+// row and used for M0 multiply-adds, so HBM bounds it - as long as the arithmetic keeps up,
+// which on the CUDA cores it does for M0 = 1 (and 2); the wider tiles take the warp-level
+// tensor-core instruction (mmt4d_narrow_mma_kernel below).
 // One block per (LHS tile row, RHS tile row); its 8 warps interleave along K, each lane reads
 // 16-byte vectors of the RHS row - a vector holds one k1 step of 4 (bf16) or 8 (s8, f16)
 // neighbouring n0 rows, and a lane always meets the same rows - with four loads in flight, takes
@@ -444,6 +446,130 @@ __global__ void __launch_bounds__(256) mmt4d_narrow_kernel(GenericArgs a) {
   }
 }
 
+// The same weight stream where the CUDA-core form above is bound by its multiply-adds (M0 per
+// weight; every M0 for bf16, M0 = 4 and 8 for f16 and s8): the warp-level tensor-core
+// instruction mma.sync m16n8k16 (bf16, f16) / m16n8k32 (s8) has exactly this shape when the 16
+// rows of an RHS tile are its M and the up to 8 rows of the LHS tile its N. Fragments come
+// straight from global memory: for bf16 (K0 = 2) one k1 step of one n0 row is the 4-byte pair an
+// A register holds, so a lane takes 8 bytes = rows 2g, 2g+1 (the instruction's rows g and g+8)
+// at k1 = kb+t and again at kb+t+4; for f16 (K0 = 1) and s8 (K0 = 2) one k1 step of one row is
+// 2 bytes, two neighbouring k1 steps make a register (a byte permute of two 4-byte loads). The
+// LHS tile is a few KB and comes through L1. Eight warps interleave along K, four MMAs' worth
+// of loads in flight per warp; sums in another order than the reference's (integers exact).
+template <NarrowType T>
+__device__ __forceinline__ void narrow_mma(uint32_t (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  if (T == NarrowType::BF16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  else if (T == NarrowType::F16)
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+  else
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <NarrowType T, int M0>
+__global__ void __launch_bounds__(256) mmt4d_narrow_mma_kernel(GenericArgs a) {
+  constexpr bool G4 = T == NarrowType::BF16;  // 4-byte granules (one k1 step of one row)
+  constexpr int KM = G4 ? 8 : 16;             // k1 steps per MMA
+  constexpr int U = 4;                        // MMAs whose loads are in flight together
+  using Acc = typename std::conditional<T == NarrowType::S8, int32_t, float>::type;
+  __shared__ Acc partial[8][M0][16];
+  const int64_t m1 = blockIdx.x / a.N, n1 = blockIdx.x - m1 * a.N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const char* rhs = a.rhs + n1 * a.rhs_stride_b;
+  const char* lhs = a.lhs + m1 * a.lhs_stride_b;
+  const int64_t K = a.K;
+  const int gm = g < M0 ? g : M0 - 1;  // the LHS row this lane reads (rows past M0 count as zero)
+  const bool row_live = g < M0;
+  uint32_t d[4] = {0u, 0u, 0u, 0u};
+  constexpr int WB = G4 ? 64 : 32;            // RHS bytes per k1 step
+  constexpr int XB = (G4 ? 4 : 2) * M0;       // LHS bytes per k1 step
+  // this lane's first addresses within a group of KM k1 steps
+  const char* wp = rhs + (G4 ? t * WB + g * 8 : 2 * t * WB + g * 4);
+  const char* xp = lhs + (G4 ? t * XB + gm * 4 : 2 * t * XB + gm * 2);
+  // One group's fragments. FULL: all KM k1 steps exist, every load is unconditional at a
+  // constant offset from the lane's pointers; else each k1 step is checked against K.
+  auto load_group = [&](int64_t grp, uint32_t (&fa)[4], uint32_t (&fb)[2], auto full) {
+    constexpr bool FULL = decltype(full)::value;
+    const int64_t kb = grp * KM;
+    const char* w = wp + kb * WB;
+    const char* x = xp + kb * XB;
+    if (G4) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const bool live = FULL || kb + t + 4 * h < K;
+        uint2 wv = make_uint2(0u, 0u);
+        uint32_t xv = 0u;
+        if (live) wv = __ldg(reinterpret_cast<const uint2*>(w + 4 * h * WB));
+        if (live && row_live) xv = __ldg(reinterpret_cast<const uint32_t*>(x + 4 * h * XB));
+        fa[2 * h] = wv.x;      // n0 = 2g   -> row g of the instruction
+        fa[2 * h + 1] = wv.y;  // n0 = 2g+1 -> row g + 8
+        fb[h] = xv;
+      }
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int64_t k1 = kb + 8 * h + 2 * t;
+        uint32_t w0 = 0u, w1 = 0u, x0 = 0u, x1 = 0u;
+        const bool live0 = FULL || k1 < K, live1 = FULL || k1 + 1 < K;
+        if (live0) w0 = __ldg(reinterpret_cast<const uint32_t*>(w + 8 * h * WB));
+        if (live1) w1 = __ldg(reinterpret_cast<const uint32_t*>(w + (8 * h + 1) * WB));
+        if (live0 && row_live) x0 = __ldg(reinterpret_cast<const uint16_t*>(x + 8 * h * XB));
+        if (live1 && row_live) x1 = __ldg(reinterpret_cast<const uint16_t*>(x + (8 * h + 1) * XB));
+        fa[2 * h] = __byte_perm(w0, w1, 0x5410);      // row 2g at k1, k1 + 1
+        fa[2 * h + 1] = __byte_perm(w0, w1, 0x7632);  // row 2g+1
+        fb[h] = x0 | (x1 << 16);
+      }
+    }
+  };
+  const int64_t groups = (K + KM - 1) / KM, full_groups = K / KM;
+  int64_t grp = int64_t(warp) * U;
+  for (; grp + U <= full_groups; grp += 8 * U) {
+    uint32_t fa[U][4], fb[U][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) load_group(grp + u, fa[u], fb[u], std::true_type());
+#pragma unroll
+    for (int u = 0; u < U; ++u) narrow_mma<T>(d, fa[u], fb[u]);
+  }
+  // what is left of this warp's share: fewer than U groups, the last one possibly ragged
+  for (int u = 0; u < U && grp + u < groups; ++u) {
+    uint32_t fa[4], fb[2];
+    load_group(grp + u, fa, fb, std::false_type());
+    narrow_mma<T>(d, fa, fb);
+  }
+  // d0, d1: n0 = 2g, m0 = 2t, 2t+1; d2, d3: n0 = 2g+1
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m0 = 2 * t + (i & 1), n0 = 2 * g + (i >> 1);
+    if (m0 < M0) {
+      Acc v;
+      if (T == NarrowType::S8) v = Acc(int32_t(d[i]));
+      else v = Acc(__uint_as_float(d[i]));
+      partial[warp][m0][n0] = v;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < M0 * 16; e += blockDim.x) {
+    const int m = e >> 4, n0 = e & 15;
+    Acc sum = Acc(0);
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) sum += partial[w8][m][n0];
+    Acc* op = reinterpret_cast<Acc*>(a.out) + m1 * a.out_stride0 + n1 * (M0 * 16) + e;
+    if (T == NarrowType::S8) {
+      uint32_t* uo = reinterpret_cast<uint32_t*>(op);
+      *uo = a.accumulate ? *uo + uint32_t(sum) : uint32_t(sum);  // wraps like the reference's int32
+    } else {
+      *op = a.accumulate ? *op + sum : sum;
+    }
+  }
+}
+
 bool fill_args(const iree_uk_mmt4d_params_t* p, GenericArgs* a) {
   Mmt4dTypes t;
   if (!mmt4d_types(p->flags, &t)) return false;
@@ -538,6 +664,20 @@ bool mmt4d_narrow_eligible(const iree_uk_mmt4d_params_t* p) {
 namespace {
 template <NarrowType T>
 int launch_narrow_m0(const GenericArgs& a, int blocks, cudaStream_t stream) {
+  // From which M0 on the tensor-core form runs. Measured per call at N = 28672, K = 8192 (M0 = 1,
+  // 4, 8; CUDA-core form / tensor-core form): bf16 76 / 69, 96 / 70, 163 / 84 us; f16 83 / 85,
+  // 104 / 90, 183 / 87 us; s8 40 / 44, 57 / 46, 105 / 44 us.
+  const int mma_from_default = T == NarrowType::BF16 ? 1 : 4;
+  const int mma_from = debug_int("IREE_UK_B200_DEBUG_NARROW_MMA_FROM", mma_from_default);
+  if (a.M0 >= mma_from) {
+    switch (a.M0) {
+      case 1: mmt4d_narrow_mma_kernel<T, 1><<<blocks, 256, 0, stream>>>(a); break;
+      case 2: mmt4d_narrow_mma_kernel<T, 2><<<blocks, 256, 0, stream>>>(a); break;
+      case 4: mmt4d_narrow_mma_kernel<T, 4><<<blocks, 256, 0, stream>>>(a); break;
+      default: mmt4d_narrow_mma_kernel<T, 8><<<blocks, 256, 0, stream>>>(a); break;
+    }
+    return cuda_status(cudaGetLastError());
+  }
   switch (a.M0) {
     case 1: mmt4d_narrow_kernel<T, 1><<<blocks, 256, 0, stream>>>(a); break;
     case 2: mmt4d_narrow_kernel<T, 2><<<blocks, 256, 0, stream>>>(a); break;
