@@ -323,6 +323,10 @@ def per_config_rooflines(supp, peaks):
            "mmt4d_gemv_s16u4_kernel", sub="graph_replay")
     memory("mmt4d_bf16_gemv_1x28672x8192_narrowed_m0_graph_replay", "mmt4d_bf16_gemv_1x28672x8192",
            "mmt4d_narrow_mma_kernel<bf16, M0=1>", sub="graph_replay")
+    memory("mmt4d_bf16_gemv_8x28672x8192_narrowed_m0_graph_replay", "mmt4d_bf16_gemv_8x28672x8192",
+           "mmt4d_narrow_mma_kernel<bf16, M0=8>", sub="graph_replay")
+    memory("mmt4d_s8_gemv_8x28672x8192_narrowed_m0_graph_replay", "mmt4d_s8_gemv_8x28672x8192",
+           "mmt4d_narrow_mma_kernel<s8, M0=8>", sub="graph_replay")
     memory("pack_f32_8192x8192_16x1", "pack_f32_8192x8192_to_512x8192x16x1",
            "relayout_staged_kernel<pack, 16x1>")
     memory("pack_f32_8192x8192_rhs_0x301", "pack_f32_rhs_0x301_512x8192x16x1",

@@ -319,6 +319,17 @@ def run(peaks, only=None, custom=None, custom_ws=True, custom_matmul=None):
         r["frac_hbm"] = r["gbs"] / hbm
         r["graph_replay"]["gbs"] = nbytes_gemv / r["graph_replay"]["ms_per_call"] / 1e6
         res[k] = r
+    # the same weights against 8 tokens (M0 = 8): bf16, and s8 at the same N and K
+    for name, flags, dt, es in [("mmt4d_bf16_gemv_8x28672x8192", abi.MMT4D_BF16BF16F32, torch.bfloat16, 2),
+                                ("mmt4d_s8_gemv_8x28672x8192", abi.MMT4D_S8S8S32, None, 1)]:
+        if want(name):
+            k, r = _mmt4d_case(name, flags, 1, 1792, 4096, 8, 16, 2, peaks, None, dt, copies=1,
+                               graph_calls=20)
+            nb = 1792 * 4096 * 32 * es + 4096 * 16 * es + 1792 * 8 * 16 * 4
+            r["gbs"] = nb / r["ms"] / 1e6
+            r["frac_hbm"] = r["gbs"] / hbm
+            r["graph_replay"]["gbs"] = nb / r["graph_replay"]["ms_per_call"] / 1e6
+            res[k] = r
 
     if custom_matmul is not None:
         mm, mn, mk = custom_matmul
