@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(256) mmt4d_narrow_kernel(GenericArgs a) {
 }
 
 // The same weight stream where the CUDA-core form above is bound by its multiply-adds (M0 per
-// weight; every M0 for bf16, M0 = 4 and 8 for f16 and s8): the warp-level tensor-core
+// weight; every M0 for bf16, from M0 = 2 for s8, from 4 for f16): the warp-level tensor-core
 // instruction mma.sync m16n8k16 (bf16, f16) / m16n8k32 (s8) has exactly this shape when the 16
 // rows of an RHS tile are its M and the up to 8 rows of the LHS tile its N. Fragments come
 // straight from global memory: for bf16 (K0 = 2) one k1 step of one n0 row is the 4-byte pair an
@@ -665,9 +665,9 @@ namespace {
 template <NarrowType T>
 int launch_narrow_m0(const GenericArgs& a, int blocks, cudaStream_t stream) {
   // From which M0 on the tensor-core form runs. Measured per call at N = 28672, K = 8192 (M0 = 1,
-  // 4, 8; CUDA-core form / tensor-core form): bf16 76 / 69, 96 / 70, 163 / 84 us; f16 83 / 85,
-  // 104 / 90, 183 / 87 us; s8 40 / 44, 57 / 46, 105 / 44 us.
-  const int mma_from_default = T == NarrowType::BF16 ? 1 : 4;
+  // 2, 4, 8; CUDA-core form / tensor-core form): bf16 76 / 69, 80 / 69, 96 / 70, 163 / 84 us;
+  // f16 83 / 85, 80 / 87, 104 / 90, 183 / 87 us; s8 40 / 44, 48 / 45, 57 / 46, 105 / 44 us.
+  const int mma_from_default = T == NarrowType::BF16 ? 1 : (T == NarrowType::S8 ? 2 : 4);
   const int mma_from = debug_int("IREE_UK_B200_DEBUG_NARROW_MMA_FROM", mma_from_default);
   if (a.M0 >= mma_from) {
     switch (a.M0) {
