@@ -201,23 +201,29 @@ __device__ __forceinline__ int32_t dp2a_hi(uint32_t a, uint32_t b, int32_t c) {
 // per call where this one takes 7.3 us.) Waits are bounded.
 constexpr int kGemvBulkWarps = 8;
 constexpr int kGemvChunkK1 = 32;                       // k1 steps per chunk
-constexpr int kGemvChunkBytes = kGemvChunkK1 * 128;    // 4 KB of weights
 
 __device__ __forceinline__ uint32_t gemv_smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// R = LHS rows (M0 = 1 tiles) one block serves: a batch of tokens shares one pass over the
+// weights and the nibble split of every weight word (R = 1: the decode call proper).
+template <int R>
 __global__ void __launch_bounds__(kGemvBulkWarps * 32)
 mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
-  __shared__ __align__(128) unsigned char wbuf[kGemvBulkWarps][kGemvChunkBytes];
+  // chunk of k1 steps per bulk copy: 32 (4 KB) for the decode call, 16 with four rows per block
+  // so that the staging rows of the four rows' activations still fit 48 KB of static memory
+  constexpr int CK = R == 1 ? kGemvChunkK1 : kGemvChunkK1 / 2;
+  __shared__ __align__(128) unsigned char wbuf[kGemvBulkWarps][CK * 128];
   __shared__ __align__(8) uint64_t bar[kGemvBulkWarps];
-  __shared__ int32_t partial[kGemvBulkWarps][32];
-  __shared__ uint4 xs[kGemvBulkWarps][kGemvChunkK1];  // per warp: the chunk's activations, paired
-  const int64_t m = blockIdx.x / a.N, n1 = blockIdx.x - m * a.N;
+  __shared__ int32_t partial[kGemvBulkWarps][R][32];
+  __shared__ uint4 xs[kGemvBulkWarps][R][CK];  // per warp: the chunk's activations, paired
+  const int64_t mg = blockIdx.x / a.N, n1 = blockIdx.x - mg * a.N;
+  const int64_t m = mg * R;                              // first LHS row of this block
+  const int rows = int(min(int64_t(R), a.M - m));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kq = lane >> 3, ng = lane & 7;
   const char* rhs = a.rhs + n1 * a.rhs_stride_b;
-  const uint4* lhs = reinterpret_cast<const uint4*>(a.lhs + m * a.lhs_stride_b);
   const uint32_t my_bar = gemv_smem_u32(&bar[warp]);
   const uint32_t my_buf = gemv_smem_u32(&wbuf[warp][0]);
   if (lane == 0) {
@@ -225,13 +231,17 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncwarp();
-  int32_t acc[4] = {0, 0, 0, 0};
-  const int64_t chunks = (a.K + kGemvChunkK1 - 1) / kGemvChunkK1;
+  int32_t acc[R][4];
+#pragma unroll
+  for (int i = 0; i < R; ++i)
+#pragma unroll
+    for (int r = 0; r < 4; ++r) acc[i][r] = 0;
+  const int64_t chunks = (a.K + CK - 1) / CK;
   uint32_t parity = 0;
   bool ok = true;
   for (int64_t c = warp; c < chunks && ok; c += kGemvBulkWarps) {
-    const int64_t k0 = c * kGemvChunkK1;
-    const int steps = int(min(int64_t(kGemvChunkK1), a.K - k0));
+    const int64_t k0 = c * CK;
+    const int steps = int(min(int64_t(CK), a.K - k0));
     if (lane == 0) {
       const uint32_t bytes = uint32_t(steps) * 128u;
       // earlier reads of this buffer (generic proxy) come before the copy's writes (async proxy)
@@ -244,12 +254,14 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
     // The activations of this chunk, while the weights are on their way: lane l takes k1 step l,
     // pairs its eight s16 values the way dp2a consumes them against the even and the odd nibbles
     // - (x0,x2) (x4,x6) (x1,x3) (x5,x7) - and leaves the four words in this warp's staging row.
-    {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
       uint4 x = make_uint4(0u, 0u, 0u, 0u);
-      if (lane < steps) x = __ldg(lhs + k0 + lane);
+      if (i < rows && lane < steps)
+        x = __ldg(reinterpret_cast<const uint4*>(a.lhs + (m + i) * a.lhs_stride_b) + k0 + lane);
       const uint4 pairs = make_uint4(__byte_perm(x.x, x.y, 0x5410), __byte_perm(x.z, x.w, 0x5410),
                                      __byte_perm(x.x, x.y, 0x7632), __byte_perm(x.z, x.w, 0x7632));
-      xs[warp][lane] = pairs;
+      if (lane < CK) xs[warp][i][lane] = pairs;
     }
     __syncwarp();
     // bounded wait for the chunk
@@ -287,41 +299,54 @@ mmt4d_gemv_s16u4_kernel(GenericArgs a, uint32_t* status) {
     }
     parity ^= 1u;
 #pragma unroll
-    for (int s = 0; s < kGemvChunkK1 / 4; ++s) {
+    for (int s = 0; s < CK / 4; ++s) {
       const int k = s * 4 + kq;
       uint4 wv = make_uint4(0u, 0u, 0u, 0u);
       if (k < steps)
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(wv.x), "=r"(wv.y), "=r"(wv.z), "=r"(wv.w)
                      : "r"(my_buf + uint32_t(k) * 128u + uint32_t(ng) * 16u) : "memory");
-      const uint4 x = xs[warp][k];  // the eight lanes of one k read the same row
       const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t w_even[4], w_odd[4];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        const uint32_t w_even = ws[r] & 0x0F0F0F0Fu, w_odd = (ws[r] >> 4) & 0x0F0F0F0Fu;
-        acc[r] = dp2a_lo(x.x, w_even, acc[r]);
-        acc[r] = dp2a_hi(x.y, w_even, acc[r]);
-        acc[r] = dp2a_lo(x.z, w_odd, acc[r]);
-        acc[r] = dp2a_hi(x.w, w_odd, acc[r]);
+        w_even[r] = ws[r] & 0x0F0F0F0Fu;
+        w_odd[r] = (ws[r] >> 4) & 0x0F0F0F0Fu;
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        if (i >= rows) break;
+        const uint4 x = xs[warp][i][k];  // the eight lanes of one k read the same row
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          acc[i][r] = dp2a_lo(x.x, w_even[r], acc[i][r]);
+          acc[i][r] = dp2a_hi(x.y, w_even[r], acc[i][r]);
+          acc[i][r] = dp2a_lo(x.z, w_odd[r], acc[i][r]);
+          acc[i][r] = dp2a_hi(x.w, w_odd[r], acc[i][r]);
+        }
       }
     }
     __syncwarp();  // every lane is done with the buffer before lane 0 refills it
   }
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 8);
-    acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 16);
-  }
-  if (lane < 8) {
+  for (int i = 0; i < R; ++i) {
 #pragma unroll
-    for (int r = 0; r < 4; ++r) partial[warp][ng * 4 + r] = acc[r];
+    for (int r = 0; r < 4; ++r) {
+      acc[i][r] += __shfl_xor_sync(0xFFFFFFFFu, acc[i][r], 8);
+      acc[i][r] += __shfl_xor_sync(0xFFFFFFFFu, acc[i][r], 16);
+    }
+    if (lane < 8) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) partial[warp][i][ng * 4 + r] = acc[i][r];
+    }
   }
   __syncthreads();
-  if (threadIdx.x < 32) {
+  for (int e = threadIdx.x; e < rows * 32; e += blockDim.x) {
+    const int i = e >> 5, n0 = e & 31;
     int32_t s = 0;
 #pragma unroll
-    for (int w = 0; w < kGemvBulkWarps; ++w) s += partial[w][threadIdx.x];
-    int32_t* op = reinterpret_cast<int32_t*>(a.out) + m * a.out_stride0 + n1 * 32 + threadIdx.x;
+    for (int w = 0; w < kGemvBulkWarps; ++w) s += partial[w][i][n0];
+    int32_t* op = reinterpret_cast<int32_t*>(a.out) + (m + i) * a.out_stride0 + n1 * 32 + n0;
     *op = a.accumulate ? int32_t(uint32_t(*op) + uint32_t(s)) : s;
   }
 }
@@ -714,11 +739,17 @@ bool mmt4d_gemv_s16u4_eligible(const iree_uk_mmt4d_params_t* p) {
 int launch_mmt4d_gemv_s16u4(const iree_uk_mmt4d_params_t* p, cudaStream_t stream) {
   GenericArgs a;
   if (!fill_args(p, &a)) return IREE_UK_B200_INVALID_ARGUMENT;
-  const int64_t blocks = a.M * a.N;
-  if (blocks <= 0) return IREE_UK_B200_OK;
+  if (a.M <= 0 || a.N <= 0) return IREE_UK_B200_OK;
   uint32_t* status = device_status_word();
   if (!status) return IREE_UK_B200_CUDA_ERROR;
-  mmt4d_gemv_s16u4_kernel<<<int(blocks), kGemvBulkWarps * 32, 0, stream>>>(a, status);
+  // One LHS row per block for the decode call; batches of rows share a pass over the weights
+  // four rows at a time.
+  if (a.M == 1) {
+    mmt4d_gemv_s16u4_kernel<1><<<int(a.N), kGemvBulkWarps * 32, 0, stream>>>(a, status);
+  } else {
+    const int64_t blocks = (a.M + 3) / 4 * a.N;
+    mmt4d_gemv_s16u4_kernel<4><<<int(blocks), kGemvBulkWarps * 32, 0, stream>>>(a, status);
+  }
   return cuda_status(cudaGetLastError());
 }
 
