@@ -179,9 +179,29 @@ const DeviceInfo* device_info() {
   return &d;
 }
 
+// Cost of the last, partial round of `rem` tiles of width bn over `clusters` CTA pairs (in the
+// unit of pick_bn_pair: columns, plus 96 per tile) and the split that gives it: the tiles stay
+// whole or are cut along N into 2 or 4 narrow ones when that shortens the round.
+int64_t tail_round_cost(int rem, int bn, int clusters, bool may_split, int* split_out) {
+  int best = 1;
+  int64_t best_cost = rem > 0 ? int64_t(bn + 96) : 0;
+  if (rem > 0 && may_split) {
+    for (int split : {2, 4}) {
+      if ((bn / split) % 16 != 0 || bn % split != 0) continue;
+      const int64_t rounds = (int64_t(rem) * split + clusters - 1) / clusters;
+      const int64_t cost = rounds * (bn / split + 96);
+      if (cost < best_cost) { best_cost = cost; best = split; }
+    }
+  }
+  if (split_out) *split_out = best;
+  return best_cost;
+}
+
 // Accumulator width for the pair kernel: among the multiples of 32 columns up to 256, the one
-// that minimises (waves of 256 x bn tiles over `clusters` pairs) x bn, i.e. the estimated time.
-int pick_bn_pair(int64_t M1, int64_t N1, int clusters) {
+// that minimises the estimated time = full rounds of 256 x bn tiles over `clusters` pairs, each
+// bn columns plus a fixed part, plus the last partial round (narrow tail tiles counted when the
+// kernel can cut them).
+int pick_bn_pair(int64_t M1, int64_t N1, int clusters, bool may_split) {
   {
     const int bn = debug_int("IREE_UK_B200_DEBUG_PAIR_BN", 0);
     if (bn >= 32 && bn <= 256 && bn % 32 == 0) return bn;
@@ -191,11 +211,15 @@ int pick_bn_pair(int64_t M1, int64_t N1, int clusters) {
   int64_t best_cost = -1;
   for (int bn = 256; bn >= 128; bn -= 32) {
     const int64_t tiles = m_tiles * ((cols + bn - 1) / bn);
-    const int64_t waves = (tiles + clusters - 1) / clusters;
     // tile time: the MMAs plus a fixed part (96 columns' worth: with 32 the 4096^3 problem chose
     // 192 columns and five waves, which measured 4 % slower than 256 columns and four waves)
-    const int64_t cost = waves * (bn + 96);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    const int64_t full = tiles / clusters;
+    const int rem = int(tiles % clusters);
+    const int64_t cost = full * (bn + 96) + tail_round_cost(rem, bn, clusters, may_split && tiles > clusters, nullptr);
+    // a narrower tile has to win by more than 2 %: 256-column MMAs are the most efficient (the
+    // 8-way shard of the headline problem: estimate 2240 for 224 columns against 2272 for 256,
+    // measured 0.3964 against 0.3931 ms)
+    if (best_cost < 0 || cost * 100 < best_cost * 98) { best_cost = cost; best = bn; }
   }
   return best;
 }
@@ -797,7 +821,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     if (pair) {
       pair_clusters = di->pair_clusters[ti.is_int ? 1 : 0][want_streamed ? streamed_granule_form : 0];
       if (pair_clusters < 1) return IREE_UK_B200_CUDA_ERROR;
-      bn = pick_bn_pair(p->M, p->N, pair_clusters);
+      bn = pick_bn_pair(p->M, p->N, pair_clusters, !ti.triple);
     }
     if (ti.triple) kboxes = 1;  // the two boxes of a stage are the hi and lo planes
     const int64_t pitch = round_up(kelems * ti.es, 128);
@@ -925,13 +949,7 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
     const int tiles = P.num_work, rem = tiles % pair_clusters;
     if (tiles > pair_clusters && rem != 0) {
       int best = 1;
-      int64_t best_cost = int64_t(bn + 96);
-      for (int split : {2, 4}) {
-        if ((bn / split) % 16 != 0 || bn % split != 0) continue;
-        const int64_t rounds = (int64_t(rem) * split + pair_clusters - 1) / pair_clusters;
-        const int64_t cost = rounds * (bn / split + 96);
-        if (cost < best_cost) { best_cost = cost; best = split; }
-      }
+      tail_round_cost(rem, bn, pair_clusters, true, &best);
       best = debug_int("IREE_UK_B200_DEBUG_TAIL_SPLIT", best);
       if (best > 1) {
         const int b_rows_narrow = bn / best / 2;
@@ -1329,7 +1347,7 @@ int launch_matmul_rowmajor(uint32_t flags, const char* lhs, int64_t lhs_pitch_b,
     if (pair_clusters >= 1) {
       pair = true;
       kboxes = 2;
-      bn = pick_bn_pair(M1, N1, pair_clusters);
+      bn = pick_bn_pair(M1, N1, pair_clusters, false);  // the fused matmul cuts no tail tiles
     }
   }
   if (b_direct) {
