@@ -382,8 +382,8 @@ IREE_UK_B200_EXPORT int iree_uk_b200_peer_close(void* device_ptr);
  * Same operation, arguments and results as iree_uk_b200_mmt4d_ws, and the same choice of
  * kernel: whatever iree_uk_b200_mmt4d_ws would run with scratch (the tensor-core triples with
  * 16x16 tiles, s16s16s32 / s16s8s32 16x16x2, s8s4s32 16x16x{2,4,8,16}, and s16u4s32 1x32x8 with at
- * least 32 rows) runs here on the array; problems
- * that use no scratch anyway (the weight-streaming s16u4s32 kernel below 32 rows, the generic
+ * least 16 rows) runs here on the array; problems
+ * that use no scratch anyway (the weight-streaming s16u4s32 kernel below 16 rows, the generic
  * kernel, the zero fill) are served exactly as by iree_uk_b200_mmt4d. Differences:
  *  - a problem whose scratch need (iree_uk_b200_mmt4d_workspace_size) exceeds the array is
  *    refused with IREE_UK_B200_WORKSPACE_TOO_SMALL and nothing is launched; it is never

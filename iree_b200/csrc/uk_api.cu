@@ -64,8 +64,10 @@ int select_mmt4d(const iree_uk_mmt4d_params_t* p, bool have_ws, Mmt4dPath* path)
   if (p->K == 0 || p->K0 == 0) { *path = Mmt4dPath::ZeroFill; return 0; }
   const bool force_generic = env_flag("IREE_UK_B200_FORCE_GENERIC");
   if (!force_generic) {
-    // s16u4s32: the tensor-core path once there are rows to fill a tile, else the GEMV.
-    if (have_ws && p->M >= 32 && mmt4d_tc_s16u4_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
+    // s16u4s32: the tensor-core path from 16 rows on, below that the GEMV. Measured per call at
+    // N = 14336, K = 4096: the tensor-core path 40-45 us whatever M (its pre-pass widens all the
+    // weights), the GEMV with four rows per block 15 / 24 / 41 / 59 / 74 us for 4 / 8 / 16 / 24 / 31 rows.
+    if (have_ws && p->M >= 16 && mmt4d_tc_s16u4_eligible(p)) { *path = Mmt4dPath::TcRetile; return 0; }
     if (mmt4d_gemv_s16u4_eligible(p)) { *path = Mmt4dPath::Gemv; return 0; }
     // narrowed M0 with N0 = 16: weight streaming, with or without scratch
     if (mmt4d_narrow_eligible(p)) { *path = Mmt4dPath::Narrow; return 0; }

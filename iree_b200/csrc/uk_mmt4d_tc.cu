@@ -1211,7 +1211,7 @@ extern "C" int iree_uk_b200_mmt4d_static_scratch(const iree_uk_mmt4d_params_t* p
   const int rc = uk::validate_mmt4d(params);
   if (rc) return rc;
   // Only the kernels that iree_uk_b200_mmt4d_ws would run with scratch need the array: the
-  // tensor-core triples with 16x16 tiles, and s16u4s32 1x32x8 once there are 32 rows (below
+  // tensor-core triples with 16x16 tiles, and s16u4s32 1x32x8 once there are 16 rows (below
   // that the weight-streaming kernel serves it, without scratch). Everything else goes the
   // usual way.
   const int path = iree_uk_b200_mmt4d_path(params, 1);

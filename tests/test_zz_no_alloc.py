@@ -56,7 +56,7 @@ def test_static_scratch_matches_workspace_entry_point_twice_in_a_row():
 
 
 def test_static_scratch_runs_s16u4_with_many_rows_on_the_tensor_cores():
-    """s16u4s32 1x32x8 with at least 32 rows is a scratch-using tensor-core problem for
+    """s16u4s32 1x32x8 with at least 16 rows is a scratch-using tensor-core problem for
     iree_uk_b200_mmt4d_ws, so it must be one here too (same kernel choice, same bytes), and a
     problem of that kind that does not fit the array must be refused."""
     case = cases.Mmt4dCase(abi.MMT4D_S16U4S32, 1, 32, 8, 200, 7, 33, 1, seed=24, mode="normal",
