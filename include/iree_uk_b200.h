@@ -269,8 +269,10 @@ IREE_UK_B200_EXPORT int iree_uk_b200_mmt4d_ws_unpacked(const iree_uk_mmt4d_param
  *       LHS is re-tiled, into `ws` of iree_uk_b200_mmt4d_prepared_workspace_size(params) bytes.
  * `buf` and `ws` are 256-byte aligned device memory. Results are identical to
  * iree_uk_b200_mmt4d_ws. The prepared form is valid while the RHS contents, N, K, K0 and the type
- * stay the same; params->rhs_buffer is not read by iree_uk_b200_mmt4d_ws_prepared. Tensor-core
- * triples with 16x16 tiles only (not s16u4s32, not the f32 mode). */
+ * stay the same; params->rhs_buffer is not read by iree_uk_b200_mmt4d_ws_prepared. For the
+ * s8s8s32 / f16 / bf16 triples with 16x16 tiles, and for s16u4s32 1x32x8, whose prepared form is
+ * the weights widened to bytes: the prepared call then runs the tensor-core kernel for any
+ * number of rows (not the f32 mode, not s16s16 / s16s8 / s8s4). */
 IREE_UK_B200_EXPORT size_t
 iree_uk_b200_mmt4d_prepared_rhs_size(const iree_uk_mmt4d_params_t* params);
 IREE_UK_B200_EXPORT size_t

@@ -367,8 +367,11 @@ int iree_uk_b200_mmt4d_ws_prepared(const iree_uk_mmt4d_params_t* params, const v
   const int rc = select_mmt4d(params, true, &path);
   if (rc) return rc;
   if (path == Mmt4dPath::None) return IREE_UK_B200_OK;
-  if (path != Mmt4dPath::TcRetile || !mmt4d_tc_prepared_rhs_size(params) ||
-      (params->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32)
+  // s16u4s32 with prepared weights takes the tensor-core kernel whatever M: nothing is left of
+  // the pre-pass but the byte-plane split of the LHS
+  const bool s16u4 = (params->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 &&
+                     path != Mmt4dPath::ZeroFill && mmt4d_tc_s16u4_eligible(params);
+  if ((path != Mmt4dPath::TcRetile && !s16u4) || !mmt4d_tc_prepared_rhs_size(params))
     return IREE_UK_B200_UNSUPPORTED;
   return launch_mmt4d_tc(params, workspace, workspace_bytes, kTcVariantDefault,
                          static_cast<cudaStream_t>(cu_stream), nullptr, 0, nullptr, prepared_rhs);

@@ -381,14 +381,16 @@ cudaError_t launch_main(Kernel kernel, int grid, int cluster, size_t smem, cudaS
   return cudaLaunchKernelEx(&cfg, kernel, P);
 }
 
+// `prepared` (optional): the weights already widened to bytes by launch_mmt4d_tc_prepare_rhs and
+// kept by the caller; the scratch then holds the two LHS byte planes only.
 int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, const void* prepared = nullptr) {
   if (!mmt4d_tc_s16u4_eligible(p)) return IREE_UK_B200_UNSUPPORTED;
   uint32_t* status = device_status_word();
   if (!status) return IREE_UK_B200_CUDA_ERROR;
   const S16U4Layout l = s16u4_layout(p);
-  if (!ws || ws_bytes < size_t(2 * l.plane_bytes + l.w_bytes)) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
-  if (reinterpret_cast<uintptr_t>(ws) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
+  if (!ws || ws_bytes < size_t(2 * l.plane_bytes + (prepared ? 0 : l.w_bytes))) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+  if ((reinterpret_cast<uintptr_t>(ws) | reinterpret_cast<uintptr_t>(prepared)) & 255) return IREE_UK_B200_INVALID_ARGUMENT;
   KernelTiming* timing = kernel_timing();
   cudaEvent_t* tev = timing ? timing->next_slot() : nullptr;
   if (tev) KernelTiming::record(tev[0], stream);
@@ -397,15 +399,17 @@ int launch_mmt4d_tc_s16u4(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_b
   const char* rhs = static_cast<const char*>(p->rhs_buffer) + p->rhs_offset / 2;
   char* hi = static_cast<char*>(ws);
   char* lo = hi + l.plane_bytes;
-  char* w8 = lo + l.plane_bytes;
+  char* w8 = prepared ? const_cast<char*>(static_cast<const char*>(prepared)) : lo + l.plane_bytes;
   {
     const int64_t total = p->M * p->K;
     const int64_t blocks = std::min<int64_t>((total + 255) / 256, 148 * 16);
     split_s16_kernel<<<int(blocks), 256, 0, stream>>>(lhs, p->lhs_stride0 * 2, hi, lo, l.pitch, p->M, p->K);
-    const int64_t kchunks = (p->K + 63) / 64;
-    if (p->N * kchunks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
-    unpack_u4_kernel<<<int(p->N * kchunks), 256, 0, stream>>>(rhs, p->rhs_stride0 / 2, w8, l.pitch,
-                                                            p->K, int(kchunks));
+    if (!prepared) {
+      const int64_t kchunks = (p->K + 63) / 64;
+      if (p->N * kchunks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
+      unpack_u4_kernel<<<int(p->N * kchunks), 256, 0, stream>>>(rhs, p->rhs_stride0 / 2, w8, l.pitch,
+                                                              p->K, int(kchunks));
+    }
     if (cudaGetLastError() != cudaSuccess) return IREE_UK_B200_CUDA_ERROR;
   }
 
@@ -701,6 +705,11 @@ size_t mmt4d_tc_workspace_size(const iree_uk_mmt4d_params_t* p) {
 // Re-tiled RHS kept by the caller across calls (weights): its size, the scratch a call then
 // still needs (the LHS part), and the pre-pass that fills it.
 size_t mmt4d_tc_prepared_rhs_size(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) {
+    // the u4 weights widened to bytes, K-major
+    if (p->M0 != 1 || p->N0 != 32 || p->K0 != 8 || p->K < 1 || p->N < 1) return 0;
+    return size_t(s16u4_layout(p).w_bytes);
+  }
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || ti.triple) return 0;
   if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->N < 1) return 0;
@@ -708,6 +717,10 @@ size_t mmt4d_tc_prepared_rhs_size(const iree_uk_mmt4d_params_t* p) {
   return size_t(round_up(p->N * 16 * pitch, 1024));
 }
 size_t mmt4d_tc_prepared_workspace_size(const iree_uk_mmt4d_params_t* p) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) {
+    if (p->M0 != 1 || p->N0 != 32 || p->K0 != 8 || p->K < 1 || p->M < 1) return 0;
+    return size_t(2 * s16u4_layout(p).plane_bytes);  // the two byte planes of the LHS
+  }
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || ti.triple) return 0;
   if (p->M0 != 16 || p->N0 != 16 || p->K0 < 1 || p->K < 1 || p->M < 1) return 0;
@@ -716,6 +729,21 @@ size_t mmt4d_tc_prepared_workspace_size(const iree_uk_mmt4d_params_t* p) {
 }
 int launch_mmt4d_tc_prepare_rhs(const iree_uk_mmt4d_params_t* p, void* prepared, size_t bytes,
                                 cudaStream_t stream) {
+  if ((p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK) == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) {
+    const size_t need = mmt4d_tc_prepared_rhs_size(p);
+    if (!need) return IREE_UK_B200_UNSUPPORTED;
+    if (!prepared || bytes < need) return IREE_UK_B200_WORKSPACE_TOO_SMALL;
+    const uintptr_t rhs = reinterpret_cast<uintptr_t>(p->rhs_buffer) + uintptr_t(p->rhs_offset / 2);
+    if ((reinterpret_cast<uintptr_t>(prepared) & 255) || (rhs & 15) || (p->rhs_offset & 1) ||
+        (p->rhs_stride0 & 1) || (p->rhs_stride0 / 2) % 16)
+      return IREE_UK_B200_INVALID_ARGUMENT;
+    const int64_t kchunks = (p->K + 63) / 64;
+    if (p->N * kchunks > 0x7FFFFFFF) return IREE_UK_B200_UNSUPPORTED;
+    unpack_u4_kernel<<<int(p->N * kchunks), 256, 0, stream>>>(
+        reinterpret_cast<const char*>(rhs), p->rhs_stride0 / 2, static_cast<char*>(prepared),
+        s16u4_layout(p).pitch, p->K, int(kchunks));
+    return cuda_status(cudaGetLastError());
+  }
   TypeInfo ti;
   if (!tc_type_info(p->flags, &ti) || ti.triple) return IREE_UK_B200_UNSUPPORTED;
   const size_t need = mmt4d_tc_prepared_rhs_size(p);
@@ -751,8 +779,9 @@ int launch_mmt4d_tc(const iree_uk_mmt4d_params_t* p, void* ws, size_t ws_bytes, 
   // Peer copies exist for the plain tiled epilogue only.
   const uint32_t type = p->flags & IREE_UK_FLAG_MMT4D_TYPE_MASK;
   const bool planes = type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32 || type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32;
-  if ((num_peers || multicast_out || prepared_rhs || rm) && planes) return IREE_UK_B200_UNSUPPORTED;
-  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream);
+  if ((num_peers || multicast_out || rm) && planes) return IREE_UK_B200_UNSUPPORTED;
+  if (prepared_rhs && type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32) return IREE_UK_B200_UNSUPPORTED;
+  if (type == IREE_UK_FLAG_MMT4D_TYPE_S16U4S32) return launch_mmt4d_tc_s16u4(p, ws, ws_bytes, stream, prepared_rhs);
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16S16S32) return launch_mmt4d_tc_s16s16(p, ws, ws_bytes, stream);
   if (type == IREE_UK_FLAG_MMT4D_TYPE_S16S8S32) {
     if (num_peers || multicast_out || prepared_rhs || rm) return IREE_UK_B200_UNSUPPORTED;

@@ -298,8 +298,12 @@ def test_scratch_sizes_are_consistent():
     q = _mmt4d(abi.MMT4D_BF16BF16F32, M=7, N=1792, K=4096)   # another M, the same weights
     assert uk.mmt4d_prepared_rhs_size(q) == uk.mmt4d_prepared_rhs_size(p)
     assert uk.mmt4d_workspace_size(_mmt4d(M0=8, N0=8)) == 0
+    # s16u4s32: the prepared form is the weights widened to bytes, the scratch then the two LHS planes
     s = _mmt4d(abi.MMT4D_S16U4S32, M=64, N=4, K=16, M0=1, N0=32, K0=8)
-    assert uk.mmt4d_workspace_size(s) > 0 and uk.mmt4d_prepared_rhs_size(s) == 0
+    assert uk.mmt4d_prepared_rhs_size(s) == 4 * 32 * 128
+    assert uk.mmt4d_prepared_workspace_size(s) == 2 * 64 * 128
+    assert uk.mmt4d_prepared_rhs_size(s) + uk.mmt4d_prepared_workspace_size(s) == uk.mmt4d_workspace_size(s)
+    assert uk.mmt4d_prepared_rhs_size(_mmt4d(abi.MMT4D_S16S16S32, M0=16, N0=16, K0=2)) == 0
     f = _mmt4d(abi.MMT4D_F32F32F32, K0=1)
     assert uk.mmt4d_workspace_size(f) == 0
     prev = uk.set_f32_mode(uk.F32_MODE_TF32X3)

@@ -505,12 +505,43 @@ def test_mmt4d_with_prepared_rhs(t, K0):
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy(), want), (M, acc)
     G.check_device_status()
-    # not applicable: s16u4s32, and an undersized scratch
-    c = cases.Mmt4dCase(abi.MMT4D_S16U4S32, 1, 32, 8, 64, 4, 16, 0, seed=1, mode="normal", loose=False)
+    # not applicable: s16s16s32, and an undersized scratch
+    c = cases.Mmt4dCase(abi.MMT4D_S16S16S32, 16, 16, 2, 64, 4, 16, 0, seed=1, mode="normal", loose=False)
     assert uk.mmt4d_prepared_rhs_size(c.params(0, 0, 0)) == 0
     with pytest.raises(uk.UkernelError) as e:
         uk.mmt4d_prepared(p, prepared, ws[:256])
     assert e.value.status == abi.WORKSPACE_TOO_SMALL
+
+
+def test_mmt4d_s16u4_with_prepared_weights():
+    """s16u4s32 1x32x8: the u4 weights widened to bytes once and kept. The prepared call runs the
+    tensor-core kernel for any number of rows (its pre-pass is then only the byte-plane split of
+    the LHS) and gives the reference's bytes, also below the 16 rows from which the ordinary call
+    would leave the weight-streaming kernel."""
+    import torch
+    from iree_b200 import ukernel as uk
+    N, K = 9, 40
+    prepared, rhs_host = None, None
+    for M, acc in [(40, 0), (1, 1), (5, 0), (300, 1)]:
+        case = cases.Mmt4dCase(abi.MMT4D_S16U4S32, 1, 32, 8, M, N, K, acc, seed=43, mode="normal",
+                               loose=False)
+        if rhs_host is None:
+            rhs_host = case.rhs
+        case.rhs = rhs_host
+        want = G.oracle_mmt4d(case)
+        lhs, rhs, out = G.to_device(case.lhs), G.to_device(case.rhs), G.to_device(case.out_init)
+        p = case.params(lhs.data_ptr(), rhs.data_ptr(), out.data_ptr())
+        if prepared is None:
+            assert uk.mmt4d_prepared_rhs_size(p) == N * 32 * 384  # K * 8 = 320 bytes, 128-byte pitch
+            prepared = torch.empty(uk.mmt4d_prepared_rhs_size(p), dtype=torch.uint8, device="cuda")
+            uk.mmt4d_prepare_rhs(p, prepared)
+        ws = torch.empty(uk.mmt4d_prepared_workspace_size(p), dtype=torch.uint8, device="cuda")
+        assert ws.numel() > 0
+        p.rhs_buffer = 0  # not read once the weights are prepared
+        uk.mmt4d_prepared(p, prepared, ws)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), want), (M, acc)
+    G.check_device_status()
 
 
 def test_concurrent_host_threads_on_their_own_streams():
